@@ -1,0 +1,83 @@
+/* librapidh3_b200 -- C ABI of the B200 (sm_100a) kernels behind the Rapid-H3 operator surface.
+ *
+ * Conventions
+ *   - every entry point returns int: 0 = ok, < 0 = argument error, > 0 = a cudaError_t value;
+ *     rh3_last_error_string() describes the last failure on the calling thread;
+ *   - all pointers are DEVICE pointers unless stated otherwise; the caller owns every buffer,
+ *     the library allocates nothing; work is enqueued on `stream` and never synchronised,
+ *     except by rh3_check_status();
+ *   - activations are bf16, codes are int8 or fp8-e4m3 bytes, scales fp32, row-major;
+ *     strides are in elements of the tensor they describe;
+ *   - "reference" citations are paths inside the jeet0733/Rapid-H3 repository.
+ */
+#ifndef RAPIDH3_B200_H_
+#define RAPIDH3_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __CUDA_RUNTIME_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+#define RH3_KIND_I8 0 /* int8 x int8 -> int32 */
+#define RH3_KIND_F8 1 /* e4m3 x e4m3 -> fp32 */
+
+/* ---- library ------------------------------------------------------------------------------- */
+const char* rh3_last_error_string(void);
+int rh3_version(void);
+int rh3_sm_count(void);
+/* Synchronises `stream`, stores the device status word in *status_out (0 = every bounded device
+ * wait completed; otherwise the code of the wait that gave up) and clears it. */
+int rh3_check_status(cudaStream_t stream, int* status_out);
+
+/* ---- per-token quantizers (HBM-bound) ------------------------------------------------------ */
+/* q[M,K] int8, s[M] fp32: s = max(amax/127, 1e-12), q = clamp(rint(x/s), +-127).
+ * Replaces kernels.quantize_rows(x, "int8_rowwise") (custom_nodes/rapid_h3/kernels.py:75-82) and
+ * triton_fp8.quant_rows_i8 (custom_nodes/rapid_h3/triton_fp8.py:57-64). */
+int rh3_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
+                      cudaStream_t stream);
+/* q[M,K] fp8-e4m3, s = max(amax/448, 1e-12). Replaces kernels.quantize_rows(x, "fp8_rowwise")
+ * (kernels.py:75-82) and triton_fp8.quant_rows (triton_fp8.py:449-455). */
+int rh3_quant_rows_fp8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
+                       cudaStream_t stream);
+/* x[M, 2F]: quantizes silu(x[:, :F]) * x[:, F:] to int8 [M, F].
+ * Replaces triton_fp8.swiglu_rot_quant_rows_i8 without rotation (triton_fp8.py:437-439, prologue :137-139). */
+int rh3_swiglu_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t F, void* q, int64_t ldq, float* s,
+                             cudaStream_t stream);
+/* o[H, M, 128] head-major (stride_h elements between heads) -> q[M, H*128] int8, no transpose copy.
+ * Replaces triton_fp8.rot_quant_heads_i8 without rotation (triton_fp8.py:429-434, gather :134-135). */
+int rh3_quant_heads_i8(const void* o, int64_t stride_h, int64_t H, int64_t M, void* q, int64_t ldq, float* s,
+                       cudaStream_t stream);
+/* y = rms_norm(x, eps) * w * (1 + scale[idx[m]]) + shift[idx[m]] -> int8 rows. w may be NULL.
+ * shift/scale are fp32 tables with row stride ld_tab. Replaces triton_fp8.norm_mod_rot_quant_rows_i8
+ * without rotation (triton_fp8.py:442-446, prologue :141-148, :165-172). */
+int rh3_norm_mod_quant_rows_i8(const void* x, int64_t ldx, const void* w, float eps, const int32_t* idx,
+                               const float* shift, const float* scale, int64_t ld_tab, int64_t M, int64_t K,
+                               void* q, int64_t ldq, float* s, cudaStream_t stream);
+
+/* ---- W8A8 row-wise-scaled GEMMs (tensor-core bound) ---------------------------------------- */
+/* out[M,N] bf16 = ((acc * xs[m]) * ws[n]) + bias[n]; xq[M,K] (row stride lda), wq[N,K] contiguous.
+ * bias may be NULL. acc_dump (optional, [M,N] int32 / fp32 bits) receives the raw accumulators.
+ * Replaces int8_rowwise_gemm / fp8_rowwise_gemm (custom_nodes/rapid_h3/csrc/fp8_rowwise.cu:512-584)
+ * and the emulation in kernels.linear (kernels.py:129-137). */
+int rh3_gemm_w8a8(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws, const void* bias,
+                  int64_t M, int64_t N, int64_t K, int kind, void* out, int64_t ldo, int32_t* acc_dump,
+                  cudaStream_t stream);
+/* resid[M,N] = bf16(fma(bf16((acc*xs)*ws), gate[n], resid)) in place (row stride ldr). M == 0 is a no-op.
+ * Replaces int8_gemm_gated_residual (fp8_rowwise.cu:333-389, :587-608). */
+int rh3_gemm_w8a8_gated_residual(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws,
+                                 const void* gate, void* resid, int64_t ldr, int64_t M, int64_t N, int64_t K,
+                                 int kind, cudaStream_t stream);
+/* wq rows interleaved [g 4j..4j+3 | u 4j..4j+3]; out[M, N/2] = bf16(silu(bf16 g) * bf16 u).
+ * Replaces int8_gemm_swiglu (fp8_rowwise.cu:29-107, :611-629; row order cutlass_fp8.py:55-62). */
+int rh3_gemm_w8a8_swiglu(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws, int64_t M,
+                         int64_t N, int64_t K, int kind, void* out, int64_t ldo, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RAPIDH3_B200_H_ */

@@ -1,0 +1,371 @@
+// Row-wise-scaled W8A8 GEMM on the Blackwell tensor cores.
+//
+//   acc[m, n] = sum_k xq[m, k] * wq[n, k]          int8 x int8 -> int32 (tcgen05 kind::i8), or
+//                                                   e4m3 x e4m3 -> fp32 (tcgen05 kind::f8f6f4)
+//   EPI_PLAIN : out[m, n]   = bf16(((float(acc) * xs[m]) * ws[n]) + bias[n])
+//   EPI_GATED : resid[m, n] = bf16(fma(bf16((float(acc) * xs[m]) * ws[n]), gate[n], resid[m, n]))   (in place)
+//   EPI_SWIGLU: columns come in groups of 8 = [g 4j..4j+3 | u 4j..4j+3];
+//               out[m, n/2] = bf16(silu(bf16(g)) * bf16(u)), half-width store
+// (reference: custom_nodes/rapid_h3/csrc/fp8_rowwise.cu:294-304 plain epilogue, :333-336 gated
+//  residual, :74-93 SwiGLU store; PyTorch emulation custom_nodes/rapid_h3/kernels.py:129-137).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: 128x128-byte A tile + 256x128-byte B tile per stage, 4-stage ring
+//   warp 1      MMA issuer: 4 x tcgen05.mma (M128 N256 K32) per stage into a TMEM accumulator;
+//               two 256-column accumulators so the epilogue of tile i overlaps the main loop of i+1
+//   warps 2..5  epilogue: tcgen05.ld 32 columns at a time, dequantize, fused epilogue, 64-byte
+//               contiguous bf16 stores per thread-row
+// Tensor-core bound: 2*M*N*K operations per call.
+#include "common.cuh"
+#include "rapidh3_b200.h"
+
+namespace rh3 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // bytes (= elements for 8-bit operands) along K per stage
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;
+constexpr int B_BYTES = BN * BK;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 16;  // tile rasterisation: 16 row-tiles share each column-tile in L2
+
+enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_SWIGLU = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  const float* xs;
+  const float* ws;
+  const __nv_bfloat16* bias;  // EPI_PLAIN, optional
+  __nv_bfloat16* out;         // EPI_PLAIN / EPI_SWIGLU
+  int64_t ldo;
+  int32_t* acc_dump;          // optional raw accumulator dump [M, N] (int32, or fp32 bits for fp8)
+  const __nv_bfloat16* gate;  // EPI_GATED
+  __nv_bfloat16* resid;       // EPI_GATED
+  int64_t ldr;
+  int* status;
+};
+
+struct __align__(8) GemmSmemTail {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float ws[BN];
+  float aux[BN];  // bias or gate as fp32
+};
+
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + sizeof(GemmSmemTail) + 1024;  // +1024 alignment slack
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
+  const int per_group = GROUP_M * num_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsize = min(GROUP_M, num_m - first_m);
+  const int t = tile - g * per_group;
+  m_blk = first_m + t % gsize;
+  n_blk = t / gsize;
+}
+
+template <int KIND_F8, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(smem + STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &tail->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail->acc_full[b], 1);
+      mbar_init(&tail->acc_empty[b], 128);
+    }
+    tail->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(tile, num_m, num_n, m_blk, n_blk);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&tail->empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_arrive_expect_tx(&tail->full[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tma_a, kb * BK, m_blk * BM, &tail->full[stage]);
+          tma_load_2d(sb, &tma_b, kb * BK, n_blk * BN, &tail->full[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = KIND_F8 ? make_idesc(1, 0, 0, BM, BN) : make_idesc(2, 1, 1, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            const uint64_t adesc = make_desc_k128(a_addr + k * 32);
+            const uint64_t bdesc = make_desc_k128(b_addr + k * 32);
+            if (KIND_F8) mma_f8_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            else mma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          mma_commit(&tail->empty[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&tail->acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ------------------------------
+    const int quad = warp & 3;           // TMEM lane quadrant this warp may read
+    const int et = threadIdx.x - 64;     // 0..127
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      const int n0 = n_blk * BN;
+      // stage the per-column scale (and bias / gate) of this tile in shared memory
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // previous tile's readers are done
+      for (int c = et; c < BN; c += 128) {
+        const int n = n0 + c;
+        tail->ws[c] = n < p.N ? p.ws[n] : 0.f;
+        if (EPI == EPI_PLAIN) tail->aux[c] = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+        if (EPI == EPI_GATED) tail->aux[c] = n < p.N ? __bfloat162float(p.gate[n]) : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) break;
+      tc_fence_after();
+      const int row = m_blk * BM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const float xs = row_ok ? p.xs[row] : 0.f;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+          if (p.acc_dump) {
+            int32_t* d = p.acc_dump + static_cast<int64_t>(row) * p.N + col0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              if (col0 + j + 4 <= p.N) *reinterpret_cast<uint4*>(d + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+          }
+          float y[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float a = KIND_F8 ? __uint_as_float(r[j]) : __int2float_rn(static_cast<int>(r[j]));
+            y[j] = __fmul_rn(__fmul_rn(a, xs), tail->ws[c * 32 + j]);
+          }
+          if (EPI == EPI_PLAIN) {
+            __nv_bfloat16* o = p.out + static_cast<int64_t>(row) * p.ldo + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 + 8 <= p.N) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int e = g * 8 + 2 * j;
+                  w[j] = pack_bf16x2(__fadd_rn(y[e], tail->aux[c * 32 + e]), __fadd_rn(y[e + 1], tail->aux[c * 32 + e + 1]));
+                }
+                *reinterpret_cast<uint4*>(o + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          } else if (EPI == EPI_GATED) {
+            __nv_bfloat16* o = p.resid + static_cast<int64_t>(row) * p.ldr + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 + 8 <= p.N) {
+                const uint4 old = *reinterpret_cast<const uint4*>(o + g * 8);
+                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int e = g * 8 + 2 * j;
+                  const float v0 = fmaf(bf16_round(y[e]), tail->aux[c * 32 + e], bf16_lo(ow[j]));
+                  const float v1 = fmaf(bf16_round(y[e + 1]), tail->aux[c * 32 + e + 1], bf16_hi(ow[j]));
+                  w[j] = pack_bf16x2(v0, v1);
+                }
+                *reinterpret_cast<uint4*>(o + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          } else {  // EPI_SWIGLU: 32 columns = 4 groups of [g0..g3 | u0..u3] -> 16 outputs
+            __nv_bfloat16* o = p.out + static_cast<int64_t>(row) * p.ldo + (col0 >> 1);
+#pragma unroll
+            for (int hgrp = 0; hgrp < 2; ++hgrp) {  // 16 columns -> 8 outputs -> one 16-byte store
+              if (col0 + hgrp * 16 + 16 <= p.N) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {  // one group of 8 columns -> 4 outputs
+                  const int b = hgrp * 16 + q * 8;
+                  float h[4];
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float gv = bf16_round(y[b + j]);
+                    const float uv = bf16_round(y[b + 4 + j]);
+                    h[j] = gv / (1.f + __expf(-gv)) * uv;
+                  }
+                  w[q * 2] = pack_bf16x2(h[0], h[1]);
+                  w[q * 2 + 1] = pack_bf16x2(h[2], h[3]);
+                }
+                *reinterpret_cast<uint4*>(o + hgrp * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tail->acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  __syncwarp();
+  if (*abort_flag && threadIdx.x == 0) {
+    // give copies that may still be in flight time to land before shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int KIND_F8, int EPI>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  auto kern = gemm_w8a8_kernel<KIND_F8, EPI>;
+  if (int e = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES),
+                         "gemm smem attribute"))
+    return e;
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = num_tiles < device_sm_count() ? num_tiles : device_sm_count();
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "gemm launch");
+}
+
+int gemm_common(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws, int64_t M, int64_t N,
+                int64_t K, int kind, CUtensorMap* ta, CUtensorMap* tb) {
+  RH3_CHECK_ARG(kind == RH3_KIND_I8 || kind == RH3_KIND_F8, "gemm_w8a8: kind must be RH3_KIND_I8 or RH3_KIND_F8");
+  RH3_CHECK_ARG(M >= 0 && N > 0 && K > 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31),
+                "gemm_w8a8: bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  RH3_CHECK_ARG(K % 16 == 0, "gemm_w8a8: K=%lld must be a multiple of 16", (long long)K);
+  RH3_CHECK_ARG(N % 8 == 0, "gemm_w8a8: N=%lld must be a multiple of 8", (long long)N);
+  RH3_CHECK_ARG(lda >= K && lda % 16 == 0, "gemm_w8a8: xq row stride must be >= K and a multiple of 16");
+  if (M == 0) return 0;
+  RH3_CHECK_ARG(xq && wq && xs && ws, "gemm_w8a8: null pointer");
+  RH3_CHECK_ARG((reinterpret_cast<uintptr_t>(xq) & 15) == 0 && (reinterpret_cast<uintptr_t>(wq) & 15) == 0,
+                "gemm_w8a8: xq and wq must be 16-byte aligned");
+  if (int e = make_tmap_2d(ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, K, M, lda, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return e;
+  if (int e = make_tmap_2d(tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wq, K, N, K, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B))
+    return e;
+  return 0;
+}
+
+}  // namespace
+}  // namespace rh3
+
+using namespace rh3;
+
+extern "C" int rh3_gemm_w8a8(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws,
+                             const void* bias, int64_t M, int64_t N, int64_t K, int kind, void* out, int64_t ldo,
+                             int32_t* acc_dump, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (int e = gemm_common(xq, lda, wq, xs, ws, M, N, K, kind, &ta, &tb)) return e;
+  if (M == 0) return 0;
+  RH3_CHECK_ARG(out && ldo >= N && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+                "gemm_w8a8: out must be 16-byte aligned with a row stride >= N that is a multiple of 8");
+  RH3_CHECK_ARG(!acc_dump || (reinterpret_cast<uintptr_t>(acc_dump) & 15) == 0, "gemm_w8a8: acc_dump misaligned");
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.acc_dump = acc_dump; p.status = device_status_word();
+  return kind == RH3_KIND_F8 ? launch_gemm<1, EPI_PLAIN>(ta, tb, p, stream) : launch_gemm<0, EPI_PLAIN>(ta, tb, p, stream);
+}
+
+extern "C" int rh3_gemm_w8a8_gated_residual(const void* xq, int64_t lda, const void* wq, const float* xs,
+                                            const float* ws, const void* gate, void* resid, int64_t ldr, int64_t M,
+                                            int64_t N, int64_t K, int kind, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (int e = gemm_common(xq, lda, wq, xs, ws, M, N, K, kind, &ta, &tb)) return e;
+  if (M == 0) return 0;
+  RH3_CHECK_ARG(gate && resid && ldr >= N && ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0,
+                "gemm_w8a8_gated_residual: resid must be 16-byte aligned with a row stride >= N, multiple of 8");
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.resid = static_cast<__nv_bfloat16*>(resid); p.ldr = ldr; p.status = device_status_word();
+  return kind == RH3_KIND_F8 ? launch_gemm<1, EPI_GATED>(ta, tb, p, stream) : launch_gemm<0, EPI_GATED>(ta, tb, p, stream);
+}
+
+extern "C" int rh3_gemm_w8a8_swiglu(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws,
+                                    int64_t M, int64_t N, int64_t K, int kind, void* out, int64_t ldo,
+                                    cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (int e = gemm_common(xq, lda, wq, xs, ws, M, N, K, kind, &ta, &tb)) return e;
+  RH3_CHECK_ARG(N % 16 == 0, "gemm_w8a8_swiglu: N=%lld must be a multiple of 16", (long long)N);
+  if (M == 0) return 0;
+  RH3_CHECK_ARG(out && ldo >= N / 2 && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+                "gemm_w8a8_swiglu: out must be 16-byte aligned with a row stride >= N/2 that is a multiple of 8");
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
+  p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.status = device_status_word();
+  return kind == RH3_KIND_F8 ? launch_gemm<1, EPI_SWIGLU>(ta, tb, p, stream) : launch_gemm<0, EPI_SWIGLU>(ta, tb, p, stream);
+}

@@ -1,0 +1,299 @@
+// Per-token (row) activation quantizers: abs-max symmetric int8 / fp8-e4m3 with optional fused
+// prologues. One CTA owns one row; the row is read ONCE from HBM with 128-bit loads, held in
+// registers through the prologue, the abs-max reduction and the quantization, and the codes are
+// written once. HBM-bound: algorithmic traffic is 2 bytes in + 1 byte out per element.
+//
+// Semantics follow the reference's PyTorch emulation exactly (bit-exact codes and scales):
+//   int8: s = max(amax/127, 1e-12), q = clamp(round_half_even(x / s), -127, 127)
+//   fp8 : s = max(amax/448, 1e-12), q = e4m3_rn(clamp(x / s, -448, 448))
+// (reference: custom_nodes/rapid_h3/kernels.py:75-82; fast kernels triton_fp8.py:17-64).
+// Prologues (reference: triton_fp8.py:128-148 `_load_act`):
+//   KIND_PLAIN   x
+//   KIND_SWIGLU  silu(x[:, k]) * x[:, F + k]
+//   KIND_NORMMOD rms_norm(x) * w * (1 + scale[idx[row]]) + shift[idx[row]]
+//   KIND_HEADS   x given head-major [H, M, 128]; output column k = head k/128, channel k%128
+// The division x / s is done as x * (1/s) with an exact IEEE re-division only for the rare values
+// that land within 1e-3 of a rounding tie, which keeps the codes identical to a true division.
+#include "common.cuh"
+#include "rapidh3_b200.h"
+
+namespace rh3 {
+namespace {
+
+enum { KIND_PLAIN = 0, KIND_SWIGLU = 1, KIND_NORMMOD = 2, KIND_HEADS = 3 };
+
+struct QuantParams {
+  const __nv_bfloat16* x;
+  int64_t ldx;        // row stride of x in elements (KIND_HEADS: stride between heads)
+  int64_t M, K;       // rows, quantized width
+  void* q;
+  int64_t ldq;
+  float* s;
+  // KIND_NORMMOD
+  const __nv_bfloat16* w;  // may be null
+  float eps;
+  const int32_t* idx;
+  const float* shift;
+  const float* scale;
+  int64_t ld_tab;
+  // KIND_SWIGLU: F == K, the up half starts at column K
+};
+
+__device__ __forceinline__ void unpack8(const uint4& u, float* v) {
+  v[0] = bf16_lo(u.x); v[1] = bf16_hi(u.x); v[2] = bf16_lo(u.y); v[3] = bf16_hi(u.y);
+  v[4] = bf16_lo(u.z); v[5] = bf16_hi(u.z); v[6] = bf16_lo(u.w); v[7] = bf16_hi(u.w);
+}
+
+// block-wide max over T threads; result returned to all threads
+template <int T>
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = red[0];
+#pragma unroll
+  for (int w = 1; w < T / 32; ++w) r = fmaxf(r, red[w]);
+  __syncthreads();
+  return r;
+}
+// block-wide sum in a fixed order: xor-butterfly inside each warp, then warps in index order
+template <int T>
+__device__ __forceinline__ float block_sum_fixed(float v, float* red) {
+  v = warp_sum_xor(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = red[0];
+#pragma unroll
+  for (int w = 1; w < T / 32; ++w) r = __fadd_rn(r, red[w]);
+  __syncthreads();
+  return r;
+}
+
+__device__ __forceinline__ int quant_i8_one(float y, float s, float inv) {
+  float yq = __fmul_rn(y, inv);
+  float r = rintf(yq);
+  if (fabsf(fabsf(yq - r) - 0.5f) < 1e-3f) r = rintf(__fdiv_rn(y, s));  // near a tie: exact division decides
+  r = fminf(fmaxf(r, -127.f), 127.f);
+  return static_cast<int>(r);
+}
+__device__ __forceinline__ uint32_t quant_f8_one(float y, float s, float inv) {
+  float yq = __fmul_rn(y, inv);
+  yq = fminf(fmaxf(yq, -448.f), 448.f);
+  uint32_t a = __nv_cvt_float_to_fp8(yq * (1.f - 0x1p-21f), __NV_SATFINITE, __NV_E4M3);
+  uint32_t b = __nv_cvt_float_to_fp8(yq * (1.f + 0x1p-21f), __NV_SATFINITE, __NV_E4M3);
+  if (a != b) {
+    float ye = fminf(fmaxf(__fdiv_rn(y, s), -448.f), 448.f);
+    a = __nv_cvt_float_to_fp8(ye, __NV_SATFINITE, __NV_E4M3);
+  }
+  return a & 0xFFu;
+}
+
+template <int KIND, int OUT_FP8, int T, int CPT>
+__global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
+  __shared__ float red[T / 32];
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int nchunk = static_cast<int>(p.K >> 3);
+
+  float v[CPT][8];
+  // ---- load (all loads issued before any use) ----
+  uint4 raw[CPT];
+  uint4 raw2[KIND == KIND_SWIGLU ? CPT : 1];
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) {
+    const int c = tid + i * T;
+    raw[i] = make_uint4(0, 0, 0, 0);
+    if (KIND == KIND_SWIGLU) raw2[i] = make_uint4(0, 0, 0, 0);
+    if (c < nchunk) {
+      const __nv_bfloat16* src;
+      if (KIND == KIND_HEADS) {
+        const int col = c << 3;
+        src = p.x + static_cast<int64_t>(col >> 7) * p.ldx + row * 128 + (col & 127);
+      } else {
+        src = p.x + row * p.ldx + (static_cast<int64_t>(c) << 3);
+      }
+      raw[i] = __ldg(reinterpret_cast<const uint4*>(src));
+      if (KIND == KIND_SWIGLU) raw2[i] = __ldg(reinterpret_cast<const uint4*>(src + p.K));
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) unpack8(raw[i], v[i]);
+
+  if (KIND == KIND_SWIGLU) {
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      float u[8];
+      unpack8(raw2[i], u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g = v[i][j];
+        const float sg = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-g)));
+        v[i][j] = __fmul_rn(__fmul_rn(g, sg), u[j]);
+      }
+    }
+  }
+
+  if (KIND == KIND_NORMMOD) {
+    // sum of squares in a fixed order (thread-sequential over its chunks, then the block tree)
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(v[i][j], v[i][j]));
+    }
+    ss = block_sum_fixed<T>(ss, red);
+    const float rstd = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(p.K)), p.eps)));
+    const int64_t trow = static_cast<int64_t>(p.idx[row]) * p.ld_tab;
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      const int c = tid + i * T;
+      if (c < nchunk) {
+        const int col = c << 3;
+        float wv[8];
+        if (p.w) {
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.w + col)), wv);
+        }
+        const float4 sc0 = __ldg(reinterpret_cast<const float4*>(p.scale + trow + col));
+        const float4 sc1 = __ldg(reinterpret_cast<const float4*>(p.scale + trow + col + 4));
+        const float4 sh0 = __ldg(reinterpret_cast<const float4*>(p.shift + trow + col));
+        const float4 sh1 = __ldg(reinterpret_cast<const float4*>(p.shift + trow + col + 4));
+        const float sc[8] = {sc0.x, sc0.y, sc0.z, sc0.w, sc1.x, sc1.y, sc1.z, sc1.w};
+        const float sh[8] = {sh0.x, sh0.y, sh0.z, sh0.w, sh1.x, sh1.y, sh1.z, sh1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float y = __fmul_rn(v[i][j], rstd);
+          if (p.w) y = __fmul_rn(y, wv[j]);
+          y = __fadd_rn(__fmul_rn(y, __fadd_rn(1.f, sc[j])), sh[j]);
+          v[i][j] = y;
+        }
+      }
+    }
+  }
+
+  // ---- abs-max and scale ----
+  float am = 0.f;
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(v[i][j]));
+  }
+  am = block_max<T>(am, red);
+  const float qmax = OUT_FP8 ? 448.f : 127.f;
+  const float s = fmaxf(__fdiv_rn(am, qmax), 1e-12f);
+  const float inv = __fdiv_rn(1.f, s);
+  if (tid == 0) p.s[row] = s;
+
+  // ---- quantize + store ----
+  uint8_t* qrow = reinterpret_cast<uint8_t*>(p.q) + row * p.ldq;
+#pragma unroll
+  for (int i = 0; i < CPT; ++i) {
+    const int c = tid + i * T;
+    if (c < nchunk) {
+      uint32_t o[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t code;
+          if (OUT_FP8) code = quant_f8_one(v[i][4 * h + j], s, inv);
+          else code = static_cast<uint32_t>(quant_i8_one(v[i][4 * h + j], s, inv)) & 0xFFu;
+          packed |= code << (8 * j);
+        }
+        o[h] = packed;
+      }
+      *reinterpret_cast<uint2*>(qrow + (static_cast<int64_t>(c) << 3)) = make_uint2(o[0], o[1]);
+    }
+  }
+}
+
+template <int KIND, int OUT_FP8>
+int launch_quant(const QuantParams& p, cudaStream_t stream) {
+  const int64_t nchunk = p.K >> 3;
+  if (p.M == 0) return 0;
+#define RH3_Q(T_, CPT_)                                                                                \
+  quant_rows_kernel<KIND, OUT_FP8, T_, CPT_><<<static_cast<unsigned>(p.M), T_, 0, stream>>>(p)
+  if (nchunk <= 128) RH3_Q(128, 1);
+  else if (nchunk <= 256) RH3_Q(128, 2);
+  else if (nchunk <= 512) RH3_Q(128, 4);
+  else if (nchunk <= 1024) RH3_Q(128, 8);
+  else if (nchunk <= 2048) RH3_Q(256, 8);
+  else if (nchunk <= 4096) RH3_Q(512, 8);
+  else if (nchunk <= 8192) RH3_Q(1024, 8);
+  else return set_error(RH3_ARG_ERROR, "quant_rows: K=%lld is larger than 65536", (long long)p.K);
+#undef RH3_Q
+  return check_cuda(cudaGetLastError(), "quant_rows launch");
+}
+
+int check_common(const void* x, int64_t ldx, int64_t M, int64_t K, const void* q, int64_t ldq, const float* s) {
+  RH3_CHECK_ARG(M >= 0 && K > 0, "quant_rows: bad shape M=%lld K=%lld", (long long)M, (long long)K);
+  RH3_CHECK_ARG(M < (1ll << 31), "quant_rows: M too large");
+  RH3_CHECK_ARG(K % 8 == 0, "quant_rows: K=%lld must be a multiple of 8", (long long)K);
+  RH3_CHECK_ARG(M == 0 || (x && q && s), "quant_rows: null pointer");
+  RH3_CHECK_ARG(ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0,
+                "quant_rows: x must be 16-byte aligned with a row stride that is a multiple of 8 elements");
+  RH3_CHECK_ARG(ldq % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+                "quant_rows: q must be 8-byte aligned with a row stride that is a multiple of 8");
+  return 0;
+}
+
+}  // namespace
+}  // namespace rh3
+
+using namespace rh3;
+
+extern "C" int rh3_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
+                                 cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, K, q, ldq, s)) return e;
+  RH3_CHECK_ARG(ldx >= K && ldq >= K, "quant_rows_i8: row strides smaller than K");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = K; p.q = q; p.ldq = ldq; p.s = s;
+  return launch_quant<KIND_PLAIN, 0>(p, stream);
+}
+
+extern "C" int rh3_quant_rows_fp8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
+                                  cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, K, q, ldq, s)) return e;
+  RH3_CHECK_ARG(ldx >= K && ldq >= K, "quant_rows_fp8: row strides smaller than K");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = K; p.q = q; p.ldq = ldq; p.s = s;
+  return launch_quant<KIND_PLAIN, 1>(p, stream);
+}
+
+extern "C" int rh3_swiglu_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t F, void* q, int64_t ldq,
+                                        float* s, cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, F, q, ldq, s)) return e;
+  RH3_CHECK_ARG(ldx >= 2 * F && ldq >= F, "swiglu_quant_rows_i8: row strides too small");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = F; p.q = q; p.ldq = ldq; p.s = s;
+  return launch_quant<KIND_SWIGLU, 0>(p, stream);
+}
+
+extern "C" int rh3_quant_heads_i8(const void* o, int64_t stride_h, int64_t H, int64_t M, void* q, int64_t ldq,
+                                  float* s, cudaStream_t stream) {
+  RH3_CHECK_ARG(H > 0, "quant_heads_i8: H must be positive");
+  if (int e = check_common(o, stride_h, M, H * 128, q, ldq, s)) return e;
+  RH3_CHECK_ARG(stride_h >= M * 128 && ldq >= H * 128, "quant_heads_i8: strides too small");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(o); p.ldx = stride_h; p.M = M; p.K = H * 128; p.q = q; p.ldq = ldq; p.s = s;
+  return launch_quant<KIND_HEADS, 0>(p, stream);
+}
+
+extern "C" int rh3_norm_mod_quant_rows_i8(const void* x, int64_t ldx, const void* w, float eps, const int32_t* idx,
+                                          const float* shift, const float* scale, int64_t ld_tab, int64_t M,
+                                          int64_t K, void* q, int64_t ldq, float* s, cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, K, q, ldq, s)) return e;
+  RH3_CHECK_ARG(ldx >= K && ldq >= K, "norm_mod_quant_rows_i8: row strides smaller than K");
+  RH3_CHECK_ARG(M == 0 || (idx && shift && scale), "norm_mod_quant_rows_i8: null modulation pointer");
+  RH3_CHECK_ARG(ld_tab % 4 == 0 && (reinterpret_cast<uintptr_t>(shift) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(scale) & 15) == 0,
+                "norm_mod_quant_rows_i8: shift/scale must be 16-byte aligned, row stride a multiple of 4");
+  RH3_CHECK_ARG(!w || (reinterpret_cast<uintptr_t>(w) & 15) == 0, "norm_mod_quant_rows_i8: w must be 16-byte aligned");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = K; p.q = q; p.ldq = ldq; p.s = s;
+  p.w = static_cast<const __nv_bfloat16*>(w); p.eps = eps; p.idx = idx; p.shift = shift; p.scale = scale;
+  p.ld_tab = ld_tab;
+  return launch_quant<KIND_NORMMOD, 0>(p, stream);
+}

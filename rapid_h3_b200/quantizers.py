@@ -1,0 +1,106 @@
+"""Per-token activation quantizers; same names and argument meaning as the reference's
+custom_nodes/rapid_h3/triton_fp8.py (`quant_rows`, `quant_rows_i8`, `rot_quant_rows_i8`,
+`rot_quant_heads_i8`, `swiglu_rot_quant_rows_i8`, `norm_mod_rot_quant_rows_i8`), each a single
+CUDA kernel launch through the C ABI.
+
+The `rot_*` names keep the reference's spelling; the H256 rotation itself is applied only when
+`rotate=True` is requested and is not available yet (the un-rotated `int8_rowwise` recipe is what
+the kernels implement), so asking for it raises NotImplementedError instead of silently differing.
+"""
+import torch
+
+from . import _lib
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+ROT_GROUP = 256
+
+
+def _check_rows(x):
+    _lib.require_cuda(x)
+    assert x.ndim == 2 and x.stride(1) == 1, "expected a 2-D tensor with unit column stride"
+    if x.dtype != torch.bfloat16:
+        raise RuntimeError(f"expected bf16 activations, got {x.dtype}")
+
+
+def quant_rows_i8(x):
+    """Per-row symmetric INT8: s = amax / 127, q = rint(x / s). Returns (q int8 [M,K], s fp32 [M,1])."""
+    _check_rows(x)
+    m, k = x.shape
+    q = torch.empty((m, k), device=x.device, dtype=torch.int8)
+    s = torch.empty((m, 1), device=x.device, dtype=torch.float32)
+    _lib.call("rh3_quant_rows_i8", x.data_ptr(), x.stride(0), m, k, q.data_ptr(), q.stride(0), s.data_ptr(),
+              _lib.stream())
+    return q, s
+
+
+def quant_rows(x):
+    """Per-row FP8 e4m3: s = amax / 448. Returns (q fp8 [M,K], s fp32 [M,1])."""
+    _check_rows(x)
+    m, k = x.shape
+    q = torch.empty((m, k), device=x.device, dtype=FP8)
+    s = torch.empty((m, 1), device=x.device, dtype=torch.float32)
+    _lib.call("rh3_quant_rows_fp8", x.data_ptr(), x.stride(0), m, k, q.data_ptr(), q.stride(0), s.data_ptr(),
+              _lib.stream())
+    return q, s
+
+
+def _no_rotation(rotate):
+    if rotate:
+        raise NotImplementedError("H256 ConvRot rotation is not implemented; use rotate=False (int8_rowwise)")
+
+
+def rot_quant_rows_i8(x, rotate=False):
+    _no_rotation(rotate)
+    return quant_rows_i8(x)
+
+
+def rot_quant_heads_i8(o, rotate=False):
+    """o [H, M, 128] bf16 head-major (attention output) -> (q int8 [M, H*128], s [M,1]), read in place."""
+    _no_rotation(rotate)
+    _lib.require_cuda(o)
+    assert o.ndim == 3 and o.shape[2] == 128 and o.stride(2) == 1 and o.stride(1) == 128
+    if o.dtype != torch.bfloat16:
+        raise RuntimeError(f"expected bf16 activations, got {o.dtype}")
+    h, m, _ = o.shape
+    q = torch.empty((m, h * 128), device=o.device, dtype=torch.int8)
+    s = torch.empty((m, 1), device=o.device, dtype=torch.float32)
+    _lib.call("rh3_quant_heads_i8", o.data_ptr(), o.stride(0), h, m, q.data_ptr(), q.stride(0), s.data_ptr(),
+              _lib.stream())
+    return q, s
+
+
+def swiglu_rot_quant_rows_i8(x, rotate=False):
+    """x [M, 2F] = [gate | up] -> int8 of silu(gate) * up, [M, F]."""
+    _no_rotation(rotate)
+    _check_rows(x)
+    m, k2 = x.shape
+    f = k2 // 2
+    q = torch.empty((m, f), device=x.device, dtype=torch.int8)
+    s = torch.empty((m, 1), device=x.device, dtype=torch.float32)
+    _lib.call("rh3_swiglu_quant_rows_i8", x.data_ptr(), x.stride(0), m, f, q.data_ptr(), q.stride(0), s.data_ptr(),
+              _lib.stream())
+    return q, s
+
+
+def norm_mod_rot_quant_rows_i8(x, weight, eps, idx, shift, scale, rotate=False):
+    """int8 of rms_norm(x) * weight * (1 + scale[idx]) + shift[idx], per-row scales.
+
+    weight: bf16 [K] or None; idx: int32 [M]; shift / scale: fp32 [R, K] views with a common row
+    stride (the six AdaLN tables of a block are views into one [R, 6K] tensor)."""
+    _no_rotation(rotate)
+    _check_rows(x)
+    m, k = x.shape
+    _lib.require_cuda(idx, shift, scale, weight)
+    assert idx.dtype == torch.int32 and idx.numel() == m and idx.is_contiguous()
+    assert shift.dtype == torch.float32 and scale.dtype == torch.float32
+    assert shift.ndim == 2 and scale.ndim == 2 and shift.shape[1] == k and scale.shape[1] == k
+    assert shift.stride(1) == 1 and scale.stride(1) == 1 and shift.stride(0) == scale.stride(0)
+    if weight is not None:
+        assert weight.dtype == torch.bfloat16 and weight.numel() == k and weight.is_contiguous()
+    q = torch.empty((m, k), device=x.device, dtype=torch.int8)
+    s = torch.empty((m, 1), device=x.device, dtype=torch.float32)
+    _lib.call("rh3_norm_mod_quant_rows_i8", x.data_ptr(), x.stride(0), _lib.ptr(weight), float(eps), idx.data_ptr(),
+              shift.data_ptr(), scale.data_ptr(), shift.stride(0), m, k, q.data_ptr(), q.stride(0), s.data_ptr(),
+              _lib.stream())
+    return q, s

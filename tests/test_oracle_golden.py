@@ -1,0 +1,92 @@
+"""The CPU oracle against golden vectors produced by the reference's own PyTorch emulation
+(tests/golden/make_golden.py imports custom_nodes/rapid_h3/kernels.py)."""
+import pytest
+import torch
+
+from oracle import linear as ol
+from oracle import quant as oq
+
+
+def _codes(t):
+    return t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+
+
+@pytest.mark.parametrize("case", ["a", "b"])
+@pytest.mark.parametrize("mode", ["int8_rowwise", "fp8_rowwise"])
+def test_quantizers_match_reference(golden_linear, case, mode):
+    c = golden_linear[case]
+    g = c[mode]
+    xq, xs = ol.quantize_rows(c["x"], mode)
+    wq, ws = ol.quantize_weight(c["w"], mode)
+    assert torch.equal(_codes(xq), g["xq"]) and torch.equal(xs, g["xs"])
+    assert torch.equal(_codes(wq), g["wq"]) and torch.equal(ws, g["ws"])
+
+
+@pytest.mark.parametrize("case", ["a", "b"])
+def test_int8_linear_matches_reference(golden_linear, case):
+    c = golden_linear[case]
+    g = c["int8_rowwise"]
+    y = ol.linear(c["x"], g["wq"], g["ws"], "int8_rowwise")
+    assert torch.equal(y, g["y"])  # same expression order as kernels.py:137
+
+
+@pytest.mark.parametrize("case", ["a", "b"])
+def test_fp8_linear_matches_reference(golden_linear, case):
+    c = golden_linear[case]
+    g = c["fp8_rowwise"]
+    wq = g["wq"].view(torch.float8_e4m3fn)
+    y = ol.linear(c["x"], wq, g["ws"], "fp8_rowwise").float()
+    # the reference's _scaled_mm rounds the product to bf16 before the scales are applied
+    # (kernels.py:133-137); the fused epilogue keeps fp32, so the two differ by one bf16 rounding
+    rel = (y - g["y"].float()).norm() / g["y"].float().norm()
+    assert rel < 4e-3
+
+
+def test_int_mm_fallback_is_exact():
+    g = torch.Generator().manual_seed(1)
+    a = torch.randint(-127, 128, (9, 48), generator=g, dtype=torch.int8)
+    b = torch.randint(-127, 128, (10, 48), generator=g, dtype=torch.int8)
+    assert torch.equal(ol.int_mm(a, b), (a.long() @ b.long().t()).to(torch.int32))
+    a = torch.randint(-127, 128, (64, 64), generator=g, dtype=torch.int8)
+    b = torch.randint(-127, 128, (32, 64), generator=g, dtype=torch.int8)
+    assert torch.equal(ol.int_mm(a, b), (a.long() @ b.long().t()).to(torch.int32))
+
+
+def test_swiglu_perm_and_epilogue():
+    f = 16
+    perm = ol.swiglu_perm(2 * f)
+    assert perm[:8].tolist() == [0, 1, 2, 3, f, f + 1, f + 2, f + 3]
+    g = torch.Generator().manual_seed(2)
+    acc = torch.randint(-5000, 5000, (4, 2 * f), generator=g, dtype=torch.int32)
+    xs = torch.rand(4, generator=g) * 1e-2
+    ws = torch.rand(2 * f, generator=g) * 1e-2
+    h = ol.swiglu_epilogue(acc[:, perm], xs, ws[perm]).float()
+    y = ol.dequant(acc, xs, ws).float()
+    ref = torch.nn.functional.silu(y[:, :f]) * y[:, f:]
+    assert torch.allclose(h, ref, rtol=2e-2, atol=1e-6)
+
+
+def test_fixed_order_sumsq_close_to_plain_sum():
+    g = torch.Generator().manual_seed(3)
+    for k in (256, 4096, 5376, 16384):
+        x = torch.randn(5, k, generator=g)
+        a = oq.fixed_order_sumsq(x)
+        b = (x.double() ** 2).sum(1)
+        assert torch.allclose(a.double(), b, rtol=1e-5)
+
+
+def test_norm_mod_matches_fp32_expression():
+    # the reference's fp32 expression for the fused prologue: bench/rot_test.py:42-51
+    g = torch.Generator().manual_seed(4)
+    m, k = 33, 512
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16)
+    shift = 0.1 * torch.randn(3, k, generator=g)
+    scale = 0.1 * torch.randn(3, k, generator=g)
+    idx = torch.randint(0, 3, (m,), generator=g, dtype=torch.int32)
+    y = oq.norm_mod(x, w, 1e-6, idx, shift, scale)
+    xf = x.float()
+    ref = xf * torch.rsqrt(xf.pow(2).mean(1, keepdim=True) + 1e-6) * w.float() * (1 + scale[idx.long()]) + shift[idx.long()]
+    assert torch.allclose(y, ref, rtol=1e-5, atol=1e-6)
+    q, s = oq.norm_mod_quant_rows_i8(x, w, 1e-6, idx, shift, scale)
+    assert q.abs().max() == 127 and s.shape == (m, 1)
