@@ -77,6 +77,42 @@ int rh3_gemm_w8a8_gated_residual(const void* xq, int64_t lda, const void* wq, co
 int rh3_gemm_w8a8_swiglu(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws, int64_t M,
                          int64_t N, int64_t K, int kind, void* out, int64_t ldo, cudaStream_t stream);
 
+/* ---- attention pre-pass (HBM-bound) and INT8 flash attention (tensor-core bound) ----------- */
+/* y = per-(token, head) RMSNorm over 128 channels (weight bf16[128]) followed, when rope_table is
+ * not NULL, by the split-half partial 3-D RoPE: rot_dim 96, pairs (i, i+48), table bf16 [S,48,2,2] =
+ * (cos, -sin, sin, cos); channels 96..127 are normalised only. x, y: [S, H, 128] views with element
+ * strides (token, head); y may alias x. Replaces comfy-kitchen's rms_rope_split_half_ as restated in
+ * custom_nodes/rapid_h3/csrc/attn_int8.cu:217-260 (rms_rope_row) / :382-399 (rms_rope_only), with IEEE
+ * division and square root instead of the .approx forms. */
+int rh3_rmsnorm_rope3d(const void* x, int64_t x_ss, int64_t x_sh, void* y, int64_t y_ss, int64_t y_sh, int64_t S,
+                       int64_t H, const void* weight, float eps, const void* rope_table, cudaStream_t stream);
+/* Bytes of scratch rh3_attn_kv_stats needs for L tokens and H heads (returns the size, not a status). */
+int64_t rh3_attn_kv_stats_scratch_bytes(int64_t L, int64_t H);
+/* kmean, vmean, vscale: fp32 [H,128]. Per-(head, channel) mean of K and V over the L tokens (sums in
+ * 256-token chunks, chunks in order) and vscale = max(max|v - vmean|, 1e-8) / 448.
+ * Replaces stats_partial + stats_final (attn_int8.cu:82-109). */
+int rh3_attn_kv_stats(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t L,
+                      int64_t H, void* scratch, int64_t scratch_bytes, float* kmean, float* vmean, float* vscale,
+                      cudaStream_t stream);
+/* codes int8 [H, Lpad, 128], scales fp32 [H, Lpad/64]: one abs-max scale per 64-token block per head,
+ * s = max(amax, 1e-8)/127, q = clamp(rint((x - mean)/s), +-127); mean (fp32 [H,128]) may be NULL (Q).
+ * Rows L..Lpad are written as zeros. Replaces quant_qk / quant_k_block (attn_int8.cu:130-170, :404-443)
+ * with the per-64-block scales of bench/attn_emulate.py:88 (`q8(k - km, 1, 64)`). */
+int rh3_attn_quant_qk(const void* x, int64_t x_ss, int64_t x_sh, int64_t L, int64_t Lpad, int64_t H,
+                      const float* mean, void* codes, float* scales, cudaStream_t stream);
+/* vt e4m3 [H, 128, Lpad] = e4m3((v - vmean) / vscale), transposed so keys are contiguous; columns
+ * L..Lpad are zeros. Replaces quant_v's e4m3 branch (attn_int8.cu:452-496) with the per-channel
+ * scale of bench/attn_emulate.py:16-18,101 (`f8(v - vm, 0)`). */
+int rh3_attn_quant_v(const void* v, int64_t v_ss, int64_t v_sh, int64_t L, int64_t Lpad, int64_t H,
+                     const float* vmean, const float* vscale, void* vt, cudaStream_t stream);
+/* out[Lq, H, 128] bf16 (element strides o_ss, o_sh) = softmax(Q.K^T * softmax_scale) . V from the
+ * pre-pass operands: int8 Q.K^T into int32, base-2 online softmax in fp32, P as e4m3 against the
+ * running maximum, e4m3 P.V into fp32, out = (O/l) * vscale + vmean. Lq may differ from Lk.
+ * Replaces attention_impl / the attn_fwd5 FP8-P.V kernel (attn_int8.cu:1538-1759, :2749-2849). */
+int rh3_attn_int8(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                  const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk, int64_t Lk_pad,
+                  int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

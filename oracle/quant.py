@@ -5,9 +5,15 @@ statistics), without the H256 rotation. The reference pins these only by a misma
 against an fp32 expression (bench/rot_test.py:42-51), so the summation order of the sum of squares
 is defined here and mirrored by the CUDA kernel: parity unpinned beyond that reference expression.
 """
+import numpy as np
 import torch
 
 from .linear import quantize_rows
+
+
+def ieee_sqrt(t):
+    """Correctly rounded fp32 square root (torch's vectorised CPU sqrt is not; numpy's is)."""
+    return torch.from_numpy(np.sqrt(t.contiguous().numpy()))
 
 
 def launch_shape(k):
@@ -49,7 +55,7 @@ def norm_mod(x, weight, eps, idx, shift, scale):
     xf = x.float()
     k = xf.shape[1]
     ss = fixed_order_sumsq(xf)
-    rstd = 1.0 / torch.sqrt(ss / k + torch.tensor(eps, dtype=torch.float32))
+    rstd = 1.0 / ieee_sqrt(ss / k + torch.tensor(eps, dtype=torch.float32))
     y = xf * rstd[:, None]
     if weight is not None:
         y = y * weight.float()[None, :]

@@ -28,7 +28,15 @@ SIGNATURES = {
     "rh3_gemm_w8a8": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I64, _P, _P],
     "rh3_gemm_w8a8_gated_residual": [_P, _I64, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _P],
     "rh3_gemm_w8a8_swiglu": [_P, _I64, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I64, _P],
+    "rh3_rmsnorm_rope3d": [_P, _I64, _I64, _P, _I64, _I64, _I64, _I64, _P, _F, _P, _P],
+    "rh3_attn_kv_stats_scratch_bytes": [_I64, _I64],
+    "rh3_attn_kv_stats": [_P, _I64, _I64, _P, _I64, _I64, _I64, _I64, _P, _I64, _P, _P, _P, _P],
+    "rh3_attn_quant_qk": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
+    "rh3_attn_quant_v": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
+    "rh3_attn_int8": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _I64, _I64, _P],
 }
+# entry points that return a value instead of a status
+RETURNS_I64 = ("rh3_attn_kv_stats_scratch_bytes",)
 
 KIND_I8, KIND_F8 = 0, 1
 
@@ -55,7 +63,7 @@ def lib():
         handle.rh3_last_error_string.argtypes = []
         for name, args in SIGNATURES.items():
             fn = getattr(handle, name)
-            fn.restype = ctypes.c_int
+            fn.restype = ctypes.c_int64 if name in RETURNS_I64 else ctypes.c_int
             fn.argtypes = args
         _lib = handle
     return _lib

@@ -1,0 +1,132 @@
+"""INT8 flash attention front end; same entry points as the reference's
+custom_nodes/rapid_h3/attn_int8.py (`attention`, `attention_bhsd`, `attention_rr`, `int8_prepass`).
+
+q, k, v are bf16 [S, H, 128] views (last dim contiguous, e.g. slices of the qkv GEMM output).
+The numerics are the block-64 / fp8-V variant: Q and K int8 with one scale per 64-token block per
+head (K mean-smoothed), V e4m3 per (head, channel), fp32 base-2 online softmax, e4m3 P.
+`config`, `rotate` and `smooth_v` of the reference are accepted for signature compatibility;
+K and V smoothing are always on and the Hadamard rotation is not part of this variant.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+
+D = 128
+
+
+def _pad128(n):
+    return (n + 127) // 128 * 128
+
+
+def _check_qkv(t, name):
+    _lib.require_cuda(t)
+    if t.dtype != torch.bfloat16 or t.ndim != 3 or t.shape[2] != D or t.stride(2) != 1:
+        raise RuntimeError(f"{name}: expected bf16 [S, H, 128] with a contiguous last dim, got {tuple(t.shape)} {t.dtype}")
+
+
+@dataclass
+class Prepass:
+    """Quantized operands of one attention call (the reference's int8_prepass list, as fields)."""
+    q8: torch.Tensor      # int8 [H, Lq_pad, 128]
+    qs: torch.Tensor      # fp32 [H, Lq_pad/64]
+    k8: torch.Tensor      # int8 [H, Lk_pad, 128]
+    ks: torch.Tensor      # fp32 [H, Lk_pad/64]
+    vt: torch.Tensor      # e4m3 [H, 128, Lk_pad]
+    vscale: torch.Tensor  # fp32 [H, 128]
+    vmean: torch.Tensor   # fp32 [H, 128]
+    kmean: torch.Tensor   # fp32 [H, 128]
+    lq: int
+    lk: int
+
+
+def rms_rope(x, weight, eps, tab=None, out=None):
+    """Per-head RMSNorm (+ split-half partial 3-D RoPE when `tab` [.., S, .., 48, 2, 2] bf16 is given) of
+    x [S, H, 128]; returns a new tensor unless `out` is given (`out=x` works in place)."""
+    _check_qkv(x, "x")
+    s, h, _ = x.shape
+    if out is None:
+        out = torch.empty((s, h, D), device=x.device, dtype=torch.bfloat16)
+    _check_qkv(out, "out")
+    if weight.dtype != torch.bfloat16 or weight.numel() != D:
+        raise RuntimeError("norm weight must be bf16 [128]")
+    weight = weight.contiguous()
+    if tab is not None:
+        if tab.dtype != torch.bfloat16 or tab.numel() != s * 48 * 4:
+            raise RuntimeError("rope table must be bf16 [S, 48, 2, 2]")
+        tab = tab.contiguous()
+    _lib.call("rh3_rmsnorm_rope3d", x.data_ptr(), x.stride(0), x.stride(1), out.data_ptr(), out.stride(0),
+              out.stride(1), s, h, weight.data_ptr(), float(eps), _lib.ptr(tab), _lib.stream())
+    return out
+
+
+def int8_prepass(q, k, v):
+    """Quantize the operands of one attention call: K/V statistics, block-64 int8 Q and K, e4m3 V^T."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_qkv(t, n)
+    lq, h, _ = q.shape
+    lk = k.shape[0]
+    if k.shape != v.shape or k.shape[1] != h:
+        raise RuntimeError("k and v must have the same shape and q's head count")
+    dev = q.device
+    lqp, lkp = _pad128(lq), _pad128(lk)
+    f32 = dict(device=dev, dtype=torch.float32)
+    kmean, vmean, vscale = (torch.empty((h, D), **f32) for _ in range(3))
+    nbytes = _lib.lib().rh3_attn_kv_stats_scratch_bytes(lk, h)
+    scratch = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+    st = _lib.stream()
+    _lib.call("rh3_attn_kv_stats", k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0), v.stride(1),
+              lk, h, scratch.data_ptr(), nbytes, kmean.data_ptr(), vmean.data_ptr(), vscale.data_ptr(), st)
+    q8 = torch.empty((h, lqp, D), device=dev, dtype=torch.int8)
+    k8 = torch.empty((h, lkp, D), device=dev, dtype=torch.int8)
+    qs = torch.empty((h, lqp // 64), **f32)
+    ks = torch.empty((h, lkp // 64), **f32)
+    vt = torch.empty((h, D, lkp), device=dev, dtype=torch.float8_e4m3fn)
+    _lib.call("rh3_attn_quant_qk", q.data_ptr(), q.stride(0), q.stride(1), lq, lqp, h, None, q8.data_ptr(),
+              qs.data_ptr(), st)
+    _lib.call("rh3_attn_quant_qk", k.data_ptr(), k.stride(0), k.stride(1), lk, lkp, h, kmean.data_ptr(),
+              k8.data_ptr(), ks.data_ptr(), st)
+    _lib.call("rh3_attn_quant_v", v.data_ptr(), v.stride(0), v.stride(1), lk, lkp, h, vmean.data_ptr(),
+              vscale.data_ptr(), vt.data_ptr(), st)
+    return Prepass(q8, qs, k8, ks, vt, vscale, vmean, kmean, lq, lk)
+
+
+def attention_pre(pre, scale=None, out=None):
+    """Main kernel on pre-quantized operands -> out [Lq, H, 128] bf16 (strided `out` allowed)."""
+    h = pre.q8.shape[0]
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty((pre.lq, h, D), device=pre.q8.device, dtype=torch.bfloat16)
+    _check_qkv(out, "out")
+    if out.shape[0] != pre.lq or out.shape[1] != h:
+        raise RuntimeError("out must be [Lq, H, 128]")
+    _lib.call("rh3_attn_int8", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
+              pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
+              pre.k8.shape[1], h, float(scale), out.data_ptr(), out.stride(0), out.stride(1), _lib.stream())
+    return out
+
+
+def attention(q, k, v, scale=None, config=0, smooth_k=True, smooth_v=True, rotate=False, out=None):
+    """q [Lq, H, 128], k, v [Lk, H, 128] bf16 (strided views allowed) -> [Lq, H, 128] bf16."""
+    if rotate:
+        raise NotImplementedError("the Hadamard-rotated per-token variant is not implemented")
+    return attention_pre(int8_prepass(q, k, v), scale, out)
+
+
+def attention_bhsd(q, k, v, scale=None, config=0, out=None):
+    """[1, H, S, 128] layout of the reference's override; returns [1, H, S, 128]."""
+    if q.ndim != 4 or q.shape[0] != 1:
+        raise RuntimeError("attention_bhsd: expected [1, H, S, 128]")
+    o = attention(q[0].transpose(0, 1), k[0].transpose(0, 1), v[0].transpose(0, 1), scale,
+                  out=None if out is None else out[0].transpose(0, 1))
+    return o.transpose(0, 1).unsqueeze(0) if out is None else out
+
+
+def attention_rr(q, k, v, tab, qw, kw, eps, scale=None, config=0, out=None):
+    """attention() on raw q/k with the per-head RMSNorm + 3-D RoPE applied first; q and k are left untouched."""
+    qn = rms_rope(q, qw, eps, tab)
+    kn = rms_rope(k, kw, eps, tab)
+    return attention(qn, kn, v, scale, out=out)
