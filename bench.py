@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized H3-shaped DiT step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload full|draft|block]
+
+One "step" = one evaluation of the 48-block transformer on the 768x1344x141-frame token grid
+(36x24x42 = 36,288 video tokens + 148 audio tokens, CFG batch 2, 512 text tokens), all Linear layers
+W8A8 row-wise int8, INT8-QK / FP8-PV attention. For N > 1 (launched by torch.distributed.run) the step is
+sequence-parallel: token shards + Ulysses all-to-all around self-attention (strong scaling).
+Rank 0 prints ONE JSON line. `--impl reference` times the reference's CPU path (its PyTorch emulation,
+restated in oracle/) on the host cores, on a bounded sample extrapolated to a full step.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (grid T,H,W, audio tokens, batch, text tokens, blocks)
+    "full": ((36, 24, 42), 148, 2, 512, 48),
+    "draft": ((36, 17, 29), 148, 2, 512, 48),
+    "block": ((36, 24, 42), 148, 1, 512, 1),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU port (the oracle) timed on a bounded sample and extrapolated to one full step
+# ---------------------------------------------------------------------------------------------------
+def cpu_port_step_seconds(workload, rows=1024, attn_rows=256):
+    """Seconds per step of the reference's CPU path, extrapolated: row-local work (quantizers, GEMMs,
+    epilogues) is timed on `rows` tokens and scaled linearly; attention is timed for one head on
+    `attn_rows` query rows against all keys and scaled to H heads x all rows."""
+    from oracle import attention as oa
+    from oracle import linear as ol
+    from oracle import quant as oq
+    from rapid_h3_b200.model import H3Config
+    cfg = H3Config()
+    grid, n_audio, batch, text_len, blocks = WORKLOADS[workload]
+    s = grid[0] * grid[1] * grid[2] + n_audio
+    d, f = cfg.d_model, cfg.mlp_hidden
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(rows, d, generator=g).to(torch.bfloat16)
+    idx = torch.zeros(rows, dtype=torch.int32)
+    tab = 0.1 * torch.randn(1, d, generator=g)
+    w_norm = torch.ones(d, dtype=torch.bfloat16)
+
+    def qw(n, k):
+        return (torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8), torch.rand(1, n, generator=g) * 1e-3)
+
+    t0 = time.perf_counter()
+    lin = 0.0
+    for n, k, kind in ((3 * d, d, "plain"), (d, d, "gated"), (d, d, "plain"), (d, d, "gated"), (2 * f, d, "swiglu"),
+                       (d, f, "gated")):
+        wq, ws = qw(n, k)
+        a = torch.randn(rows, k, generator=g).to(torch.bfloat16)
+        t1 = time.perf_counter()
+        if kind == "swiglu" or n == 3 * d:
+            xq, xs = oq.norm_mod_quant_rows_i8(a, w_norm[:k], 1e-6, idx, tab[:, :k], tab[:, :k])
+        else:
+            xq, xs = ol.quantize_rows(a, "int8_rowwise")
+        acc = ol.int_mm(xq, wq)
+        if kind == "plain":
+            ol.dequant(acc, xs, ws)
+        elif kind == "gated":
+            ol.gated_residual(acc, xs, ws, w_norm[:n], x[:, :n] if n <= d else a[:, :n])
+        else:
+            ol.swiglu_epilogue(acc, xs, ws)
+        lin += time.perf_counter() - t1
+    q, k, v = (torch.randn(s, 1, 128, generator=g).to(torch.bfloat16) for _ in range(3))
+    t1 = time.perf_counter()
+    pre = oa.prepass(q, k, v)
+    t_pre = time.perf_counter() - t1
+    t1 = time.perf_counter()
+    oa.attention_pre(pre, rows=torch.arange(attn_rows))
+    t_attn = time.perf_counter() - t1
+    per_block_sample = lin * (s / rows) + cfg.heads * (t_pre + t_attn * (s / attn_rows))
+    total = per_block_sample * blocks * batch
+    return total, {"rows": rows, "attn_rows": attn_rows, "sample_seconds": time.perf_counter() - t0,
+                   "linear_s_per_rows": lin, "attn_s_per_head_rows": t_attn, "prepass_s_per_head": t_pre}
+
+
+def cpu_baseline_record(workload):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cpu_port_step_seconds(workload, rows=128, attn_rows=32)  # warm-up
+    val, info = cpu_port_step_seconds(workload)
+    return {"value": val, "unit": "s/step", "cores": cores, "kind": "port",
+            "sample": (f"row-local ops of one block on {info['rows']} of the tokens, attention of 1 head on "
+                       f"{info['attn_rows']} query rows x all keys ({info['sample_seconds']:.1f} s of CPU work), "
+                       "scaled linearly to all rows, heads, blocks and the CFG batch")}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    grid, n_audio, batch, text_len, blocks = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    for _ in range(max(args.warmup, 1)):
+        cpu_port_step_seconds(args.workload, rows=128, attn_rows=32)
+    vals = []
+    for _ in range(args.steps):
+        v, info = cpu_port_step_seconds(args.workload, rows=512, attn_rows=128)
+        vals.append(v)
+    val = statistics.median(vals)
+    rec = {"impl": "reference", "metric": "H3 DiT step seconds @768x1344x141f", "value": val, "unit": "s/step",
+           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": val * 1e3,
+           "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
+           "data": "synthetic", "config": workload_config(args.workload, args.gpus),
+           "cpu_baseline": {"value": val, "unit": "s/step", "cores": cores, "kind": "port",
+                            "sample": "per step: row-local ops of one block on 512 tokens + attention of 1 head on "
+                                      "128 query rows x all keys, scaled linearly to the full step"},
+           "e2e": {"value": val, "unit": "s/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(rec), flush=True)
+
+
+def workload_config(name, n):
+    grid, n_audio, batch, text_len, blocks = WORKLOADS[name]
+    return {"workload": f"h3_dit_step_{name}", "token_grid": list(grid), "video_tokens": grid[0] * grid[1] * grid[2],
+            "audio_tokens": n_audio, "cfg_batch": batch, "text_tokens": text_len, "blocks": blocks, "d_model": 4096,
+            "heads": 32, "head_dim": 128, "mlp_hidden": 16384, "linear": "w8a8 int8 row-wise",
+            "attention": "int8 QK^T (block-64 scales, K smoothing) + fp8 e4m3 PV",
+            "parallelism": "single GPU" if n == 1 else f"sequence-parallel sp{n} (token shards + Ulysses all-to-all)",
+            "l2": "every step streams >16 GB of weights and activations, far larger than the 126 MB L2"}
+
+
+# ---------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="full", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    import rapid_h3_b200 as r
+    from rapid_h3_b200.model import H3Config
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    grid, n_audio, batch, text_len, blocks = WORKLOADS[args.workload]
+    cfg = H3Config(n_blocks=blocks)
+    rt = r.step.H3Runtime.random(cfg, seed=0, device=f"cuda:{local}")
+    s_total = grid[0] * grid[1] * grid[2] + n_audio
+    sp = r.sp.Ulysses(s_total) if world > 1 else None
+    host = [t.pin_memory() for t in r.step.make_inputs(cfg, grid, n_audio, batch, text_len, seed=0)]
+    dev = [t.cuda(non_blocking=True) for t in host]
+    rope_dev = dev[3]
+    out_host = [torch.empty((batch, cfg.latent_ch) + tuple(grid), dtype=torch.bfloat16).pin_memory(),
+                torch.empty((batch, n_audio, cfg.latent_ch), dtype=torch.bfloat16).pin_memory()]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        return rt.step(dev[0], dev[1], dev[2], rope_dev, dev[4], sp=sp)
+
+    def step_e2e():
+        lat, aud, temb, ctx = (host[i].cuda(non_blocking=True) for i in (0, 1, 2, 4))
+        v, a = rt.step(lat, aud, temb, rope_dev, ctx, sp=sp)
+        out_host[0].copy_(v, non_blocking=True)
+        out_host[1].copy_(a, non_blocking=True)
+
+    def timed(fn, k):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / k], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    r._lib.check_status()
+    sampler = ClockSampler(local)
+    sampler.start()
+    r._lib.launch_count = 0
+    r.attn_int8.TIMING = []
+    ms_step = timed(step_resident, args.steps)
+    launches = r._lib.launch_count
+    timing, r.attn_int8.TIMING = r.attn_int8.TIMING, None
+    clocks = sampler.stop()
+    r._lib.check_status()
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    r._lib.check_status()
+
+    # roofline of the dominant kernel (self-attention main kernel), from CUDA events around its launches
+    self_attn = [(a.elapsed_time(b), lq, lk, h) for a, b, lq, lk, h in timing if lk >= 1024]
+    pk = peaks()
+    roof = None
+    if self_attn:
+        ms_launch = statistics.mean(t for t, *_ in self_attn)
+        _, lq, lk, h = self_attn[0]
+        tflop = 4.0 * lq * lk * 128 * h / 1e12
+        achieved = tflop / (ms_launch / 1e3)
+        peak = 2.0 * pk["bf16_tflops_sustained"]
+        roof = {"bound": "tensor", "kernel": "attn_int8_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None, "ms_per_launch": ms_launch, "launches": len(self_attn),
+                "share_of_step": sum(t for t, *_ in self_attn) / (ms_step * args.steps),
+                "peak_note": f"2 x {pk['source']} sustained cuBLAS bf16 ({pk['bf16_tflops_sustained']} TF/s): "
+                             "8-bit operands run at twice the bf16 rate; nominal dense INT8/FP8 peak is 4500",
+                "frac_of_nominal_int8": achieved / 4500.0}
+    h2d = sum(host[i].numel() * host[i].element_size() for i in (0, 1, 2, 4))
+    d2h = sum(t.numel() * t.element_size() for t in out_host)
+    rec = {"metric": "H3 DiT step seconds @768x1344x141f", "value": ms_step / 1e3, "unit": "s/step", "n_gpus": world,
+           "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False,
+           "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+           "config": workload_config(args.workload, world), "clocks": clocks,
+           "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+           "gpu_launches": launches, "roofline": roof}
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            rec["cpu_baseline"] = cpu_baseline_record(args.workload)
+        print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -52,6 +52,11 @@ int rh3_swiglu_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t F, v
  * Replaces triton_fp8.rot_quant_heads_i8 without rotation (triton_fp8.py:429-434, gather :134-135). */
 int rh3_quant_heads_i8(const void* o, int64_t stride_h, int64_t H, int64_t M, void* q, int64_t ldq, float* s,
                        cudaStream_t stream);
+/* Generalisation of rh3_quant_heads_i8 to groups of gw columns: o[G, M, gw] -> q[M, G*gw]. Used on the
+ * output of the head-to-token exchange of sequence-parallel attention, which arrives grouped by source
+ * rank. Same reference as rh3_quant_heads_i8. */
+int rh3_quant_groups_i8(const void* o, int64_t stride_g, int64_t G, int64_t gw, int64_t M, void* q, int64_t ldq,
+                        float* s, cudaStream_t stream);
 /* y = rms_norm(x, eps) * w * (1 + scale[idx[m]]) + shift[idx[m]] -> int8 rows. w may be NULL.
  * shift/scale are fp32 tables with row stride ld_tab. Replaces triton_fp8.norm_mod_rot_quant_rows_i8
  * without rotation (triton_fp8.py:442-446, prologue :141-148, :165-172). */

@@ -1,0 +1,93 @@
+"""Oracle: one fused DiT block on CPU from the oracle primitives (TEST INFRASTRUCTURE ONLY).
+
+Restates the graph of the reference's `_fused_block` (custom_nodes/rapid_h3/__init__.py:253-320):
+norm+modulation quantizer -> qkv GEMM -> per-head RMSNorm + RoPE -> attention -> quantizer ->
+out_proj GEMM with gated residual per modality segment -> norm+modulation quantizer -> fc1 GEMM with
+SwiGLU epilogue -> quantizer -> fc2 GEMM with gated residual. The cross-attention to text tokens has no
+counterpart in the reference (parity unpinned); it is built from the same quantized primitives.
+`block` is a rapid_h3_b200.model.DiTBlock held on the CPU (only its parameters are read).
+"""
+import torch
+
+from . import attention as oa
+from . import linear as ol
+from . import quant as oq
+
+
+def _qlinear(x, weight):
+    wq, ws = ol.quantize_weight(weight, "int8_rowwise")
+    xq, xs = ol.quantize_rows(x, "int8_rowwise")
+    return ol.int_mm(xq, wq), xs, ws
+
+
+def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None):
+    s, d = x.shape
+    a = block.attn
+    hd = a.heads * a.head_dim
+    sh1, sc1, g1, sh2, sc2, g2 = block.adaln_proj(t_emb)
+    idx = torch.empty(s, dtype=torch.int32)
+    for lo, hi, row in mod_segments:
+        idx[lo:hi] = int(row)
+    tab = rope_freqs.reshape(s, 48, 2, 2)
+    x = x.clone()
+
+    def rec(name, value):
+        if trace is not None:
+            trace[name] = value.clone()
+
+    def gated(acc, xs, ws, gate_tab, x):
+        for lo, hi, row in mod_segments:
+            if hi > lo:
+                x[lo:hi] = ol.gated_residual(acc[lo:hi], xs[lo:hi], ws, gate_tab[int(row)].to(torch.bfloat16), x[lo:hi])
+        return x
+
+    def q_weight(lin):
+        return ol.quantize_weight(lin.weight.detach(), "int8_rowwise")
+
+    # self-attention
+    xq, xs = oq.norm_mod_quant_rows_i8(x, block.norm1.weight.detach(), block.norm1.eps, idx, sh1, sc1)
+    rec("attn_in_q", xq), rec("attn_in_s", xs)
+    wq, ws = q_weight(a.qkv_proj)
+    qkv = ol.dequant(ol.int_mm(xq, wq), xs, ws)
+    rec("qkv", qkv)
+    q, k, v = (t.reshape(s, a.heads, a.head_dim) for t in qkv.split(hd, dim=-1))
+    q = oa.rmsnorm_rope(q, a.q_norm.weight.detach(), a.q_norm.eps, tab)
+    k = oa.rmsnorm_rope(k, a.k_norm.weight.detach(), a.k_norm.eps, tab)
+    rec("qkv_rr", torch.cat([q.reshape(s, hd), k.reshape(s, hd), v.reshape(s, hd)], 1))
+    o = oa.attention(q, k, v)
+    rec("attn_out", o)
+    oq8, os_ = ol.quantize_rows(o.reshape(s, hd), "int8_rowwise")
+    wq, ws = q_weight(a.out_proj)
+    x = gated(ol.int_mm(oq8, wq), os_, ws, g1, x)
+    rec("x_attn", x)
+
+    if hasattr(block, "cross"):
+        c = block.cross
+        zeros = torch.zeros(1, d)
+        xq, xs = oq.norm_mod_quant_rows_i8(x, block.norm_c.weight.detach(), block.norm_c.eps,
+                                           torch.zeros(s, dtype=torch.int32), zeros, zeros)
+        wq, ws = q_weight(c.q_proj)
+        qc = ol.dequant(ol.int_mm(xq, wq), xs, ws).reshape(s, c.heads, c.head_dim)
+        cq8, cs = ol.quantize_rows(ctx, "int8_rowwise")
+        wq, ws = q_weight(c.kv_proj)
+        kv = ol.dequant(ol.int_mm(cq8, wq), cs, ws)
+        kc, vc = (t.reshape(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
+        qc = oa.rmsnorm_rope(qc, c.q_norm.weight.detach(), c.q_norm.eps, None)
+        kc = oa.rmsnorm_rope(kc, c.k_norm.weight.detach(), c.k_norm.eps, None)
+        oc = oa.attention(qc, kc, vc)
+        rec("cross_out", oc)
+        oq8, os_ = ol.quantize_rows(oc.reshape(s, hd), "int8_rowwise")
+        wq, ws = q_weight(c.out_proj)
+        x = ol.gated_residual(ol.int_mm(oq8, wq), os_, ws, torch.ones(d, dtype=torch.bfloat16), x)
+        rec("x_cross", x)
+
+    xq, xs = oq.norm_mod_quant_rows_i8(x, block.norm2.weight.detach(), block.norm2.eps, idx, sh2, sc2)
+    wq, ws = q_weight(block.mlp.fc1)
+    perm = ol.swiglu_perm(wq.shape[0])
+    h = ol.swiglu_epilogue(ol.int_mm(xq, wq[perm]), xs, ws[:, perm])
+    rec("mlp_h", h)
+    hq, hs = ol.quantize_rows(h, "int8_rowwise")
+    wq, ws = q_weight(block.mlp.fc2)
+    x = gated(ol.int_mm(hq, wq), hs, ws, g2, x)
+    rec("x_out", x)
+    return x

@@ -24,6 +24,7 @@ SIGNATURES = {
     "rh3_quant_rows_fp8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_swiglu_quant_rows_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_quant_heads_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
+    "rh3_quant_groups_i8": [_P, _I64, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_norm_mod_quant_rows_i8": [_P, _I64, _P, _F, _P, _P, _P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_gemm_w8a8": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I64, _P, _P],
     "rh3_gemm_w8a8_gated_residual": [_P, _I64, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _P],
@@ -41,6 +42,11 @@ RETURNS_I64 = ("rh3_attn_kv_stats_scratch_bytes",)
 KIND_I8, KIND_F8 = 0, 1
 
 _lib = None
+
+# kernels launched per entry point (for launch accounting in benchmarks)
+LAUNCHES = {"rh3_attn_kv_stats": 2, "rh3_version": 0, "rh3_sm_count": 0, "rh3_check_status": 0,
+            "rh3_attn_kv_stats_scratch_bytes": 0}
+launch_count = 0
 
 
 def declared_symbols():
@@ -84,7 +90,9 @@ def stream():
 
 def call(name, *args):
     """Invoke an entry point; a non-zero return raises RuntimeError with the library's message."""
+    global launch_count
     rc = getattr(lib(), name)(*args)
+    launch_count += LAUNCHES.get(name, 1)
     if rc != 0:
         raise RuntimeError(f"{name} failed ({rc}): {last_error()}")
 

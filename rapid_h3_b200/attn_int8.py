@@ -16,6 +16,10 @@ from . import _lib
 
 D = 128
 
+# When set to a list, attention_pre() appends (start_event, stop_event, Lq, Lk, H) around every launch of
+# the main kernel on the current stream (the reference's RAPIDH3_TIMING idea, __init__.py:258-264).
+TIMING = None
+
 
 def _pad128(n):
     return (n + 127) // 128 * 128
@@ -103,9 +107,15 @@ def attention_pre(pre, scale=None, out=None):
     _check_qkv(out, "out")
     if out.shape[0] != pre.lq or out.shape[1] != h:
         raise RuntimeError("out must be [Lq, H, 128]")
+    if TIMING is not None:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
     _lib.call("rh3_attn_int8", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
               pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
               pre.k8.shape[1], h, float(scale), out.data_ptr(), out.stride(0), out.stride(1), _lib.stream())
+    if TIMING is not None:
+        ev1.record()
+        TIMING.append((ev0, ev1, pre.lq, pre.lk, h))
     return out
 
 

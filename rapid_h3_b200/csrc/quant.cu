@@ -11,7 +11,8 @@
 //   KIND_PLAIN   x
 //   KIND_SWIGLU  silu(x[:, k]) * x[:, F + k]
 //   KIND_NORMMOD rms_norm(x) * w * (1 + scale[idx[row]]) + shift[idx[row]]
-//   KIND_HEADS   x given head-major [H, M, 128]; output column k = head k/128, channel k%128
+//   KIND_HEADS   x given group-major [G, M, gw] (gw = 128: head-major attention output);
+//                output column k = group k/gw, channel k%gw
 // The division x / s is done as x * (1/s) with an exact IEEE re-division only for the rare values
 // that land within 1e-3 of a rounding tie, which keeps the codes identical to a true division.
 #include "common.cuh"
@@ -37,6 +38,7 @@ struct QuantParams {
   const float* scale;
   int64_t ld_tab;
   // KIND_SWIGLU: F == K, the up half starts at column K
+  int gw;  // KIND_HEADS: columns per group (128 for one head); x is [K/gw, M, gw] with group stride ldx
 };
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* v) {
@@ -110,7 +112,8 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
       const __nv_bfloat16* src;
       if (KIND == KIND_HEADS) {
         const int col = c << 3;
-        src = p.x + static_cast<int64_t>(col >> 7) * p.ldx + row * 128 + (col & 127);
+        const int grp = col / p.gw;
+        src = p.x + static_cast<int64_t>(grp) * p.ldx + row * p.gw + (col - grp * p.gw);
       } else {
         src = p.x + row * p.ldx + (static_cast<int64_t>(c) << 3);
       }
@@ -271,14 +274,20 @@ extern "C" int rh3_swiglu_quant_rows_i8(const void* x, int64_t ldx, int64_t M, i
   return launch_quant<KIND_SWIGLU, 0>(p, stream);
 }
 
+extern "C" int rh3_quant_groups_i8(const void* o, int64_t stride_g, int64_t G, int64_t gw, int64_t M, void* q,
+                                   int64_t ldq, float* s, cudaStream_t stream) {
+  RH3_CHECK_ARG(G > 0 && gw > 0 && gw % 8 == 0 && gw < (1ll << 30), "quant_groups_i8: G must be positive, gw a multiple of 8");
+  if (int e = check_common(o, stride_g, M, G * gw, q, ldq, s)) return e;
+  RH3_CHECK_ARG(stride_g >= M * gw && ldq >= G * gw, "quant_groups_i8: strides too small");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(o); p.ldx = stride_g; p.M = M; p.K = G * gw; p.q = q; p.ldq = ldq; p.s = s;
+  p.gw = static_cast<int>(gw);
+  return launch_quant<KIND_HEADS, 0>(p, stream);
+}
+
 extern "C" int rh3_quant_heads_i8(const void* o, int64_t stride_h, int64_t H, int64_t M, void* q, int64_t ldq,
                                   float* s, cudaStream_t stream) {
-  RH3_CHECK_ARG(H > 0, "quant_heads_i8: H must be positive");
-  if (int e = check_common(o, stride_h, M, H * 128, q, ldq, s)) return e;
-  RH3_CHECK_ARG(stride_h >= M * 128 && ldq >= H * 128, "quant_heads_i8: strides too small");
-  QuantParams p{};
-  p.x = static_cast<const __nv_bfloat16*>(o); p.ldx = stride_h; p.M = M; p.K = H * 128; p.q = q; p.ldq = ldq; p.s = s;
-  return launch_quant<KIND_HEADS, 0>(p, stream);
+  return rh3_quant_groups_i8(o, stride_h, H, 128, M, q, ldq, s, stream);
 }
 
 extern "C" int rh3_norm_mod_quant_rows_i8(const void* x, int64_t ldx, const void* w, float eps, const int32_t* idx,

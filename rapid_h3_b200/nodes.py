@@ -1,0 +1,276 @@
+"""Operator surface of the Rapid-H3 node pack for the DiT block, over the CUDA kernels of this package.
+
+Mirrors custom_nodes/rapid_h3/__init__.py of the reference: `_QuantLinear` (:83-167), `_row_index`
+(:189-200), `_fused_block` (:207-321), `RapidH3LinearQuant.patch` (:369-417) and
+`RapidH3Int8Attention.patch` (:995-1047). ComfyUI is not required: `patch` takes any module tree whose
+blocks expose the attributes the reference reads (see rapid_h3_b200.model) and returns a handle whose
+`block_forward` list replaces the blocks' forwards. Calls the reference would silently route to the
+stock path (non-bf16, CPU tensors, missing rope table) raise NotImplementedError here instead: there is
+no fallback path.
+"""
+import re
+
+import torch
+
+from . import attn_int8, kernels
+from . import gemm as cf
+from . import quantizers as tq
+
+NAME_RE = re.compile(r"^blocks\.(\d+)\.(attn|mlp|cross)\.(qkv_proj|out_proj|fc1|fc2|q_proj|kv_proj)$")
+
+_IDX_CACHE = {}
+
+
+def _row_index(segments, s, device):
+    """Per-token modulation-row index (int32 [S]) from [(start, stop, row)], cached per segment list."""
+    key = (id(segments), s, str(device))
+    hit = _IDX_CACHE.get(key)
+    if hit is not None and hit[0] is segments:
+        return hit[1]
+    idx = torch.empty(s, dtype=torch.int32, device=device)
+    for a, b, row in segments:
+        idx[a:b] = int(row)
+    _IDX_CACHE.clear()
+    _IDX_CACHE[key] = (segments, idx)
+    return idx
+
+
+class _QuantLinear:
+    """Replacement forward bound to one Linear: row quantizer + W8A8 GEMM, bias added afterwards in bf16
+    (reference: __init__.py:132-167). The quantized weight is made once and cached."""
+
+    def __init__(self, module, name, mode):
+        self.module, self.name, self.mode = module, name, mode
+        self.qweight = None
+        self.calls = 0
+
+    def qweight_for(self, x=None):
+        if self.qweight is None:
+            self.qweight = kernels.quantize_weight(self.module.weight.detach(), self.mode)
+        return self.qweight
+
+    def __call__(self, x):
+        if x.device.type != "cuda" or x.dtype != torch.bfloat16:
+            raise NotImplementedError("_QuantLinear: only CUDA bf16 activations are supported (no fallback path)")
+        shape = x.shape
+        qw = self.qweight_for(x)
+        y = kernels.linear(x.reshape(-1, shape[-1]), qw, self.mode)
+        if getattr(qw, "swiglu_perm", False):  # fc1 weight held in SwiGLU-epilogue order
+            y = y[:, torch.argsort(cf.swiglu_perm(y.shape[-1], y.device))]
+        if self.module.bias is not None:
+            y = y + self.module.bias.to(y.dtype)
+        self.calls += 1
+        return y.reshape(*shape[:-1], y.shape[-1])
+
+
+class FusedBlock:
+    """DiTBlock.forward with norm + modulation fused into the int8 quantizers, W8A8 GEMMs with fused
+    epilogues, and the INT8 attention kernel (the graph of reference __init__.py:253-320, plus the
+    cross-attention of the benchmark configuration):
+
+        norm_mod_quant -> qkv GEMM -> q/k RMSNorm+RoPE -> [heads<->tokens exchange] -> attention
+        -> row quantizer -> out_proj GEMM with gated residual (per modality segment)
+        -> norm_quant -> q GEMM / kv GEMM on text -> q/k RMSNorm -> attention(Lq != Lk) -> quantizer
+        -> out GEMM + residual
+        -> norm_mod_quant -> fc1 GEMM with SwiGLU epilogue -> row quantizer -> fc2 GEMM with gated residual
+
+    `sp` (rapid_h3_b200.sp.Ulysses or None) re-shards q/k/v from tokens to heads around self-attention.
+    """
+
+    def __init__(self, block, qkv_q, out_q, fc1_q, fc2_q, cq_q=None, ckv_q=None, co_q=None):
+        self.block = block
+        self.qkv_q, self.out_q, self.fc1_q, self.fc2_q = qkv_q, out_q, fc1_q, fc2_q
+        self.cq_q, self.ckv_q, self.co_q = cq_q, ckv_q, co_q
+        self._const = {}
+
+    # -- helpers -----------------------------------------------------------------------------
+    @staticmethod
+    def _norm_w(norm):
+        w = getattr(norm, "weight", None)
+        return None if w is None else w.detach().to(torch.bfloat16).contiguous()
+
+    @staticmethod
+    def _eps(norm):
+        e = getattr(norm, "eps", None)
+        return torch.finfo(torch.bfloat16).eps if e is None else e
+
+    def _fc1_swiglu_weight(self):
+        """fc1's int8 weight with rows interleaved for the SwiGLU epilogue (cached in place of the plain copy)."""
+        qw = self.fc1_q.qweight_for()
+        if not getattr(qw, "swiglu_perm", False):
+            perm = cf.swiglu_perm(qw.q.shape[0], qw.q.device)
+            qw = kernels.QWeight(qw.q[perm].contiguous(), qw.scale[:, perm].contiguous())
+            qw.swiglu_perm = True
+            self.fc1_q.qweight = qw
+        return qw.q, qw.scale
+
+    def _zeros_tab(self, d, device):
+        key = ("zeros", d, str(device))
+        if key not in self._const:
+            self._const[key] = (torch.zeros(1, d, device=device), torch.ones(d, device=device, dtype=torch.bfloat16))
+        return self._const[key]
+
+    @staticmethod
+    def _gemm_gated(xq, xs, q, x, gate_tab, segments):
+        """x += gate * (xq @ W^T), one GEMM per modality segment, each with its own gate row."""
+        qw = q.qweight_for()
+        for a, b, row in segments:
+            if b > a:
+                g = gate_tab[int(row)].to(torch.bfloat16).contiguous()
+                cf.int8_gemm_gated_residual(xq[a:b], xs[a:b], qw.q, qw.scale, g, x[a:b])
+        return x
+
+    # -- forward -----------------------------------------------------------------------------
+    def forward(self, x, t_emb, mod_segments, rope_freqs, ctx=None, sp=None, trace=None):
+        blk = self.block
+        if rope_freqs is None or x.dtype != torch.bfloat16 or x.device.type != "cuda" or x.ndim != 2:
+            raise NotImplementedError("FusedBlock: needs a 2-D CUDA bf16 packed sequence and a rope table")
+        s, d = x.shape
+        a = blk.attn
+        hd = a.heads * a.head_dim
+        shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = blk.adaln_proj(t_emb)
+        idx = _row_index(mod_segments, s, x.device)
+        tab = rope_freqs.reshape(s, 48, 2, 2)
+
+        def rec(name, value):
+            if trace is not None:
+                trace[name] = value.clone() if torch.is_tensor(value) else value
+
+        # ---- self-attention ----
+        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm1), self._eps(blk.norm1), idx, shift_msa, scale_msa)
+        rec("attn_in_q", xq), rec("attn_in_s", xs)
+        qw = self.qkv_q.qweight_for()
+        qkv = cf.int8_gemm(xq, xs, qw.q, qw.scale)
+        rec("qkv", qkv)
+        q, k, v = (t.view(s, a.heads, a.head_dim) for t in qkv.split(hd, dim=-1))
+        attn_int8.rms_rope(q, self._norm_w(a.q_norm), a.q_norm.eps, tab, out=q)
+        attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
+        rec("qkv_rr", qkv)
+        if sp is None:
+            o = attn_int8.attention(q, k, v)                       # [S, H, 128] token-major
+            rec("attn_out", o)
+            oq, os_ = tq.quant_rows_i8(o.view(s, hd))
+        else:
+            qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
+            og = attn_int8.attention(qg, kg, vg)
+            o = sp.heads_to_tokens(og)                              # [P, S_local, (H/P)*128] group-major
+            oq, os_ = tq.quant_groups_i8(o)
+        del qkv, q, k, v
+        x = self._gemm_gated(oq, os_, self.out_q, x, gate_msa, mod_segments)
+        rec("x_attn", x)
+
+        # ---- cross-attention to text ----
+        if self.cq_q is not None:
+            c = blk.cross
+            zeros, ones = self._zeros_tab(d, x.device)
+            idx0 = self._const.setdefault(("idx0", s, str(x.device)), torch.zeros(s, dtype=torch.int32, device=x.device))
+            xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm_c), self._eps(blk.norm_c), idx0, zeros, zeros)
+            qw = self.cq_q.qweight_for()
+            qc = cf.int8_gemm(xq, xs, qw.q, qw.scale).view(s, c.heads, c.head_dim)
+            cq8, cs = tq.quant_rows_i8(ctx)
+            qw = self.ckv_q.qweight_for()
+            kv = cf.int8_gemm(cq8, cs, qw.q, qw.scale)
+            kc, vc = (t.view(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
+            attn_int8.rms_rope(qc, self._norm_w(c.q_norm), c.q_norm.eps, None, out=qc)
+            attn_int8.rms_rope(kc, self._norm_w(c.k_norm), c.k_norm.eps, None, out=kc)
+            oc = attn_int8.attention(qc, kc, vc)
+            rec("cross_out", oc)
+            oq, os_ = tq.quant_rows_i8(oc.view(s, hd))
+            qw = self.co_q.qweight_for()
+            cf.int8_gemm_gated_residual(oq, os_, qw.q, qw.scale, ones, x)
+            rec("x_cross", x)
+
+        # ---- MLP ----
+        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm2), self._eps(blk.norm2), idx, shift_mlp, scale_mlp)
+        h = cf.int8_gemm_swiglu(xq, xs, *self._fc1_swiglu_weight())
+        rec("mlp_h", h)
+        hq, hs = tq.rot_quant_rows_i8(h)
+        del h
+        out = self._gemm_gated(hq, hs, self.fc2_q, x, gate_mlp, mod_segments)
+        rec("x_out", out)
+        return out
+
+    __call__ = forward
+
+
+def _fused_block(block, qkv_q, out_q, fc1_q, fc2_q, cq_q=None, ckv_q=None, co_q=None):
+    """The reference's factory name: returns the fused forward bound to `block`."""
+    return FusedBlock(block, qkv_q, out_q, fc1_q, fc2_q, cq_q, ckv_q, co_q)
+
+
+class PatchedModel:
+    """What `RapidH3LinearQuant.patch` returns in place of ComfyUI's patched MODEL clone."""
+
+    def __init__(self, model, linears, block_forward):
+        self.model, self.linears, self.block_forward = model, linears, block_forward
+
+    def __call__(self, latent, audio, t_emb, rope_freqs, ctx):
+        return self.model(latent, audio, t_emb, rope_freqs, ctx, block_forward=self.block_forward)
+
+
+def _parse_blocks(spec):
+    out = set()
+    for part in filter(None, (p.strip() for p in spec.split(","))):
+        if "-" in part:
+            a, b = part.split("-")
+            out.update(range(int(a), int(b) + 1))
+        else:
+            out.add(int(part))
+    return out
+
+
+class RapidH3LinearQuant:
+    """Node adapter: quantize the DiT's linears and fuse the blocks (reference __init__.py:352-417)."""
+
+    MODES = ["bf16", "fp8_rowwise", "int8_rowwise", "int8_fast"]
+
+    def patch(self, model, mode="int8_rowwise", targets="qkv_proj,out_proj,fc1,fc2,q_proj,kv_proj",
+              keep_bf16_blocks="", measure_every=0, fuse_block=True):
+        if mode == "bf16":
+            return (PatchedModel(model, {}, None),)
+        if mode not in self.MODES:
+            kernels.quantize_weight(torch.zeros(1, 8), mode)  # raises ValueError / NotImplementedError by name
+        want = {t.strip() for t in targets.split(",") if t.strip()}
+        keep = _parse_blocks(keep_bf16_blocks)
+        by_name = {}
+        for name, mod in model.named_modules():
+            hit = NAME_RE.match(name)
+            if not hit or hit.group(3) not in want or int(hit.group(1)) in keep:
+                continue
+            by_name[name] = _QuantLinear(mod, name, mode)
+        forwards = []
+        for i, blk in enumerate(model.blocks):
+            n = f"blocks.{i}"
+            parts = [by_name.get(f"{n}.{m}") for m in ("attn.qkv_proj", "attn.out_proj", "mlp.fc1", "mlp.fc2")]
+            cross = [by_name.get(f"{n}.{m}") for m in ("cross.q_proj", "cross.kv_proj", "cross.out_proj")]
+            if all(parts) and fuse_block and mode in ("int8_rowwise", "int8_fast"):
+                if hasattr(blk, "cross") and not all(cross):
+                    raise NotImplementedError("fused block needs the cross-attention linears quantized as well")
+                forwards.append(_fused_block(blk, *parts, *(cross if hasattr(blk, "cross") else ())))
+            else:
+                forwards.append(blk)  # stock forward (bf16 blocks kept on request)
+        return (PatchedModel(model, by_name, forwards),)
+
+
+class RapidH3Int8Attention:
+    """Node adapter: returns the attention override the reference installs in transformer_options
+    (reference __init__.py:995-1047). Accepts only what the reference accepts for its INT8 path (no mask,
+    [1, H, S, 128] bf16, skip_reshape); anything else raises instead of falling back."""
+
+    def patch(self, model, config=80, exact_rows=""):
+        if exact_rows:
+            raise NotImplementedError("exact_rows (bf16 SDPA patch-up) is not implemented")
+
+        def override(func, q, k, v, heads=None, mask=None, skip_reshape=False, skip_output_reshape=False, scale=None,
+                     **kwargs):
+            if not (mask is None and skip_reshape and q.dim() == 4 and q.shape[0] == 1 and q.shape[-1] == 128
+                    and q.dtype == torch.bfloat16):
+                raise NotImplementedError("RapidH3Int8Attention: unsupported attention call (no fallback path)")
+            out = attn_int8.attention_bhsd(q, k, v, scale)
+            return out if skip_output_reshape else out.transpose(1, 2).reshape(1, q.shape[2], -1)
+
+        override.rapidh3_rmsrope = config % 100 if config >= 100 else None
+        return (model, override)
+
+
+NODE_CLASS_MAPPINGS = {"RapidH3LinearQuant": RapidH3LinearQuant, "RapidH3Int8Attention": RapidH3Int8Attention}

@@ -70,6 +70,18 @@ def rot_quant_heads_i8(o, rotate=False):
     return q, s
 
 
+def quant_groups_i8(o):
+    """o [G, M, gw] bf16 group-major -> (q int8 [M, G*gw], s [M,1]); the general form of rot_quant_heads_i8."""
+    _lib.require_cuda(o)
+    assert o.ndim == 3 and o.stride(2) == 1 and o.stride(1) == o.shape[2] and o.dtype == torch.bfloat16
+    g, m, gw = o.shape
+    q = torch.empty((m, g * gw), device=o.device, dtype=torch.int8)
+    s = torch.empty((m, 1), device=o.device, dtype=torch.float32)
+    _lib.call("rh3_quant_groups_i8", o.data_ptr(), o.stride(0), g, gw, m, q.data_ptr(), q.stride(0), s.data_ptr(),
+              _lib.stream())
+    return q, s
+
+
 def swiglu_rot_quant_rows_i8(x, rotate=False):
     """x [M, 2F] = [gate | up] -> int8 of silu(gate) * up, [M, F]."""
     _no_rotation(rotate)
