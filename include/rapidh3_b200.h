@@ -99,6 +99,17 @@ int64_t rh3_attn_kv_stats_scratch_bytes(int64_t L, int64_t H);
 int rh3_attn_kv_stats(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t L,
                       int64_t H, void* scratch, int64_t scratch_bytes, float* kmean, float* vmean, float* vscale,
                       cudaStream_t stream);
+/* Same result as rh3_attn_kv_stats, for callers that are not able to allocate device memory (a host
+ * framework that owns all VRAM, a serving loop where cudaMalloc is forbidden, a plugin that only receives its
+ * input and output buffers). The chunk partials go to a 16 MiB array built into the library image (held on
+ * every GPU that loads the library until the process exits), so no scratch is passed and nothing is
+ * allocated or freed. Limit: H * ceil(L/256) <= 8192; larger problems are rejected with an error.
+ * The first call on a device looks up the array's device address; make that first call outside any stream
+ * capture. All calls share the one array: two calls whose kernels overlap on the GPU (different streams)
+ * race on it; calls on one stream are safe, and nothing needs to be cleared between calls.
+ * This entry point has no counterpart in the reference. */
+int rh3_attn_kv_stats_noalloc(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh,
+                              int64_t L, int64_t H, float* kmean, float* vmean, float* vscale, cudaStream_t stream);
 /* codes int8 [H, Lpad, 128], scales fp32 [H, Lpad/64]: one abs-max scale per 64-token block per head,
  * s = max(amax, 1e-8)/127, q = clamp(rint((x - mean)/s), +-127); mean (fp32 [H,128]) may be NULL (Q).
  * Rows L..Lpad are written as zeros. Replaces quant_qk / quant_k_block (attn_int8.cu:130-170, :404-443)

@@ -294,6 +294,65 @@ extern "C" int rh3_attn_kv_stats(const void* k, int64_t k_ss, int64_t k_sh, cons
   return check_cuda(cudaGetLastError(), "attn_kv_stats final launch");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free K/V statistics.
+//
+// Some hosts of this library may not create device memory at the moment they need the statistics:
+// a sampler loop running under a framework that has already handed every byte of VRAM to its own
+// pool, a latency-critical serving thread where cudaMalloc (which synchronises the device) is
+// banned, or a plugin that is only ever given input and output buffers. For them the chunk
+// partials live in a fixed array inside the library's device image instead of caller scratch.
+// The array costs 16 MiB on every GPU that loads the library, for the life of the process.
+//
+// Host code cannot use `g_kv_stats_scratch` as a pointer: on the host that name is only a handle
+// for the symbol. The real device address is looked up once per device, with that device current,
+// through cudaGetSymbolAddress, and that address is what the kernels receive.
+// ---------------------------------------------------------------------------------------------
+constexpr int64_t KV_STATS_NOALLOC_MAX_UNITS = 8192;  // limit on H * ceil(L / 256)
+static __device__ __align__(256) float g_kv_stats_scratch[KV_STATS_NOALLOC_MAX_UNITS * 4 * 128];
+
+static int kv_stats_scratch_address(float** out) {
+  static float* per_device[64] = {};
+  int dev = -1;
+  if (int e = rh3::check_cuda(cudaGetDevice(&dev), "attn_kv_stats_noalloc: cudaGetDevice")) return e;
+  if (dev < 0 || dev >= 64) return rh3::set_error(RH3_ARG_ERROR, "attn_kv_stats_noalloc: device index %d out of range", dev);
+  if (per_device[dev] == nullptr) {
+    void* p = nullptr;
+    if (int e = rh3::check_cuda(cudaGetSymbolAddress(&p, g_kv_stats_scratch),
+                                "attn_kv_stats_noalloc: cudaGetSymbolAddress"))
+      return e;
+    per_device[dev] = static_cast<float*>(p);
+  }
+  *out = per_device[dev];
+  return 0;
+}
+
+extern "C" int rh3_attn_kv_stats_noalloc(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss,
+                                         int64_t v_sh, int64_t L, int64_t H, float* kmean, float* vmean,
+                                         float* vscale, cudaStream_t stream) {
+  RH3_CHECK_ARG(L > 0 && H > 0 && H < 65536, "attn_kv_stats_noalloc: bad shape L=%lld H=%lld", (long long)L,
+                (long long)H);
+  const int64_t nchunk64 = (L + STAT_CHUNK - 1) / STAT_CHUNK;
+  RH3_CHECK_ARG(H * nchunk64 <= KV_STATS_NOALLOC_MAX_UNITS,
+                "attn_kv_stats_noalloc: H * ceil(L/256) = %lld exceeds the built-in scratch limit of %lld; "
+                "use rh3_attn_kv_stats with caller-provided scratch",
+                (long long)(H * nchunk64), (long long)KV_STATS_NOALLOC_MAX_UNITS);
+  RH3_CHECK_ARG(k && v && kmean && vmean && vscale, "attn_kv_stats_noalloc: null pointer");
+  RH3_CHECK_ARG(aligned(k, 8) && aligned(v, 8) && k_ss % 4 == 0 && k_sh % 4 == 0 && v_ss % 4 == 0 && v_sh % 4 == 0,
+                "attn_kv_stats_noalloc: misaligned input");
+  float* scratch = nullptr;
+  if (int e = kv_stats_scratch_address(&scratch)) return e;
+  const int nchunk = static_cast<int>(nchunk64);
+  // every partial that the second kernel reads is written by the first one in this call, so nothing
+  // left over from an earlier call needs clearing
+  kv_stats_partial_kernel<<<dim3(static_cast<unsigned>((H + 7) / 8), nchunk), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(k), k_ss, k_sh, static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, L, (int)H,
+      nchunk, scratch);
+  if (int e = check_cuda(cudaGetLastError(), "attn_kv_stats_noalloc partial launch")) return e;
+  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(scratch, nchunk, L, kmean, vmean, vscale);
+  return check_cuda(cudaGetLastError(), "attn_kv_stats_noalloc final launch");
+}
+
 extern "C" int rh3_attn_quant_qk(const void* x, int64_t x_ss, int64_t x_sh, int64_t L, int64_t Lpad, int64_t H,
                                  const float* mean, void* codes, float* scales, cudaStream_t stream) {
   RH3_CHECK_ARG(L > 0 && H > 0 && H < 65536 && Lpad >= L && Lpad % 128 == 0,
