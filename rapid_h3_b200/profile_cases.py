@@ -1,0 +1,93 @@
+"""Small single-kernel cases for profiling one kernel of the library in isolation.
+
+    python -m rapid_h3_b200.profile_cases attn  --L 16384 --H 8  [--iters 3]
+    python -m rapid_h3_b200.profile_cases gemm  --M 8192 --N 12288 --K 4096 [--epi plain|gated|swiglu]
+    python -m rapid_h3_b200.profile_cases quant --M 36436 --K 4096 [--kind plain|fp8|normmod]
+    python -m rapid_h3_b200.profile_cases prepass --L 16384 --H 8
+
+Each case builds seeded random inputs on the device, runs the kernel `--iters` times and prints the mean time
+from CUDA events, so the same command line serves a plain timing run and a profiler capture.
+"""
+import argparse
+
+import torch
+
+from . import _lib, attn_int8, gemm, quantizers
+
+
+def _time(fn, iters):
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["attn", "gemm", "quant", "prepass"])
+    ap.add_argument("--L", type=int, default=16384)
+    ap.add_argument("--H", type=int, default=8)
+    ap.add_argument("--M", type=int, default=8192)
+    ap.add_argument("--N", type=int, default=12288)
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--epi", default="plain")
+    ap.add_argument("--kind", default="plain")
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def randn(*shape):
+        return torch.randn(*shape, device="cuda", generator=g)
+
+    if a.case in ("attn", "prepass"):
+        q = randn(a.L, a.H, 128).to(torch.bfloat16)
+        k = (randn(a.L, a.H, 128) + 2 * randn(1, a.H, 128)).to(torch.bfloat16)
+        v = randn(a.L, a.H, 128).to(torch.bfloat16)
+        if a.case == "prepass":
+            ms = _time(lambda: attn_int8.int8_prepass(q, k, v), a.iters)
+            print(f"prepass L={a.L} H={a.H}: {ms:.3f} ms")
+            return
+        pre = attn_int8.int8_prepass(q, k, v)
+        out = torch.empty(a.L, a.H, 128, device="cuda", dtype=torch.bfloat16)
+        ms = _time(lambda: attn_int8.attention_pre(pre, out=out), a.iters)
+        print(f"attn L={a.L} H={a.H}: {ms:.3f} ms, {4 * a.L * a.L * 128 * a.H / ms / 1e9:.1f} TFLOP/s")
+    elif a.case == "gemm":
+        xq = torch.randint(-127, 128, (a.M, a.K), device="cuda", dtype=torch.int8, generator=g)
+        wq = torch.randint(-127, 128, (a.N, a.K), device="cuda", dtype=torch.int8, generator=g)
+        xs = torch.rand(a.M, device="cuda", generator=g) * 1e-3
+        ws = torch.rand(a.N, device="cuda", generator=g) * 1e-3
+        if a.epi == "swiglu":
+            out = torch.empty(a.M, a.N // 2, device="cuda", dtype=torch.bfloat16)
+            fn = lambda: gemm.int8_gemm_swiglu(xq, xs, wq, ws, out=out)  # noqa: E731
+        elif a.epi == "gated":
+            resid = randn(a.M, a.N).to(torch.bfloat16)
+            gate = randn(a.N).to(torch.bfloat16)
+            fn = lambda: gemm.int8_gemm_gated_residual(xq, xs, wq, ws, gate, resid)  # noqa: E731
+        else:
+            out = torch.empty(a.M, a.N, device="cuda", dtype=torch.bfloat16)
+            fn = lambda: gemm.int8_gemm(xq, xs, wq, ws, out=out)  # noqa: E731
+        ms = _time(fn, a.iters)
+        print(f"gemm {a.epi} M={a.M} N={a.N} K={a.K}: {ms:.3f} ms, {2 * a.M * a.N * a.K / ms / 1e9:.1f} TOP/s")
+    else:
+        x = randn(a.M, a.K).to(torch.bfloat16)
+        if a.kind == "fp8":
+            fn = lambda: quantizers.quant_rows(x)  # noqa: E731
+        elif a.kind == "normmod":
+            tab = randn(2, 6 * a.K) * 0.1
+            idx = torch.zeros(a.M, dtype=torch.int32, device="cuda")
+            w = torch.ones(a.K, device="cuda", dtype=torch.bfloat16)
+            fn = lambda: quantizers.norm_mod_rot_quant_rows_i8(x, w, 1e-6, idx, tab[:, :a.K], tab[:, a.K:2 * a.K])  # noqa: E731
+        else:
+            fn = lambda: quantizers.quant_rows_i8(x)  # noqa: E731
+        ms = _time(fn, a.iters)
+        print(f"quant {a.kind} M={a.M} K={a.K}: {ms:.3f} ms, {a.M * a.K * 3 / ms / 1e6:.0f} GB/s (3 B/element)")
+
+
+if __name__ == "__main__":
+    main()
