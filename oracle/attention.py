@@ -9,8 +9,10 @@ What it follows in the reference:
     epilogue O/l*vscale+vmean) and bench/attn_emulate.py:33-65 (`run_fp8`).
 Parity unpinned: the reference holds no vectors for this block-64 / e4m3-V variant (its production
 kernel is per-token int8 with u8 P), and its rms/rope uses hardware .approx operations. This oracle
-defines IEEE arithmetic with a fixed summation order, and P = e4m3(2^(t - M + 8)) with M the row
-maximum rounded up to an integer (so the result does not depend on the key-tile order).
+defines IEEE arithmetic with a fixed summation order, the exponent as the reference's magic-number
+dequantisation t = fma(1.5*2^23 + s, c, (8 - M) - 1.5*2^23*c) (attn_int8.cu:22-27, :2365-2370), and
+P = e4m3(2^t) with M the row maximum rounded up to an integer (so the result does not depend on the
+key-tile order).
 """
 import math
 
@@ -20,6 +22,7 @@ from .quant import ieee_sqrt
 
 D = 128
 FP8 = torch.float8_e4m3fn
+MAGIC = 12582912.0  # 1.5 * 2^23: the bias that turns int32 accumulator bits into floats
 
 
 def _bf(x):
@@ -121,17 +124,21 @@ def attention_pre(pre, scale=None, heads=None, rows=None):
         kf = pre["k8"][h, :lk].float()
         vf = pre["vt"][h, :, :lk].view(FP8).float().t().contiguous()  # [Lk, 128]
         kc = pre["ks"][h][torch.arange(lk) // 64]                      # per-key scale
-        for r0 in range(0, len(rows), 1024):
-            rr = rows[r0:r0 + 1024]
+        for r0 in range(0, len(rows), 512):
+            rr = rows[r0:r0 + 512]
             s = pre["q8"][h, rr].float() @ kf.t()                      # exact: |s| < 2^24
-            c = (pre["qs"][h][rr // 64] * sl2)[:, None] * kc[None, :]
-            t = s * c
-            m = torch.ceil(t.amax(1, keepdim=True))
-            p = torch.exp2(t - m + 8.0)
+            c = (pre["qs"][h][rr // 64] * sl2)[:, None] * kc[None, :]  # fp32: (qs * sl2) * ks
+            b = MAGIC * c                                              # fp32, one rounding
+            sf = (s + MAGIC).double()                                  # exact float 1.5*2^23 + s
+            # t = fma(sf, c, off): the product is exact in float64 and so is the sum (48 + 24 bits)
+            m = torch.ceil((sf * c.double() - b.double()).float().amax(1, keepdim=True))
+            off = (8.0 - m) - b
+            t = (sf * c.double() + off.double()).float()
+            p = torch.exp2(t)
             l = p.sum(1, keepdim=True)
             o = p.to(FP8).float() @ vf
             y = (o / l) * pre["vscale"][h][None] + pre["vmean"][h][None]
-            out[r0:r0 + 1024, hi] = y.to(torch.bfloat16)
+            out[r0:r0 + 512, hi] = y.to(torch.bfloat16)
     return out
 
 

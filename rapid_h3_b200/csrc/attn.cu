@@ -1,7 +1,9 @@
 // INT8 flash attention for head_dim 128, non-causal, on the Blackwell tensor cores.
 //
 //   S = Q8 . K8^T            int8 x int8 -> int32 in TMEM (tcgen05 kind::i8), one 128x128 tile at a time
-//   t = S * (qs[q block] * ks[k block] * softmax_scale * log2 e)      one scale per 64-token block
+//   t = fma(1.5*2^23 + S, c, off),  c = (qs[q block] * sl2) * ks[k block],  off = (8 - M) - 1.5*2^23 * c
+//       (sl2 = softmax_scale * log2 e; one scale per 64-token block; the reference's magic-number
+//       dequantisation, attn_int8.cu:22-27,2365-2370)
 //   online softmax in base 2; the running maximum is kept rounded UP to an integer M, so every
 //   rescale of O and l is an exact power of two and P's fp8 rounding does not depend on the order
 //   in which key tiles arrive
@@ -18,8 +20,11 @@
 // overlaps the other's MMAs):
 //   warp 0      TMA producer: Q once, then K tile (128 keys x 128 B) + V^T tile (128 ch x 128 keys)
 //   warp 1      MMA issuer: QK^T of tile j+1 is issued before P.V of tile j
-//   warps 2..5  one query row per thread: two passes over S in TMEM (max, then exp2 + fp8 pack),
-//               P written to shared memory in the 128-byte-swizzled K-major layout the MMA reads
+//   warps 2..5  one query row per thread: the accumulator is pre-biased with 1.5*2^23 so its int32 bits
+//               are a float (no conversion); pass 1 = 3-input max over the raw values, pass 2 =
+//               t = fma(bits, c, off) in packed f32x2, exp2, e4m3 pack; P goes to shared memory in the
+//               128-byte-swizzled K-major layout the MMA reads; O and l are rescaled by an exact power
+//               of two when the integer maximum grows
 // Tensor-core bound: 4 * Lq * Lk * 128 operations per head.
 #include <limits.h>
 
@@ -71,6 +76,95 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
       : "=r"(r)
       : "f"(a), "f"(b), "f"(c), "f"(d));
   return r;
+}
+
+constexpr float kMagic = 12582912.f;            // 1.5 * 2^23: float(kMagic + s) has s in its low mantissa bits
+constexpr uint32_t kMagicBits = 0x4B400000u;    // the same value as int32 bits, used to pre-bias S in TMEM
+
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {  // two fp32 FMAs in one instruction
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Largest raw value (a float 1.5*2^23 + s, or 0 if every column is masked) of one 32-column chunk.
+template <bool FULL>
+__device__ __forceinline__ float chunk_max(const uint32_t* r, int col0, int valid) {
+  float m = 0.f;
+  if (FULL) {
+    m = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+#pragma unroll
+    for (int i = 3; i < 31; i += 2) m = max3(m, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+    m = fmaxf(m, __uint_as_float(r[31]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < valid) m = fmaxf(m, __uint_as_float(r[i]));
+  }
+  return m;
+}
+
+// Pass 1: largest raw value of each 64-key half of one row of S (TMEM loads double-buffered).
+template <bool FULL>
+__device__ __forceinline__ void row_max_pass(uint32_t t_row, int valid, float& mx0, float& mx1) {
+  uint32_t ra[32], rb[32];
+  tmem_ld32(t_row, ra);
+  tmem_ld32(t_row + 32, rb);
+  tmem_ld_wait_regs(ra);
+  tmem_ld_wait_regs(rb);
+  const float m0 = chunk_max<FULL>(ra, 0, valid), m1 = chunk_max<FULL>(rb, 32, valid);
+  tmem_ld32(t_row + 64, ra);
+  tmem_ld32(t_row + 96, rb);
+  tmem_ld_wait_regs(ra);
+  tmem_ld_wait_regs(rb);
+  const float m2 = chunk_max<FULL>(ra, 64, valid), m3 = chunk_max<FULL>(rb, 96, valid);
+  mx0 = fmaxf(m0, m1);
+  mx1 = fmaxf(m2, m3);
+}
+
+// Pass 2, one 32-column chunk: p = 2^(bits * cc + off) in packed f32x2, e4m3 codes written to the row of P
+// in shared memory (16-byte chunks 2k and 2k+1 of the row, XOR-swizzled), unrounded p added to the sum.
+template <bool FULL>
+__device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, int valid, float cc, float off, uint8_t* p_row,
+                                          int sw, uint64_t& lsum2) {
+  const uint64_t cc2 = pack2(cc, cc), off2 = pack2(off, off);
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float pa, pb, pc, pd;
+    unpack2(fma2(pack2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), cc2, off2), pa, pb);
+    unpack2(fma2(pack2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), cc2, off2), pc, pd);
+    pa = ex2_approx(pa); pb = ex2_approx(pb); pc = ex2_approx(pc); pd = ex2_approx(pd);
+    if (!FULL) {
+      const int col = k * 32 + 4 * i;
+      if (col >= valid) pa = 0.f;
+      if (col + 1 >= valid) pb = 0.f;
+      if (col + 2 >= valid) pc = 0.f;
+      if (col + 3 >= valid) pd = 0.f;
+    }
+    lsum2 = add2(lsum2, add2(pack2(pa, pb), pack2(pc, pd)));
+    w[i] = pack_e4m3x4(pa, pb, pc, pd);
+  }
+  *reinterpret_cast<uint4*>(p_row + (((2 * k) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(p_row + (((2 * k + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
 __global__ void __launch_bounds__(ATTN_THREADS, 2)
@@ -139,11 +233,13 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         const uint32_t k_addr = smem_u32(sKV + (j % KV_STAGES) * 2 * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          mma_i8_ss(tmem_S, make_desc_k128(q_addr + k * 32), make_desc_k128(k_addr + k * 32), idesc_qk, k != 0);
+          mma_i8_ss(tmem_S, make_desc_k128(q_addr + k * 32), make_desc_k128(k_addr + k * 32), idesc_qk, 1);
         mma_commit(&tail->s_full);
       };
+      // S is pre-biased by the softmax warps (completion k of s_empty precedes Q.K^T of tile k)
       bool ok = mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
-                mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
+                mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
+                mbar_wait(&tail->s_empty, 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
       if (ok) {
         tc_fence_after();
         issue_qk(0);
@@ -152,7 +248,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         if (j + 1 < n_kv) {
           const int ns = (j + 1) % KV_STAGES;
           if (!mbar_wait(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) ||
-              !mbar_wait(&tail->s_empty, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY)) {
+              !mbar_wait(&tail->s_empty, (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY)) {
             ok = false;
             break;
           }
@@ -176,6 +272,10 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     }
   } else {
     // ------------------------------ softmax / correction / epilogue ------------------------------
+    // S arrives as raw bits of the float 1.5*2^23 + s (the accumulator is pre-biased, see below), so
+    // t = fma(bits, c, off) needs no int->float conversion and the row maximum is a 3-input float max
+    // on the raw values. Pass 1 finds the maximum, pass 2 computes P; S is handed back to the MMA warp
+    // as soon as pass 2 has it in registers, so the next Q.K^T overlaps the last quarter of the tile.
     const int quad = warp & 3;
     const int row = quad * 32 + lane;  // row of the tile = TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
@@ -184,44 +284,47 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     const float* ks_h = p.ks + static_cast<int64_t>(h) * (p.Lk_pad / 64);
     uint8_t* p_row = sP + row * 128;
     const int sw = row & 7;
-    float Mi = -INFINITY, l = 0.f;
+    float M = 0.f, l = 0.f;
     bool ok = true;
+
+    // bias the accumulator for tile 0
+    {
+      uint32_t bias[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) bias[i] = kMagicBits;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_st32(tmem_S + lane_off + c * 32, bias);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&tail->s_empty);
+    }
+
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait(&tail->s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
       tc_fence_after();
       const float c0 = __fmul_rn(c_row, ks_h[2 * j]), c1 = __fmul_rn(c_row, ks_h[2 * j + 1]);
+      const float b0 = __fmul_rn(kMagic, c0), b1 = __fmul_rn(kMagic, c1);
       const int valid = min(BKV, p.Lk - j * BKV);
-      // ---- pass 1: row maximum in scaled units ----
-      float mloc = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_S + lane_off + c * 32, r);
-        tmem_ld_wait();
-        int imax = INT_MIN;
-        if (valid == BKV) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) imax = max(imax, static_cast<int>(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < valid) imax = max(imax, static_cast<int>(r[i]));
-        }
-        if (imax != INT_MIN) mloc = fmaxf(mloc, __fmul_rn(__int2float_rn(imax), c < 2 ? c0 : c1));
-      }
-      const float Mi_new = fmaxf(Mi, ceilf(mloc));
-      const bool grow = Mi_new > Mi;
+      const bool full = valid == BKV;
+      const uint32_t t_row = tmem_S + lane_off;
+      // ---- pass 1: row maximum (3-input max on the raw values, no arithmetic) ----
+      float mx0, mx1;
+      if (full) row_max_pass<true>(t_row, valid, mx0, mx1);
+      else row_max_pass<false>(t_row, valid, mx0, mx1);
+      const float m = fmaxf(mx0 > 0.f ? fmaf(mx0, c0, -b0) : -INFINITY, mx1 > 0.f ? fmaf(mx1, c1, -b1) : -INFINITY);
+      const float M_new = j == 0 ? ceilf(m) : fmaxf(M, ceilf(m));
+      const bool grow = j > 0 && M_new > M;
       if (j > 0) {
         // P.V of the previous tile has finished: O is complete up to tile j-1 and the P buffer is free
         if (!mbar_wait(&tail->pv_done, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) { ok = false; break; }
         if (__any_sync(0xffffffffu, grow)) {
           tc_fence_after();
-          const float f = grow ? ex2_approx(Mi - Mi_new) : 1.f;  // exact power of two
+          const float f = grow ? ex2_approx(M - M_new) : 1.f;  // exact power of two
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t r[32];
             tmem_ld32(tmem_O + lane_off + c * 32, r);
-            tmem_ld_wait();
+            tmem_ld_wait_regs(r);
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
             tmem_st32(tmem_O + lane_off + c * 32, r);
@@ -230,33 +333,43 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
           l *= f;
         }
       }
-      Mi = Mi_new;
-      const float off = 8.f - Mi;
-      // ---- pass 2: P = e4m3(2^(t - M + 8)) into shared memory, l += p ----
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_S + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (c == 3) {  // S has been read completely: the next Q.K^T may overwrite it
+      M = M_new;
+      const float off0 = __fsub_rn(__fsub_rn(8.f, M), b0), off1 = __fsub_rn(__fsub_rn(8.f, M), b1);
+      // ---- pass 2: P = e4m3(2^t) into shared memory, l += p; S is released as soon as it is in registers ----
+      uint64_t lsum2 = pack2(0.f, 0.f);
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld32(t_row, ra);
+        tmem_ld32(t_row + 32, rb);
+        tmem_ld_wait_regs(ra);
+        if (full) exp_chunk<true>(ra, 0, valid, c0, off0, p_row, sw, lsum2);
+        else exp_chunk<false>(ra, 0, valid, c0, off0, p_row, sw, lsum2);
+        tmem_ld_wait_regs(rb);
+        tmem_ld32(t_row + 64, ra);
+        if (full) exp_chunk<true>(rb, 1, valid, c0, off0, p_row, sw, lsum2);
+        else exp_chunk<false>(rb, 1, valid, c0, off0, p_row, sw, lsum2);
+        tmem_ld_wait_regs(ra);
+        tmem_ld32(t_row + 96, rb);
+        if (full) exp_chunk<true>(ra, 2, valid, c1, off1, p_row, sw, lsum2);
+        else exp_chunk<false>(ra, 2, valid, c1, off1, p_row, sw, lsum2);
+        tmem_ld_wait_regs(rb);
+        // all of S is in registers: bias it for the next Q.K^T and hand it back to the MMA warp
+        {
+          uint32_t bias[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) bias[i] = kMagicBits;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_st32(t_row + c * 32, bias);
+          tmem_st_wait();
           tc_fence_before();
           mbar_arrive(&tail->s_empty);
         }
-        const float cc = c < 2 ? c0 : c1;
-        float pv[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = ex2_approx(fmaf(__int2float_rn(static_cast<int>(r[i])), cc, off));
-          if (valid != BKV && c * 32 + i >= valid) e = 0.f;
-          pv[i] = e;
-          l += e;
-        }
-        uint32_t w[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = pack_e4m3x4(pv[4 * i], pv[4 * i + 1], pv[4 * i + 2], pv[4 * i + 3]);
-        *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        if (full) exp_chunk<true>(rb, 3, valid, c1, off1, p_row, sw, lsum2);
+        else exp_chunk<false>(rb, 3, valid, c1, off1, p_row, sw, lsum2);
       }
+      float la, lb;
+      unpack2(lsum2, la, lb);
+      l += la + lb;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&tail->p_full);
@@ -272,7 +385,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_O + lane_off + c * 32, r);
-        tmem_ld_wait();
+        tmem_ld_wait_regs(r);
         if (q_row < p.Lq) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {

@@ -140,13 +140,6 @@ __global__ void __launch_bounds__(128) kv_stats_final_kernel(const float* __rest
 // ---------------------------------------------------------------------------------------------
 // Q/K block-64 int8. One CTA per (64-token block, head); 8 warps x 8 tokens, lane = 4 channels.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ int quant_i8(float y, float s, float inv) {
-  const float yq = __fmul_rn(y, inv);
-  float r = rintf(yq);
-  if (fabsf(fabsf(yq - r) - 0.5f) < 1e-3f) r = rintf(__fdiv_rn(y, s));  // near a tie: exact division decides
-  return static_cast<int>(fminf(fmaxf(r, -127.f), 127.f));
-}
-
 __global__ void __launch_bounds__(256) quant_block64_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_ss,
                                                             int64_t x_sh, int64_t L, int64_t Lpad,
                                                             const float* __restrict__ mean,  // [H][128] or null
@@ -188,9 +181,8 @@ __global__ void __launch_bounds__(256) quant_block64_kernel(const __nv_bfloat16*
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int64_t s = blk * 64 + warp * 8 + i;
-    uint32_t packed = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) packed |= (static_cast<uint32_t>(quant_i8(v[i][j], sc, inv)) & 0xFFu) << (8 * j);
+    const uint32_t packed = pack_low_bytes(quant_code_i8(v[i][0], sc, inv), quant_code_i8(v[i][1], sc, inv),
+                                           quant_code_i8(v[i][2], sc, inv), quant_code_i8(v[i][3], sc, inv));
     *reinterpret_cast<uint32_t*>(out + (static_cast<int64_t>(h) * Lpad + s) * D + lane * 4) = packed;
   }
 }
@@ -198,17 +190,6 @@ __global__ void __launch_bounds__(256) quant_block64_kernel(const __nv_bfloat16*
 // ---------------------------------------------------------------------------------------------
 // V -> e4m3, transposed. One CTA per (128-token tile, head).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t quant_f8(float y, float s, float inv) {
-  float yq = fminf(fmaxf(__fmul_rn(y, inv), -448.f), 448.f);
-  uint32_t a = __nv_cvt_float_to_fp8(yq * (1.f - 0x1p-21f), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t b = __nv_cvt_float_to_fp8(yq * (1.f + 0x1p-21f), __NV_SATFINITE, __NV_E4M3);
-  if (a != b) {
-    const float ye = fminf(fmaxf(__fdiv_rn(y, s), -448.f), 448.f);
-    a = __nv_cvt_float_to_fp8(ye, __NV_SATFINITE, __NV_E4M3);
-  }
-  return a & 0xFFu;
-}
-
 __global__ void __launch_bounds__(256) quant_v_kernel(const __nv_bfloat16* __restrict__ V, int64_t v_ss, int64_t v_sh,
                                                       int64_t L, int64_t Lpad, const float* __restrict__ vmean,
                                                       const float* __restrict__ vscale, uint8_t* __restrict__ Vt) {
@@ -228,7 +209,7 @@ __global__ void __launch_bounds__(256) quant_v_kernel(const __nv_bfloat16* __res
       const float mm[4] = {m.x, m.y, m.z, m.w}, ss[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        packed |= quant_f8(__fsub_rn(x[j], mm[j]), ss[j], __fdiv_rn(1.f, ss[j])) << (8 * j);
+        packed |= quant_code_e4m3(__fsub_rn(x[j], mm[j]), ss[j], __fdiv_rn(1.f, ss[j])) << (8 * j);
     }
     *reinterpret_cast<uint32_t*>(&tile[r * P + c4]) = packed;
   }

@@ -201,6 +201,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Same wait, tied to the 32 destination registers of an earlier tmem_ld32 so that the compiler cannot
+// move arithmetic on them above the wait (the load delivers its registers asynchronously).
+__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),
+                 "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                 "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
@@ -249,6 +261,34 @@ __device__ __forceinline__ float warp_sum_xor(float v) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// exact quantizer steps without the conversion unit
+// ---------------------------------------------------------------------------------------------
+// int8 code of round_half_even(y / s) (|y / s| <= 127 by construction of s), returned in the low byte.
+// y * (1/s) is rounded by adding 1.5 * 2^23; only when the product lands within 1e-3 of a tie is the exact
+// IEEE quotient computed, so the code always equals the one a true division would give.
+__device__ __forceinline__ uint32_t quant_code_i8(float y, float s, float inv) {
+  const float kMagic = 12582912.f;
+  const float yq = __fmul_rn(y, inv);
+  float t = __fadd_rn(yq, kMagic);
+  const float r = __fsub_rn(t, kMagic);
+  if (fabsf(fabsf(yq - r) - 0.5f) < 1e-3f) t = __fadd_rn(__fdiv_rn(y, s), kMagic);
+  return __float_as_uint(t);  // low byte = two's complement code
+}
+// e4m3 code of clamp(y / s, +-448) rounded to nearest even. The fast path converts y * (1/s); the exact
+// quotient is used when the product is within 16 fp32 ulps of an e4m3 rounding tie or in e4m3's subnormal
+// range, where the two could round differently.
+__device__ __forceinline__ uint32_t quant_code_e4m3(float y, float s, float inv) {
+  float yq = fminf(fmaxf(__fmul_rn(y, inv), -448.f), 448.f);
+  const uint32_t drop = __float_as_uint(yq) & 0xFFFFFu;
+  if (fabsf(yq) < 0.015625f || (drop - 0x7FFF0u) < 0x20u) yq = fminf(fmaxf(__fdiv_rn(y, s), -448.f), 448.f);
+  return static_cast<uint32_t>(__nv_cvt_float_to_fp8(yq, __NV_SATFINITE, __NV_E4M3)) & 0xFFu;
+}
+// pack the low bytes of four words into one word (a -> byte 0 ... d -> byte 3)
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 }  // namespace rh3

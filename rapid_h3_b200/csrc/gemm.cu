@@ -196,7 +196,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(t_row + c * 32, r);
-        tmem_ld_wait();
+        tmem_ld_wait_regs(r);
         const int col0 = n0 + c * 32;
         if (row_ok && col0 < p.N) {
           if (p.acc_dump) {

@@ -73,25 +73,6 @@ __device__ __forceinline__ float block_sum_fixed(float v, float* red) {
   return r;
 }
 
-__device__ __forceinline__ int quant_i8_one(float y, float s, float inv) {
-  float yq = __fmul_rn(y, inv);
-  float r = rintf(yq);
-  if (fabsf(fabsf(yq - r) - 0.5f) < 1e-3f) r = rintf(__fdiv_rn(y, s));  // near a tie: exact division decides
-  r = fminf(fmaxf(r, -127.f), 127.f);
-  return static_cast<int>(r);
-}
-__device__ __forceinline__ uint32_t quant_f8_one(float y, float s, float inv) {
-  float yq = __fmul_rn(y, inv);
-  yq = fminf(fmaxf(yq, -448.f), 448.f);
-  uint32_t a = __nv_cvt_float_to_fp8(yq * (1.f - 0x1p-21f), __NV_SATFINITE, __NV_E4M3);
-  uint32_t b = __nv_cvt_float_to_fp8(yq * (1.f + 0x1p-21f), __NV_SATFINITE, __NV_E4M3);
-  if (a != b) {
-    float ye = fminf(fmaxf(__fdiv_rn(y, s), -448.f), 448.f);
-    a = __nv_cvt_float_to_fp8(ye, __NV_SATFINITE, __NV_E4M3);
-  }
-  return a & 0xFFu;
-}
-
 template <int KIND, int OUT_FP8, int T, int CPT>
 __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
   __shared__ float red[T / 32];
@@ -197,15 +178,11 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
       uint32_t o[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        uint32_t packed = 0;
+        uint32_t code[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t code;
-          if (OUT_FP8) code = quant_f8_one(v[i][4 * h + j], s, inv);
-          else code = static_cast<uint32_t>(quant_i8_one(v[i][4 * h + j], s, inv)) & 0xFFu;
-          packed |= code << (8 * j);
-        }
-        o[h] = packed;
+        for (int j = 0; j < 4; ++j)
+          code[j] = OUT_FP8 ? quant_code_e4m3(v[i][4 * h + j], s, inv) : quant_code_i8(v[i][4 * h + j], s, inv);
+        o[h] = pack_low_bytes(code[0], code[1], code[2], code[3]);
       }
       *reinterpret_cast<uint2*>(qrow + (static_cast<int64_t>(c) << 3)) = make_uint2(o[0], o[1]);
     }
