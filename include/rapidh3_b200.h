@@ -124,6 +124,7 @@ int rh3_attn_quant_v(const void* v, int64_t v_ss, int64_t v_sh, int64_t L, int64
 /* out[Lq, H, 128] bf16 (element strides o_ss, o_sh) = softmax(Q.K^T * softmax_scale) . V from the
  * pre-pass operands: int8 Q.K^T into int32, base-2 online softmax in fp32, P as e4m3 against the
  * running maximum, e4m3 P.V into fp32, out = (O/l) * vscale + vmean. Lq may differ from Lk.
+ * Lq_pad (the padded row count of q8 / qs per head) must be a multiple of 256, Lk_pad a multiple of 128.
  * Replaces attention_impl / the attn_fwd5 FP8-P.V kernel (attn_int8.cu:1538-1759, :2749-2849). */
 int rh3_attn_int8(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
                   const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk, int64_t Lk_pad,

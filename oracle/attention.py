@@ -78,10 +78,10 @@ def kv_stats(k, v):
     return kmean, vmean, am.clamp_min(1e-8) / 448.0
 
 
-def quant_block64(x, mean=None):
-    """x bf16 [L,H,128] -> (int8 [H,Lpad,128], fp32 [H,Lpad/64])."""
+def quant_block64(x, mean=None, pad=128):
+    """x bf16 [L,H,128] -> (int8 [H,Lpad,128], fp32 [H,Lpad/64]); Lpad = L rounded up to `pad`."""
     l, h, _ = x.shape
-    lpad = (l + 127) // 128 * 128
+    lpad = (l + pad - 1) // pad * pad
     xf = x.float()
     if mean is not None:
         xf = xf - mean[None]
@@ -105,7 +105,7 @@ def quant_v(v, vmean, vscale):
 
 def prepass(q, k, v):
     kmean, vmean, vscale = kv_stats(k, v)
-    q8, qs = quant_block64(q)
+    q8, qs = quant_block64(q, pad=256)  # the main kernel works on pairs of 128-query tiles
     k8, ks = quant_block64(k, kmean)
     return dict(q8=q8, qs=qs, k8=k8, ks=ks, vt=quant_v(v, vmean, vscale), vscale=vscale, vmean=vmean, kmean=kmean,
                 lq=q.shape[0], lk=k.shape[0])

@@ -42,7 +42,7 @@ def _headers_mtime():
 
 
 def _compile(nvcc, src, obj, verbose):
-    cmd = [nvcc, *NVCC_FLAGS, "-Xptxas", "-v" if verbose else "-warn-spills", "-c", src, "-o", obj]
+    cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("RH3_EXTRA_NVCC", "").split(), "-Xptxas", "-v" if verbose else "-warn-spills", "-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")

@@ -25,6 +25,11 @@ def _pad128(n):
     return (n + 127) // 128 * 128
 
 
+def _pad256(n):
+    """Query rows are padded to the 256-row pair of tiles one CTA of the main kernel works on."""
+    return (n + 255) // 256 * 256
+
+
 def _check_qkv(t, name):
     _lib.require_cuda(t)
     if t.dtype != torch.bfloat16 or t.ndim != 3 or t.shape[2] != D or t.stride(2) != 1:
@@ -34,7 +39,7 @@ def _check_qkv(t, name):
 @dataclass
 class Prepass:
     """Quantized operands of one attention call (the reference's int8_prepass list, as fields)."""
-    q8: torch.Tensor      # int8 [H, Lq_pad, 128]
+    q8: torch.Tensor      # int8 [H, Lq_pad, 128], Lq_pad a multiple of 256
     qs: torch.Tensor      # fp32 [H, Lq_pad/64]
     k8: torch.Tensor      # int8 [H, Lk_pad, 128]
     ks: torch.Tensor      # fp32 [H, Lk_pad/64]
@@ -75,7 +80,7 @@ def int8_prepass(q, k, v):
     if k.shape != v.shape or k.shape[1] != h:
         raise RuntimeError("k and v must have the same shape and q's head count")
     dev = q.device
-    lqp, lkp = _pad128(lq), _pad128(lk)
+    lqp, lkp = _pad256(lq), _pad128(lk)
     f32 = dict(device=dev, dtype=torch.float32)
     kmean, vmean, vscale = (torch.empty((h, D), **f32) for _ in range(3))
     nbytes = _lib.lib().rh3_attn_kv_stats_scratch_bytes(lk, h)

@@ -16,15 +16,20 @@
 // epilogue O/l*vscale+vmean) with the per-key-block scale structure of :1781-1889 (attn_fwd6) and
 // the operand definitions of bench/attn_emulate.py:10-23,88,101-103.
 //
-// One CTA = one 128-query tile of one head, 192 threads, two CTAs per SM (so one CTA's softmax
-// overlaps the other's MMAs):
-//   warp 0      TMA producer: Q once, then K tile (128 keys x 128 B) + V^T tile (128 ch x 128 keys)
-//   warp 1      MMA issuer: QK^T of tile j+1 is issued before P.V of tile j
-//   warps 2..5  one query row per thread: the accumulator is pre-biased with 1.5*2^23 so its int32 bits
-//               are a float (no conversion); pass 1 = 3-input max over the raw values, pass 2 =
-//               t = fma(bits, c, off) in packed f32x2, exp2, e4m3 pack; P goes to shared memory in the
-//               128-byte-swizzled K-major layout the MMA reads; O and l are rescaled by an exact power
-//               of two when the integer maximum grows
+// One CTA = TWO 128-query tiles of one head (256 rows), 384 threads = three warp groups, one CTA per
+// SM. The two tiles share every K / V^T tile that TMA brings in (3-stage ring) and run as two
+// independent softmax pipelines:
+//   warp group 0  service: warp 0 = TMA producer (Q once, then K tile 128 keys x 128 B + V^T tile 128
+//                 channels x 128 keys per step), warp 1 = MMA issuer (for both query tiles, Q.K^T of
+//                 key tile j+1 is issued before P.V of tile j); gives its registers away (setmaxnreg)
+//   warp groups 1, 2  softmax of query tile 0 / 1, one query row per thread, 240 registers each so a
+//                 whole row of S (128 values) lives in registers: the accumulator is pre-biased with
+//                 1.5*2^23 so its int32 bits are a float (no conversion); the row is read from TMEM
+//                 ONCE and S is handed straight back, so the next Q.K^T runs under the whole softmax;
+//                 3-input max over the raw values, then t = fma(bits, c, off) in packed f32x2, exp2,
+//                 e4m3 pack; P goes to shared memory in the 128-byte-swizzled K-major layout the MMA
+//                 reads; O and l are rescaled by an exact power of two when the integer maximum grows
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 columns each.
 // Tensor-core bound: 4 * Lq * Lk * 128 operations per head.
 #include <limits.h>
 
@@ -35,9 +40,10 @@ namespace rh3 {
 namespace {
 
 constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int QG = 2;                  // query tiles per CTA
 constexpr int TILE_BYTES = 128 * 128;  // every operand tile is 128 rows x 128 bytes
-constexpr int KV_STAGES = 2;
-constexpr int ATTN_THREADS = 192;
+constexpr int KV_STAGES = 3;
+constexpr int ATTN_THREADS = 384;      // service warp group + two softmax warp groups
 
 struct AttnParams {
   const float* qs;      // [H][Lq_pad/64]
@@ -55,12 +61,13 @@ struct __align__(8) AttnSmemTail {
   uint64_t q_full;
   uint64_t kv_full[KV_STAGES];
   uint64_t kv_empty[KV_STAGES];
-  uint64_t s_full, s_empty, p_full, pv_done;
+  uint64_t s_full[QG], s_empty[QG], p_full[QG], pv_done[QG];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-constexpr int ATTN_SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + sizeof(AttnSmemTail) + 1024;
+// Q (2 tiles) | P (2 tiles) | KV ring (K + V^T per stage)
+constexpr int ATTN_SMEM_BYTES = (2 * QG + 2 * KV_STAGES) * TILE_BYTES + sizeof(AttnSmemTail) + 1024;
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -80,6 +87,7 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
 
 constexpr float kMagic = 12582912.f;            // 1.5 * 2^23: float(kMagic + s) has s in its low mantissa bits
 constexpr uint32_t kMagicBits = 0x4B400000u;    // the same value as int32 bits, used to pre-bias S in TMEM
+constexpr uint32_t kNegInfBits = 0xFF800000u;
 
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
@@ -105,46 +113,26 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-// Largest raw value (a float 1.5*2^23 + s, or 0 if every column is masked) of one 32-column chunk.
-template <bool FULL>
-__device__ __forceinline__ float chunk_max(const uint32_t* r, int col0, int valid) {
-  float m = 0.f;
-  if (FULL) {
-    m = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+// Columns at or beyond `valid` (padding keys of the last tile) become -inf: they lose every max and
+// their probability is exactly 0.
+__device__ __forceinline__ void mask_tail(uint32_t* r, int col0, int valid) {
 #pragma unroll
-    for (int i = 3; i < 31; i += 2) m = max3(m, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-    m = fmaxf(m, __uint_as_float(r[31]));
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (col0 + i < valid) m = fmaxf(m, __uint_as_float(r[i]));
-  }
-  return m;
+  for (int i = 0; i < 32; ++i)
+    if (col0 + i >= valid) r[i] = kNegInfBits;
 }
 
-// Pass 1: largest raw value of each 64-key half of one row of S (TMEM loads double-buffered).
-template <bool FULL>
-__device__ __forceinline__ void row_max_pass(uint32_t t_row, int valid, float& mx0, float& mx1) {
-  uint32_t ra[32], rb[32];
-  tmem_ld32(t_row, ra);
-  tmem_ld32(t_row + 32, rb);
-  tmem_ld_wait_regs(ra);
-  tmem_ld_wait_regs(rb);
-  const float m0 = chunk_max<FULL>(ra, 0, valid), m1 = chunk_max<FULL>(rb, 32, valid);
-  tmem_ld32(t_row + 64, ra);
-  tmem_ld32(t_row + 96, rb);
-  tmem_ld_wait_regs(ra);
-  tmem_ld_wait_regs(rb);
-  const float m2 = chunk_max<FULL>(ra, 64, valid), m3 = chunk_max<FULL>(rb, 96, valid);
-  mx0 = fmaxf(m0, m1);
-  mx1 = fmaxf(m2, m3);
+// Largest raw value (a float 1.5*2^23 + s) of one 32-column chunk, with 3-input max.
+__device__ __forceinline__ float chunk_max(const uint32_t* r) {
+  float m = max3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+#pragma unroll
+  for (int i = 3; i < 31; i += 2) m = max3(m, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+  return fmaxf(m, __uint_as_float(r[31]));
 }
 
-// Pass 2, one 32-column chunk: p = 2^(bits * cc + off) in packed f32x2, e4m3 codes written to the row of P
-// in shared memory (16-byte chunks 2k and 2k+1 of the row, XOR-swizzled), unrounded p added to the sum.
-template <bool FULL>
-__device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, int valid, float cc, float off, uint8_t* p_row,
-                                          int sw, uint64_t& lsum2) {
+// One 32-column chunk: p = 2^(bits * cc + off) in packed f32x2, e4m3 codes written to 16-byte chunks
+// 2k and 2k+1 of the row of P in shared memory (XOR-swizzled), unrounded p added to the sum.
+__device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, float cc, float off, uint8_t* p_row, int sw,
+                                          uint64_t& lsum2) {
   const uint64_t cc2 = pack2(cc, cc), off2 = pack2(off, off);
   uint32_t w[8];
 #pragma unroll
@@ -153,13 +141,6 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, int valid, f
     unpack2(fma2(pack2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), cc2, off2), pa, pb);
     unpack2(fma2(pack2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), cc2, off2), pc, pd);
     pa = ex2_approx(pa); pb = ex2_approx(pb); pc = ex2_approx(pc); pd = ex2_approx(pd);
-    if (!FULL) {
-      const int col = k * 32 + 4 * i;
-      if (col >= valid) pa = 0.f;
-      if (col + 1 >= valid) pb = 0.f;
-      if (col + 2 >= valid) pc = 0.f;
-      if (col + 3 >= valid) pd = 0.f;
-    }
     lsum2 = add2(lsum2, add2(pack2(pa, pb), pack2(pc, pd)));
     w[i] = pack_e4m3x4(pa, pb, pc, pd);
   }
@@ -167,19 +148,23 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, int valid, f
   *reinterpret_cast<uint4*>(p_row + (((2 * k + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-__global__ void __launch_bounds__(ATTN_THREADS, 2)
+// Register reallocation between warp groups (one instruction per warp, all four warps of the group).
+__device__ __forceinline__ void reg_dealloc_24() { asm volatile("setmaxnreg.dec.sync.aligned.u32 24;"); }
+__device__ __forceinline__ void reg_alloc_240() { asm volatile("setmaxnreg.inc.sync.aligned.u32 240;"); }
+
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                  const __grid_constant__ CUtensorMap tma_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sP = smem + TILE_BYTES;
-  uint8_t* sKV = smem + 2 * TILE_BYTES;  // stage s: K at +s*2*TILE, V^T at +s*2*TILE + TILE
-  AttnSmemTail* tail = reinterpret_cast<AttnSmemTail*>(smem + (2 + 2 * KV_STAGES) * TILE_BYTES);
+  uint8_t* sQ = smem;                            // [QG] tiles
+  uint8_t* sP = smem + QG * TILE_BYTES;          // [QG] tiles
+  uint8_t* sKV = smem + 2 * QG * TILE_BYTES;     // stage s: K at +s*2*TILE, V^T at +s*2*TILE + TILE
+  AttnSmemTail* tail = reinterpret_cast<AttnSmemTail*>(smem + (2 * QG + 2 * KV_STAGES) * TILE_BYTES);
   volatile int* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = blockIdx.x, h = blockIdx.y;
+  const int q_pair = blockIdx.x, h = blockIdx.y;
   const int n_kv = (p.Lk + BKV - 1) / BKV;
 
   if (threadIdx.x == 0) {
@@ -188,31 +173,34 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       mbar_init(&tail->kv_full[s], 1);
       mbar_init(&tail->kv_empty[s], 1);
     }
-    mbar_init(&tail->s_full, 1);
-    mbar_init(&tail->s_empty, 128);
-    mbar_init(&tail->p_full, 128);
-    mbar_init(&tail->pv_done, 1);
+    for (int g = 0; g < QG; ++g) {
+      mbar_init(&tail->s_full[g], 1);
+      mbar_init(&tail->s_empty[g], 128);
+      mbar_init(&tail->p_full[g], 128);
+      mbar_init(&tail->pv_done[g], 1);
+    }
     tail->abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(&tail->tmem_base, 256);
+    tmem_alloc(&tail->tmem_base, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tail->tmem_base;
-  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+  if (warp < 4) {
+    // ============================ service warp group: TMA + MMA issue ============================
+    reg_dealloc_24();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
       tma_prefetch_desc(&tma_q);
       tma_prefetch_desc(&tma_k);
       tma_prefetch_desc(&tma_v);
-      mbar_arrive_expect_tx(&tail->q_full, TILE_BYTES);
-      tma_load_2d(sQ, &tma_q, 0, h * p.Lq_pad + q_tile * BQ, &tail->q_full);
+      mbar_arrive_expect_tx(&tail->q_full, QG * TILE_BYTES);
+      tma_load_2d(sQ, &tma_q, 0, h * p.Lq_pad + q_pair * (QG * BQ), &tail->q_full);
       for (int j = 0; j < n_kv; ++j) {
         const int stage = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
@@ -222,112 +210,145 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         tma_load_2d(sk, &tma_k, 0, h * p.Lk_pad + j * BKV, &tail->kv_full[stage]);
         tma_load_2d(sk + TILE_BYTES, &tma_v, j * BKV, h * HD, &tail->kv_full[stage]);
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------ MMA issuer ------------------------------
       constexpr uint32_t idesc_qk = make_idesc(2, 1, 1, BQ, BKV);  // s32 += s8 * s8
       constexpr uint32_t idesc_pv = make_idesc(1, 0, 0, BQ, HD);   // f32 += e4m3 * e4m3
-      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-      auto issue_qk = [&](int j) {
+      // S is pre-biased by the softmax warps: completion k of s_empty[g] precedes Q.K^T of key tile k,
+      // which therefore always accumulates onto the bias.
+      auto issue_qk = [&](int g, int j) {
+        const uint32_t q_addr = smem_u32(sQ + g * TILE_BYTES);
         const uint32_t k_addr = smem_u32(sKV + (j % KV_STAGES) * 2 * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          mma_i8_ss(tmem_S, make_desc_k128(q_addr + k * 32), make_desc_k128(k_addr + k * 32), idesc_qk, 1);
-        mma_commit(&tail->s_full);
+          mma_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr + k * 32), make_desc_k128(k_addr + k * 32), idesc_qk, 1);
+        mma_commit(&tail->s_full[g]);
       };
-      // S is pre-biased by the softmax warps (completion k of s_empty precedes Q.K^T of tile k)
       bool ok = mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
-                mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
-                mbar_wait(&tail->s_empty, 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
-      if (ok) {
-        tc_fence_after();
-        issue_qk(0);
+                mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
+      for (int g = 0; g < QG && ok; ++g) {
+        ok = mbar_wait(&tail->s_empty[g], 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
+        if (ok) {
+          tc_fence_after();
+          issue_qk(g, 0);
+        }
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) {
           const int ns = (j + 1) % KV_STAGES;
-          if (!mbar_wait(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) ||
-              !mbar_wait(&tail->s_empty, (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY)) {
-            ok = false;
-            break;
+          ok = mbar_wait(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
+          for (int g = 0; g < QG && ok; ++g) {
+            ok = mbar_wait(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
+            if (ok) {
+              tc_fence_after();
+              issue_qk(g, j + 1);
+            }
           }
-          tc_fence_after();
-          issue_qk(j + 1);
+          if (!ok) break;
         }
-        if (!mbar_wait(&tail->p_full, j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
         const int stage = j % KV_STAGES;
         const uint32_t v_addr = smem_u32(sKV + stage * 2 * TILE_BYTES + TILE_BYTES);
+        for (int g = 0; g < QG && ok; ++g) {
+          ok = mbar_wait(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f8_ss(tmem_O, make_desc_k128(p_addr + k * 32), make_desc_k128(v_addr + k * 32), idesc_pv,
-                    (j | k) != 0);
-        mma_commit(&tail->kv_empty[stage]);
-        mma_commit(&tail->pv_done);
+          for (int k = 0; k < 4; ++k)
+            mma_f8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr + k * 32), make_desc_k128(v_addr + k * 32),
+                      idesc_pv, (j | k) != 0);
+          mma_commit(&tail->pv_done[g]);
+        }
+        if (ok) mma_commit(&tail->kv_empty[stage]);  // both query tiles have read this K / V^T stage
       }
     }
   } else {
-    // ------------------------------ softmax / correction / epilogue ------------------------------
+    // ============================ softmax warp groups ============================
     // S arrives as raw bits of the float 1.5*2^23 + s (the accumulator is pre-biased, see below), so
     // t = fma(bits, c, off) needs no int->float conversion and the row maximum is a 3-input float max
-    // on the raw values. Pass 1 finds the maximum, pass 2 computes P; S is handed back to the MMA warp
-    // as soon as pass 2 has it in registers, so the next Q.K^T overlaps the last quarter of the tile.
-    const int quad = warp & 3;
+    // on the raw values. The row is read from TMEM once and S is handed back to the MMA warp right
+    // away, so the next Q.K^T of this query tile runs under the whole softmax of the current one.
+    reg_alloc_240();
+    const int g = (warp >> 2) - 1;     // query tile of this warp group
+    const int quad = warp & 3;         // TMEM lane quadrant this warp may access
     const int row = quad * 32 + lane;  // row of the tile = TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    const int64_t q_row = static_cast<int64_t>(q_tile) * BQ + row;
+    const uint32_t t_row = tmem_base + g * 128 + lane_off;        // this row of S
+    const uint32_t o_row = tmem_base + 256 + g * 128 + lane_off;  // this row of O
+    const int64_t q_row = static_cast<int64_t>(q_pair) * (QG * BQ) + g * BQ + row;
     const float c_row = __fmul_rn(p.qs[static_cast<int64_t>(h) * (p.Lq_pad / 64) + (q_row >> 6)], p.sl2);
     const float* ks_h = p.ks + static_cast<int64_t>(h) * (p.Lk_pad / 64);
-    uint8_t* p_row = sP + row * 128;
+    uint8_t* p_row = sP + g * TILE_BYTES + row * 128;
     const int sw = row & 7;
+    uint64_t* s_full = &tail->s_full[g];
+    uint64_t* s_empty = &tail->s_empty[g];
+    uint64_t* p_full = &tail->p_full[g];
+    uint64_t* pv_done = &tail->pv_done[g];
     float M = 0.f, l = 0.f;
     bool ok = true;
 
     // bias the accumulator for tile 0
-    {
-      uint32_t bias[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) bias[i] = kMagicBits;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_st32(tmem_S + lane_off + c * 32, bias);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&tail->s_empty);
-    }
+    tmem_st32_splat(t_row, kMagicBits);
+    tmem_st32_splat(t_row + 32, kMagicBits);
+    tmem_st32_splat(t_row + 64, kMagicBits);
+    tmem_st32_splat(t_row + 96, kMagicBits);
+    tmem_st_wait();
+    tc_fence_before();
+    mbar_arrive(s_empty);
+    float ks0 = ks_h[0], ks1 = ks_h[1];  // block scales of the tile ahead are fetched one tile early
 
     for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait(&tail->s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
-      tc_fence_after();
-      const float c0 = __fmul_rn(c_row, ks_h[2 * j]), c1 = __fmul_rn(c_row, ks_h[2 * j + 1]);
+      const float c0 = __fmul_rn(c_row, ks0), c1 = __fmul_rn(c_row, ks1);
+      if (j + 1 < n_kv) {
+        ks0 = ks_h[2 * j + 2];
+        ks1 = ks_h[2 * j + 3];
+      }
       const float b0 = __fmul_rn(kMagic, c0), b1 = __fmul_rn(kMagic, c1);
       const int valid = min(BKV, p.Lk - j * BKV);
-      const bool full = valid == BKV;
-      const uint32_t t_row = tmem_S + lane_off;
-      // ---- pass 1: row maximum (3-input max on the raw values, no arithmetic) ----
-      float mx0, mx1;
-      if (full) row_max_pass<true>(t_row, valid, mx0, mx1);
-      else row_max_pass<false>(t_row, valid, mx0, mx1);
+      if (!mbar_wait(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
+      tc_fence_after();
+      // ---- the whole row of S (128 raw values) into registers, once ----
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld32(t_row, r0);
+      tmem_ld32(t_row + 32, r1);
+      tmem_ld32(t_row + 64, r2);
+      tmem_ld32(t_row + 96, r3);
+      tmem_ld_wait_regs(r0);
+      tmem_ld_wait_regs(r1);
+      tmem_ld_wait_regs(r2);
+      tmem_ld_wait_regs(r3);
+      // S is in registers: bias it for the next Q.K^T and hand it back
+      tmem_st32_splat(t_row, kMagicBits);
+      tmem_st32_splat(t_row + 32, kMagicBits);
+      tmem_st32_splat(t_row + 64, kMagicBits);
+      tmem_st32_splat(t_row + 96, kMagicBits);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(s_empty);
+      if (valid != BKV) {
+        mask_tail(r0, 0, valid);
+        mask_tail(r1, 32, valid);
+        mask_tail(r2, 64, valid);
+        mask_tail(r3, 96, valid);
+      }
+      // ---- row maximum: 3-input max on the raw values, one multiply-add per 64-key block ----
+      const float mx0 = fmaxf(chunk_max(r0), chunk_max(r1)), mx1 = fmaxf(chunk_max(r2), chunk_max(r3));
       const float m = fmaxf(mx0 > 0.f ? fmaf(mx0, c0, -b0) : -INFINITY, mx1 > 0.f ? fmaf(mx1, c1, -b1) : -INFINITY);
       const float M_new = j == 0 ? ceilf(m) : fmaxf(M, ceilf(m));
       const bool grow = j > 0 && M_new > M;
       if (j > 0) {
         // P.V of the previous tile has finished: O is complete up to tile j-1 and the P buffer is free
-        if (!mbar_wait(&tail->pv_done, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) { ok = false; break; }
+        if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) { ok = false; break; }
         if (__any_sync(0xffffffffu, grow)) {
           tc_fence_after();
           const float f = grow ? ex2_approx(M - M_new) : 1.f;  // exact power of two
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tmem_O + lane_off + c * 32, r);
-            tmem_ld_wait_regs(r);
+          for (int c = 0; c < 16; ++c) {  // 8 columns at a time: this path is rare and must stay small
+            uint32_t r[8];
+            tmem_ld8(o_row + c * 8, r);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-            tmem_st32(tmem_O + lane_off + c * 32, r);
+            for (int i = 0; i < 8; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+            tmem_st8(o_row + c * 8, r);
           }
           tmem_st_wait();
           l *= f;
@@ -335,70 +356,40 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       }
       M = M_new;
       const float off0 = __fsub_rn(__fsub_rn(8.f, M), b0), off1 = __fsub_rn(__fsub_rn(8.f, M), b1);
-      // ---- pass 2: P = e4m3(2^t) into shared memory, l += p; S is released as soon as it is in registers ----
+      // ---- P = e4m3(2^t) into shared memory, l += p ----
       uint64_t lsum2 = pack2(0.f, 0.f);
-      {
-        uint32_t ra[32], rb[32];
-        tmem_ld32(t_row, ra);
-        tmem_ld32(t_row + 32, rb);
-        tmem_ld_wait_regs(ra);
-        if (full) exp_chunk<true>(ra, 0, valid, c0, off0, p_row, sw, lsum2);
-        else exp_chunk<false>(ra, 0, valid, c0, off0, p_row, sw, lsum2);
-        tmem_ld_wait_regs(rb);
-        tmem_ld32(t_row + 64, ra);
-        if (full) exp_chunk<true>(rb, 1, valid, c0, off0, p_row, sw, lsum2);
-        else exp_chunk<false>(rb, 1, valid, c0, off0, p_row, sw, lsum2);
-        tmem_ld_wait_regs(ra);
-        tmem_ld32(t_row + 96, rb);
-        if (full) exp_chunk<true>(ra, 2, valid, c1, off1, p_row, sw, lsum2);
-        else exp_chunk<false>(ra, 2, valid, c1, off1, p_row, sw, lsum2);
-        tmem_ld_wait_regs(rb);
-        // all of S is in registers: bias it for the next Q.K^T and hand it back to the MMA warp
-        {
-          uint32_t bias[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) bias[i] = kMagicBits;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_st32(t_row + c * 32, bias);
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(&tail->s_empty);
-        }
-        if (full) exp_chunk<true>(rb, 3, valid, c1, off1, p_row, sw, lsum2);
-        else exp_chunk<false>(rb, 3, valid, c1, off1, p_row, sw, lsum2);
-      }
+      exp_chunk(r0, 0, c0, off0, p_row, sw, lsum2);
+      exp_chunk(r1, 1, c0, off0, p_row, sw, lsum2);
+      exp_chunk(r2, 2, c1, off1, p_row, sw, lsum2);
+      exp_chunk(r3, 3, c1, off1, p_row, sw, lsum2);
       float la, lb;
       unpack2(lsum2, la, lb);
       l += la + lb;
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&tail->p_full);
+      mbar_arrive(p_full);
     }
     // ---- epilogue ----
-    if (ok && mbar_wait(&tail->pv_done, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) {
+    if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) {
       tc_fence_after();
       const float inv_l = __fdiv_rn(1.f, l);
       const float* vs = p.vscale + h * HD;
       const float* vm = p.vmean + h * HD;
       __nv_bfloat16* o = p.out + q_row * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem_O + lane_off + c * 32, r);
-        tmem_ld_wait_regs(r);
+      for (int c = 0; c < 16; ++c) {
+        uint32_t r[8];
+        tmem_ld8(o_row + c * 8, r);
         if (q_row < p.Lq) {
+          uint32_t w[4];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int d = c * 32 + g * 8 + 2 * i;
-              const float a = fmaf(__uint_as_float(r[g * 8 + 2 * i]) * inv_l, vs[d], vm[d]);
-              const float b = fmaf(__uint_as_float(r[g * 8 + 2 * i + 1]) * inv_l, vs[d + 1], vm[d + 1]);
-              w[i] = pack_bf16x2(a, b);
-            }
-            *reinterpret_cast<uint4*>(o + c * 32 + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int i = 0; i < 4; ++i) {
+            const int d = c * 8 + 2 * i;
+            const float a = fmaf(__uint_as_float(r[2 * i]) * inv_l, vs[d], vm[d]);
+            const float b = fmaf(__uint_as_float(r[2 * i + 1]) * inv_l, vs[d + 1], vm[d + 1]);
+            w[i] = pack_bf16x2(a, b);
           }
+          *reinterpret_cast<uint4*>(o + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
@@ -413,7 +404,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -430,15 +421,15 @@ extern "C" int rh3_attn_int8(const void* q8, const float* qs, const void* k8, co
                              cudaStream_t stream) {
   RH3_CHECK_ARG(Lq > 0 && Lk > 0 && H > 0 && H < 65536, "attn_int8: bad shape Lq=%lld Lk=%lld H=%lld", (long long)Lq,
                 (long long)Lk, (long long)H);
-  RH3_CHECK_ARG(Lq_pad >= Lq && Lk_pad >= Lk && Lq_pad % 128 == 0 && Lk_pad % 128 == 0,
-                "attn_int8: padded lengths must be multiples of 128 and cover Lq / Lk");
+  RH3_CHECK_ARG(Lq_pad >= Lq && Lk_pad >= Lk && Lq_pad % 256 == 0 && Lk_pad % 128 == 0,
+                "attn_int8: Lq_pad must be a multiple of 256 and Lk_pad a multiple of 128, covering Lq / Lk");
   RH3_CHECK_ARG(H * Lq_pad < (1ll << 31) && H * Lk_pad < (1ll << 31), "attn_int8: H * Lpad too large");
   RH3_CHECK_ARG(q8 && qs && k8 && ks && vt && vscale && vmean && out, "attn_int8: null pointer");
   RH3_CHECK_ARG(aligned16(q8) && aligned16(k8) && aligned16(vt) && aligned16(out) && o_ss % 8 == 0 && o_sh % 8 == 0,
                 "attn_int8: operands must be 16-byte aligned, output strides multiples of 8 elements");
   RH3_CHECK_ARG(softmax_scale > 0.f, "attn_int8: softmax scale must be positive");
   CUtensorMap tq, tk, tv;
-  if (int e = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q8, HD, H * Lq_pad, HD, HD, BQ,
+  if (int e = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q8, HD, H * Lq_pad, HD, HD, QG * BQ,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return e;
   if (int e = make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k8, HD, H * Lk_pad, HD, HD, BKV,
@@ -453,11 +444,12 @@ extern "C" int rh3_attn_int8(const void* q8, const float* qs, const void* k8, co
   p.Lq = (int)Lq; p.Lk = (int)Lk; p.Lq_pad = (int)Lq_pad; p.Lk_pad = (int)Lk_pad; p.H = (int)H;
   p.sl2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
   p.status = device_status_word();
-  if (int e = check_cuda(cudaFuncSetAttribute(attn_int8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              ATTN_SMEM_BYTES),
+  const dim3 grid(static_cast<unsigned>((Lq + QG * BQ - 1) / (QG * BQ)), static_cast<unsigned>(H));
+  auto kern = attn_int8_kernel;
+  if (int e = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM_BYTES),
                          "attn smem attribute"))
     return e;
-  const dim3 grid(static_cast<unsigned>((Lq + BQ - 1) / BQ), static_cast<unsigned>(H));
-  attn_int8_kernel<<<grid, ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  kern<<<grid, ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
   return check_cuda(cudaGetLastError(), "attn_int8 launch");
 }
+
