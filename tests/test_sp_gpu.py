@@ -1,0 +1,48 @@
+"""Sequence-parallel step on 2 GPUs (NCCL) against the single-GPU step: token shards + Ulysses exchange must
+reproduce the single-GPU result exactly (every op is row-local or head-local, and the attention statistics
+of a head always see its full sequence). Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+    import rapid_h3_b200 as r
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        cfg = r.model.H3Config.tiny(n_blocks=2, heads=4, d_model=512, mlp_hidden=1024)
+        model = r.model.init_weights(r.model.H3Transformer(cfg), seed=2).cuda()
+        grid, n_audio = (5, 6, 7), 11
+        inputs = [t.cuda() for t in r.step.make_inputs(cfg, grid, n_audio, 2, 40, seed=3)]
+        rt = r.step.H3Runtime(model)
+        ref_v, ref_a = rt.step(*inputs)                       # every rank: the whole sequence on its own GPU
+        sp = r.sp.Ulysses(grid[0] * grid[1] * grid[2] + n_audio)
+        v, a = rt.step(*inputs, sp=sp)
+        r._lib.check_status()
+        ret[rank] = bool(torch.equal(v, ref_v) and torch.equal(a, ref_a))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_two_rank_step_equals_single_gpu_step():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert dict(ret) == {0: True, 1: True}
