@@ -9,12 +9,16 @@ import torch
 import torch.distributed as dist
 
 
-def shard_bounds(total, world):
-    """Contiguous, nearly equal token ranges: [(start, stop)] per rank."""
-    base, extra = divmod(total, world)
+def shard_bounds(total, world, align=64):
+    """Contiguous, nearly equal token ranges [(start, stop)] per rank. Boundaries fall on multiples of
+    `align` tokens (the last rank takes the ragged tail): the attention query quantizer works on blocks of
+    64 tokens, so aligned shards see exactly the blocks the unsharded sequence has and the sequence-parallel
+    step reproduces the single-GPU step bit for bit."""
+    nblk = (total + align - 1) // align
+    base, extra = divmod(nblk, world)
     out, a = [], 0
     for r in range(world):
-        b = a + base + (1 if r < extra else 0)
+        b = min(total, a + (base + (1 if r < extra else 0)) * align)
         out.append((a, b))
         a = b
     return out

@@ -13,13 +13,15 @@ from rapid_h3_b200 import sp as spmod
 
 def test_shard_bounds_and_segments():
     b = spmod.shard_bounds(36436, 8)
-    assert b[0] == (0, 4555) and b[-1][1] == 36436 and sum(hi - lo for lo, hi in b) == 36436
-    assert max(hi - lo for lo, hi in b) - min(hi - lo for lo, hi in b) <= 1
+    assert b[0] == (0, 72 * 64) and b[-1][1] == 36436 and sum(hi - lo for lo, hi in b) == 36436
+    assert all(lo % 64 == 0 for lo, _ in b) and all(hi > lo for lo, hi in b)
+    assert max(hi - lo for lo, hi in b) - min(hi - lo for lo, hi in b) <= 128
+    assert spmod.shard_bounds(37, 2, align=1) == [(0, 19), (19, 37)]
     segs = [(0, 36288, 0), (36288, 36436, 1)]
     lo, hi = b[-1]
     cut = spmod.shard_segments(segs, lo, hi)
     assert cut == [(0, 36288 - lo, 0), (36288 - lo, hi - lo, 1)]
-    assert spmod.shard_segments(segs, *b[0]) == [(0, 4555, 0)]
+    assert spmod.shard_segments(segs, *b[0]) == [(0, 72 * 64, 0)]
 
 
 def _free_port():
@@ -54,7 +56,7 @@ def _worker(rank, world, port, total, heads, hd, ret):
 
 @pytest.mark.timeout(120)
 def test_ulysses_exchanges_are_exact_permutations():
-    world, total, heads, hd = 2, 37, 4, 8   # 37 tokens: uneven shards (19 + 18)
+    world, total, heads, hd = 2, 165, 4, 8   # 165 tokens: uneven shards (128 + 37)
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), total, heads, hd, ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}

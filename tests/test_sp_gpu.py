@@ -26,7 +26,7 @@ def _worker(rank, world, port, ret):
     try:
         cfg = r.model.H3Config.tiny(n_blocks=2, heads=4, d_model=512, mlp_hidden=1024)
         model = r.model.init_weights(r.model.H3Transformer(cfg), seed=2).cuda()
-        grid, n_audio = (5, 6, 7), 11
+        grid, n_audio = (5, 6, 7), 11  # 221 tokens: shards of 128 + 93
         inputs = [t.cuda() for t in r.step.make_inputs(cfg, grid, n_audio, 2, 40, seed=3)]
         rt = r.step.H3Runtime(model)
         ref_v, ref_a = rt.step(*inputs)                       # every rank: the whole sequence on its own GPU
