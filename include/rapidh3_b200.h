@@ -130,6 +130,28 @@ int rh3_attn_int8(const void* q8, const float* qs, const void* k8, const float* 
                   const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk, int64_t Lk_pad,
                   int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh, cudaStream_t stream);
 
+/* ---- VAE decoder: causal 3-D convolution as implicit GEMM, GroupNorm + SiLU, upsampling --------------- */
+/* None of these has a counterpart in the reference (its VAE fast path accelerates a transformer decoder,
+ * custom_nodes/rapid_h3/vae_fast.py:430-437); they implement the causal conv3d decoder of the benchmark
+ * configuration. Activations are channels-last bf16 [N, T, H, W, C]. */
+/* out = bf16(conv3x3x3(x, w) + bias (+ residual)); w is [Cout, 27, Cin] with tap = (dt*3 + dh)*3 + dw; zero
+ * padding of one pixel in H and W and of two frames before t = 0 (causal). Cin % 64 == 0, Cout % 16 == 0.
+ * bias, residual and gn_part may be NULL. gn_part (fp32 [rh3_conv3d_gn_part_rows(), 32, 2]) receives
+ * per-row-block partial (sum, sum of squares) of the stored outputs for each of 32 GroupNorm groups. */
+int rh3_conv3d_causal(const void* x, const void* w, const void* bias, const void* residual, void* out,
+                      float* gn_part, int64_t N, int64_t T, int64_t H, int64_t W, int64_t Cin, int64_t Cout,
+                      cudaStream_t stream);
+/* Number of row blocks (first dimension of gn_part) for an output of N x T x H x W sites (a size, not a status). */
+int64_t rh3_conv3d_gn_part_rows(int64_t N, int64_t T, int64_t H, int64_t W);
+/* sums (fp64 [N, 32, 2]) = per-sample, per-group (sum, sum of squares) over rows_per_sample row blocks. */
+int rh3_gn_reduce(const float* gn_part, int64_t rows_per_sample, int64_t N, double* sums, cudaStream_t stream);
+/* y = silu((x - mean[n, g]) * rstd[n, g] * gamma[c] + beta[c]); mean_rstd is fp32 [N, 32, 2]; 32 groups. */
+int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const void* gamma, const void* beta, int64_t N,
+                      int64_t sites_per_sample, int64_t C, void* y, cudaStream_t stream);
+/* y[N, 2T-1, 2H, 2W, C]: nearest-neighbour 2x in space, causal 2x in time (the first frame is not repeated). */
+int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t T, int64_t H, int64_t W, int64_t C,
+                          cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

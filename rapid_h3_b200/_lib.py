@@ -36,9 +36,14 @@ SIGNATURES = {
     "rh3_attn_quant_qk": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
     "rh3_attn_quant_v": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
     "rh3_attn_int8": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _I64, _I64, _P],
+    "rh3_conv3d_causal": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
+    "rh3_conv3d_gn_part_rows": [_I64, _I64, _I64, _I64],
+    "rh3_gn_reduce": [_P, _I64, _I64, _P, _P],
+    "rh3_gn_silu_apply": [_P, _P, _P, _P, _I64, _I64, _I64, _P, _P],
+    "rh3_upsample_causal2x": [_P, _P, _I64, _I64, _I64, _I64, _I64, _P],
 }
 # entry points that return a value instead of a status
-RETURNS_I64 = ("rh3_attn_kv_stats_scratch_bytes",)
+RETURNS_I64 = ("rh3_attn_kv_stats_scratch_bytes", "rh3_conv3d_gn_part_rows")
 
 KIND_I8, KIND_F8 = 0, 1
 
@@ -46,7 +51,7 @@ _lib = None
 
 # kernels launched per entry point (for launch accounting in benchmarks)
 LAUNCHES = {"rh3_attn_kv_stats": 2, "rh3_attn_kv_stats_noalloc": 2, "rh3_version": 0, "rh3_sm_count": 0, "rh3_check_status": 0,
-            "rh3_attn_kv_stats_scratch_bytes": 0}
+            "rh3_attn_kv_stats_scratch_bytes": 0, "rh3_conv3d_gn_part_rows": 0}
 launch_count = 0
 
 

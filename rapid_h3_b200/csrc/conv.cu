@@ -1,0 +1,460 @@
+// Causal 3x3x3 convolution of the VAE decoder as an implicit GEMM on the Blackwell tensor cores, plus
+// the GroupNorm + SiLU kernels that sit between convolutions.
+//
+//   x   [N, T, H, W, Cin]  bf16 channels-last          w [Cout, 27, Cin] bf16 (tap = (dt*3 + dh)*3 + dw)
+//   out [N, T, H, W, Cout] bf16 = bf16( sum_{tap, ci} x[n, t+dt-2, h+dh-1, w+dw-1, ci] * w[co, tap, ci]
+//                                      + bias[co] (+ residual[n, t, h, w, co]) )
+//   zero padding: one pixel around H and W, two frames BEFORE t = 0 (causal: no frame after t is read).
+//
+// There is no im2col buffer: for every tap the A operand of the GEMM is a shifted box of the input,
+// fetched by a 5-D TMA tensor copy whose out-of-range coordinates are filled with zeros (that is the
+// padding). One output tile = bh x bw sites of one frame (bh * bw <= 128 rows of the MMA) x BN output
+// channels; the K loop runs over 27 taps x Cin/64 channel chunks (64 bf16 = one 128-byte swizzled row).
+// Same warp roles, 4-stage ring and double-buffered TMEM accumulators as the W8A8 GEMM.
+// The epilogue also emits per-tile partial sums (sum, sum of squares of the rounded outputs) per
+// GroupNorm group, so the statistics of the next GroupNorm cost no extra pass over the activations.
+//
+// No counterpart exists in the reference repository (its VAE fast path is a transformer decoder,
+// custom_nodes/rapid_h3/vae_fast.py:430-437); the CPU oracle (oracle/vae.py) defines the arithmetic.
+// Tensor-core bound: 2 * sites * Cout * Cin * 27 operations per call.
+#include "common.cuh"
+#include "rapidh3_b200.h"
+
+namespace rh3 {
+namespace {
+
+constexpr int CBM = 128;        // MMA rows (output sites per tile, bh * bw of them used)
+constexpr int CBK = 64;         // channels per K chunk (128 bytes of bf16)
+constexpr int CSTAGES = 4;
+constexpr int CA_BYTES = CBM * 128;
+constexpr int CB_BYTES = 256 * 128;
+constexpr int CSTAGE_BYTES = CA_BYTES + CB_BYTES;
+constexpr int CONV_THREADS = 192;
+constexpr int GN_GROUPS = 32;
+
+struct ConvParams {
+  int N, T, H, W, Cin, Cout;
+  int bh, bw;          // tile of output sites inside a frame
+  int tiles_h, tiles_w;
+  int BN;              // output channels per tile (multiple of 16, <= 256)
+  const __nv_bfloat16* bias;      // [Cout] or null
+  const __nv_bfloat16* residual;  // [N,T,H,W,Cout] or null
+  __nv_bfloat16* out;
+  float* gn_part;      // [num_m_tiles * 4][32][2] partial (sum, sumsq) per GroupNorm group, or null
+  int* status;
+};
+
+struct __align__(8) ConvSmemTail {
+  uint64_t full[CSTAGES];
+  uint64_t empty[CSTAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float bias[256];
+};
+
+constexpr int CONV_SMEM_BYTES = CSTAGES * CSTAGE_BYTES + sizeof(ConvSmemTail) + 1024;
+
+struct TileCoord {
+  int n, t, h0, w0, n_blk;
+};
+
+__device__ __forceinline__ TileCoord conv_tile(int tile, const ConvParams& p, int num_n) {
+  // column tiles fastest: the CTAs running together share the same input boxes through L2
+  TileCoord c;
+  c.n_blk = tile % num_n;
+  int m = tile / num_n;
+  c.w0 = (m % p.tiles_w) * p.bw;
+  m /= p.tiles_w;
+  c.h0 = (m % p.tiles_h) * p.bh;
+  m /= p.tiles_h;
+  c.t = m % p.T;
+  c.n = m / p.T;
+  return c;
+}
+
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
+              const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  ConvSmemTail* tail = reinterpret_cast<ConvSmemTail*>(smem + CSTAGES * CSTAGE_BYTES);
+  volatile int* abort_flag = &tail->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_n = (p.Cout + p.BN - 1) / p.BN;
+  const int num_m = p.N * p.T * p.tiles_h * p.tiles_w;
+  const int num_tiles = num_m * num_n;
+  const int chunks = p.Cin / CBK;
+  const int num_kb = 27 * chunks;
+  const uint32_t a_bytes = static_cast<uint32_t>(p.bh * p.bw) * 128u;
+  const uint32_t b_bytes = static_cast<uint32_t>(p.BN) * 128u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < CSTAGES; ++s) {
+      mbar_init(&tail->full[s], 1);
+      mbar_init(&tail->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail->acc_full[b], 1);
+      mbar_init(&tail->acc_empty[b], 128);
+    }
+    tail->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_x);
+      tma_prefetch_desc(&tma_w);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileCoord c = conv_tile(tile, p, num_n);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const int tap = kb / chunks, cc = kb - tap * chunks;
+          const int dt = tap / 9, dh = (tap / 3) % 3, dw = tap % 3;
+          if (!mbar_wait(&tail->empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * CSTAGE_BYTES;
+          mbar_arrive_expect_tx(&tail->full[stage], a_bytes + b_bytes);
+          // out-of-range coordinates (negative or past the edge) read zeros: spatial and causal padding
+          tma_load_5d(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2, c.n, &tail->full[stage]);
+          tma_load_2d(sa + CA_BYTES, &tma_w, tap * p.Cin + cc * CBK, c.n_blk * p.BN, &tail->full[stage]);
+          if (++stage == CSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(1, 1, 1, CBM, p.BN);  // f32 += bf16 * bf16
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * CSTAGE_BYTES);
+          const uint32_t b_addr = a_addr + CA_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // 16 bf16 (32 bytes) per MMA along K
+            mma_f16_ss(d_tmem, make_desc_k128(a_addr + k * 32), make_desc_k128(b_addr + k * 32), idesc, (kb | k) != 0);
+          mma_commit(&tail->empty[stage]);
+          if (++stage == CSTAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&tail->acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ------------------------------
+    const int quad = warp & 3;
+    const int et = threadIdx.x - 64;
+    const int gs = p.Cout / GN_GROUPS;  // channels per GroupNorm group (used only when gn_part != null)
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const TileCoord c = conv_tile(tile, p, num_n);
+      const int n0 = c.n_blk * p.BN;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int i = et; i < p.BN; i += 128)
+        tail->bias[i] = (p.bias && n0 + i < p.Cout) ? __bfloat162float(p.bias[n0 + i]) : 0.f;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) break;
+      tc_fence_after();
+      const int m = quad * 32 + lane;
+      const int hh = m / p.bw, ww = m - hh * p.bw;
+      const int h = c.h0 + hh, w = c.w0 + ww;
+      const bool row_ok = m < p.bh * p.bw && h < p.H && w < p.W;
+      const int64_t site = ((static_cast<int64_t>(c.n) * p.T + c.t) * p.H + h) * p.W + w;
+      const uint32_t t_row = tmem_base + acc * 256 + (static_cast<uint32_t>(quad * 32) << 16);
+      const int m_tile = tile / num_n;
+      float* part = p.gn_part ? p.gn_part + (static_cast<int64_t>(m_tile) * 4 + quad) * GN_GROUPS * 2 : nullptr;
+#pragma unroll 1
+      for (int cb = 0; cb < p.BN; cb += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_row + cb, r);
+        tmem_ld_wait_regs(r);
+        const int col0 = n0 + cb;
+        float y[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(r[j]) + tail->bias[cb + j];
+        if (p.residual && row_ok) {
+          const __nv_bfloat16* rs = p.residual + site * p.Cout + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 + 8 <= p.Cout) {
+              const uint4 v = *reinterpret_cast<const uint4*>(rs + g * 8);
+              const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                y[g * 8 + 2 * j] += bf16_lo(vw[j]);
+                y[g * 8 + 2 * j + 1] += bf16_hi(vw[j]);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = row_ok ? bf16_round(y[j]) : 0.f;  // what is stored; rows off the edge add 0
+        if (row_ok) {
+          __nv_bfloat16* o = p.out + site * p.Cout + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 + 8 <= p.Cout) {
+              *reinterpret_cast<uint4*>(o + g * 8) =
+                  make_uint4(pack_bf16x2(y[g * 8], y[g * 8 + 1]), pack_bf16x2(y[g * 8 + 2], y[g * 8 + 3]),
+                             pack_bf16x2(y[g * 8 + 4], y[g * 8 + 5]), pack_bf16x2(y[g * 8 + 6], y[g * 8 + 7]));
+            }
+          }
+        }
+        if (part) {
+          // GroupNorm partials of this warp's 32 rows: channels of a group are summed per row, rows by shuffle
+          for (int j0 = 0; j0 < 32; j0 += gs) {
+            float s1 = 0.f, s2 = 0.f;
+            for (int j = j0; j < j0 + gs && j < 32; ++j) {
+              s1 += y[j];
+              s2 += y[j] * y[j];
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+              s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+              s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+            }
+            const int grp = (col0 + j0) / gs;
+            if (lane == 0 && col0 + j0 < p.Cout) {
+              part[grp * 2] = s1;
+              part[grp * 2 + 1] = s2;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tail->acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// GroupNorm statistics from the convolution's partials, GroupNorm + SiLU, causal 2x upsampling
+// ---------------------------------------------------------------------------------------------
+// sums[n][g] = (sum, sum of squares) over all row blocks of sample n, added in a fixed order in fp64.
+__global__ void __launch_bounds__(256) gn_reduce_kernel(const float* __restrict__ part, int64_t rows_per_sample,
+                                                        double* __restrict__ sums) {
+  __shared__ double red[2][256];
+  const int n = blockIdx.x / GN_GROUPS, g = blockIdx.x % GN_GROUPS;
+  const float* p = part + (static_cast<int64_t>(n) * rows_per_sample * GN_GROUPS + g) * 2;
+  double s1 = 0.0, s2 = 0.0;
+  for (int64_t r = threadIdx.x; r < rows_per_sample; r += 256) {
+    s1 += p[r * GN_GROUPS * 2];
+    s2 += p[r * GN_GROUPS * 2 + 1];
+  }
+  red[0][threadIdx.x] = s1;
+  red[1][threadIdx.x] = s2;
+  __syncthreads();
+  for (int o = 128; o; o >>= 1) {
+    if (threadIdx.x < o) {
+      red[0][threadIdx.x] += red[0][threadIdx.x + o];
+      red[1][threadIdx.x] += red[1][threadIdx.x + o];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    sums[blockIdx.x * 2] = red[0][0];
+    sums[blockIdx.x * 2 + 1] = red[1][0];
+  }
+}
+
+// y = silu((x - mean[g]) * rstd[g] * gamma[c] + beta[c]); 8 channels per thread.
+__global__ void __launch_bounds__(256) gn_silu_kernel(const __nv_bfloat16* __restrict__ x,
+                                                      const float* __restrict__ mean_rstd,  // [N][32][2]
+                                                      const __nv_bfloat16* __restrict__ gamma,
+                                                      const __nv_bfloat16* __restrict__ beta, int64_t sites_per_sample,
+                                                      int C, int64_t total_vec, __nv_bfloat16* __restrict__ y) {
+  const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (v >= total_vec) return;
+  const int vec_per_site = C >> 3;
+  const int64_t site = v / vec_per_site;
+  const int c0 = static_cast<int>(v - site * vec_per_site) << 3;
+  const int n = static_cast<int>(site / sites_per_sample);
+  const int gs = C / GN_GROUPS;
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + site * C + c0));
+  const uint4 gr = __ldg(reinterpret_cast<const uint4*>(gamma + c0));
+  const uint4 br = __ldg(reinterpret_cast<const uint4*>(beta + c0));
+  const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w}, bw[4] = {br.x, br.y, br.z, br.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float r[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int c = c0 + 2 * j + e;
+      const float2 mr = *reinterpret_cast<const float2*>(mean_rstd + (static_cast<int64_t>(n) * GN_GROUPS + c / gs) * 2);
+      const float xv = e ? bf16_hi(xw[j]) : bf16_lo(xw[j]);
+      const float gv = e ? bf16_hi(gw[j]) : bf16_lo(gw[j]);
+      const float bv = e ? bf16_hi(bw[j]) : bf16_lo(bw[j]);
+      const float t = (xv - mr.x) * mr.y * gv + bv;
+      r[e] = t / (1.f + __expf(-t));
+    }
+    o[j] = pack_bf16x2(r[0], r[1]);
+  }
+  *reinterpret_cast<uint4*>(y + site * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// out[n, u, yy, xx, :] = in[n, (u + 1) / 2, yy / 2, xx / 2, :]: nearest 2x in space, causal 2x in time
+// (the first frame is not repeated: T frames become 2T - 1).
+__global__ void __launch_bounds__(256) upsample_kernel(const __nv_bfloat16* __restrict__ x, int T, int H, int W, int C,
+                                                       int64_t total_vec, __nv_bfloat16* __restrict__ y) {
+  const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (v >= total_vec) return;
+  const int vec_per_site = C >> 3;
+  int64_t s = v / vec_per_site;
+  const int c0 = static_cast<int>(v - s * vec_per_site) << 3;
+  const int T2 = 2 * T - 1, H2 = 2 * H, W2 = 2 * W;
+  const int xx = static_cast<int>(s % W2);
+  s /= W2;
+  const int yy = static_cast<int>(s % H2);
+  s /= H2;
+  const int u = static_cast<int>(s % T2);
+  const int64_t n = s / T2;
+  const int64_t src = ((n * T + (u + 1) / 2) * H + yy / 2) * W + xx / 2;
+  *reinterpret_cast<uint4*>(y + (v / vec_per_site) * C + c0) = __ldg(reinterpret_cast<const uint4*>(x + src * C + c0));
+}
+
+// tile of output sites inside a frame: bh * bw <= 128, chosen to waste as few MMA rows as possible
+void choose_tile(int H, int W, int* bh, int* bw) {
+  double best = -1.0;
+  for (int w = 1; w <= 128 && w <= 256; ++w) {
+    const int h = 128 / w;
+    if (h < 1) break;
+    const int hh = h < H ? h : H, ww = w < W ? w : W;
+    const double eff = static_cast<double>(H) * W / (static_cast<double>((H + hh - 1) / hh) * ((W + ww - 1) / ww) * 128.0);
+    if (eff > best + 1e-9) {
+      best = eff;
+      *bh = hh;
+      *bw = ww;
+    }
+  }
+}
+
+bool a16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace rh3
+
+using namespace rh3;
+
+extern "C" int64_t rh3_conv3d_gn_part_rows(int64_t N, int64_t T, int64_t H, int64_t W) {
+  int bh = 1, bw = 1;
+  choose_tile((int)H, (int)W, &bh, &bw);
+  return N * T * ((H + bh - 1) / bh) * ((W + bw - 1) / bw) * 4;
+}
+
+extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias, const void* residual, void* out,
+                                 float* gn_part, int64_t N, int64_t T, int64_t H, int64_t W, int64_t Cin,
+                                 int64_t Cout, cudaStream_t stream) {
+  RH3_CHECK_ARG(N > 0 && T > 0 && H > 0 && W > 0 && N * T * H * W < (1ll << 31), "conv3d_causal: bad shape");
+  RH3_CHECK_ARG(Cin > 0 && Cin % 64 == 0, "conv3d_causal: Cin=%lld must be a multiple of 64", (long long)Cin);
+  RH3_CHECK_ARG(Cout > 0 && Cout % 16 == 0, "conv3d_causal: Cout=%lld must be a multiple of 16", (long long)Cout);
+  RH3_CHECK_ARG(!gn_part || (Cout % GN_GROUPS == 0 && 32 % (Cout / GN_GROUPS) == 0),
+                "conv3d_causal: GroupNorm partials need Cout/32 in {1,2,4,8,16,32}");
+  RH3_CHECK_ARG(x && w && out && a16(x) && a16(w) && a16(out) && (!residual || a16(residual)),
+                "conv3d_causal: null or misaligned pointer");
+  ConvParams p{};
+  p.N = (int)N; p.T = (int)T; p.H = (int)H; p.W = (int)W; p.Cin = (int)Cin; p.Cout = (int)Cout;
+  choose_tile(p.H, p.W, &p.bh, &p.bw);
+  p.tiles_h = (p.H + p.bh - 1) / p.bh;
+  p.tiles_w = (p.W + p.bw - 1) / p.bw;
+  // output channels per tile: the whole width when it fits one accumulator, else an even split
+  const int splits = (p.Cout + 255) / 256;
+  p.BN = ((p.Cout + splits - 1) / splits + 15) / 16 * 16;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.gn_part = gn_part;
+  p.status = device_status_word();
+  CUtensorMap tx, tw;
+  const uint64_t dims[5] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, (uint64_t)T, (uint64_t)N};
+  const uint64_t strides[4] = {(uint64_t)Cin * 2, (uint64_t)W * Cin * 2, (uint64_t)H * W * Cin * 2,
+                               (uint64_t)T * H * W * Cin * 2};
+  const uint32_t box[5] = {CBK, (uint32_t)p.bw, (uint32_t)p.bh, 1, 1};
+  if (int e = make_tmap_nd(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, 5, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+    return e;
+  if (int e = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, 27 * Cin, Cout, 27 * Cin * 2, CBK, p.BN,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return e;
+  if (int e = check_cuda(cudaFuncSetAttribute(conv3d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              CONV_SMEM_BYTES),
+                         "conv3d smem attribute"))
+    return e;
+  const int64_t tiles = N * T * p.tiles_h * p.tiles_w * ((Cout + p.BN - 1) / p.BN);
+  const int grid = tiles < device_sm_count() ? (int)tiles : device_sm_count();
+  conv3d_kernel<<<grid, CONV_THREADS, CONV_SMEM_BYTES, stream>>>(tx, tw, p);
+  return check_cuda(cudaGetLastError(), "conv3d_causal launch");
+}
+
+extern "C" int rh3_gn_reduce(const float* gn_part, int64_t rows_per_sample, int64_t N, double* sums,
+                             cudaStream_t stream) {
+  RH3_CHECK_ARG(gn_part && sums && rows_per_sample > 0 && N > 0 && N * GN_GROUPS < (1ll << 31), "gn_reduce: bad argument");
+  gn_reduce_kernel<<<static_cast<unsigned>(N * GN_GROUPS), 256, 0, stream>>>(gn_part, rows_per_sample, sums);
+  return check_cuda(cudaGetLastError(), "gn_reduce launch");
+}
+
+extern "C" int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const void* gamma, const void* beta, int64_t N,
+                                 int64_t sites_per_sample, int64_t C, void* y, cudaStream_t stream) {
+  RH3_CHECK_ARG(x && mean_rstd && gamma && beta && y && a16(x) && a16(y) && a16(gamma) && a16(beta),
+                "gn_silu_apply: null or misaligned pointer");
+  RH3_CHECK_ARG(N > 0 && sites_per_sample > 0 && C > 0 && C % 8 == 0 && C % GN_GROUPS == 0, "gn_silu_apply: bad shape");
+  const int64_t total_vec = N * sites_per_sample * (C / 8);
+  RH3_CHECK_ARG((total_vec + 255) / 256 < (1ll << 31), "gn_silu_apply: tensor too large");
+  gn_silu_kernel<<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), mean_rstd, static_cast<const __nv_bfloat16*>(gamma),
+      static_cast<const __nv_bfloat16*>(beta), sites_per_sample, (int)C, total_vec, static_cast<__nv_bfloat16*>(y));
+  return check_cuda(cudaGetLastError(), "gn_silu_apply launch");
+}
+
+extern "C" int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t T, int64_t H, int64_t W, int64_t C,
+                                     cudaStream_t stream) {
+  RH3_CHECK_ARG(x && y && a16(x) && a16(y) && N > 0 && T > 0 && H > 0 && W > 0 && C > 0 && C % 8 == 0,
+                "upsample_causal2x: bad argument");
+  const int64_t total_vec = N * (2 * T - 1) * 2 * H * 2 * W * (C / 8);
+  RH3_CHECK_ARG((total_vec + 255) / 256 < (1ll << 31), "upsample_causal2x: tensor too large");
+  upsample_kernel<<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), (int)T, (int)H, (int)W, (int)C, total_vec, static_cast<__nv_bfloat16*>(y));
+  return check_cuda(cudaGetLastError(), "upsample_causal2x launch");
+}

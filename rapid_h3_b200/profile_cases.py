@@ -30,7 +30,7 @@ def _time(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["attn", "gemm", "quant", "prepass"])
+    ap.add_argument("case", choices=["attn", "gemm", "quant", "prepass", "conv", "vae"])
     ap.add_argument("--L", type=int, default=16384)
     ap.add_argument("--H", type=int, default=8)
     ap.add_argument("--M", type=int, default=8192)
@@ -38,6 +38,11 @@ def main():
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--epi", default="plain")
     ap.add_argument("--kind", default="plain")
+    ap.add_argument("--T", type=int, default=36)
+    ap.add_argument("--HH", type=int, default=24)
+    ap.add_argument("--WW", type=int, default=42)
+    ap.add_argument("--Cin", type=int, default=512)
+    ap.add_argument("--Cout", type=int, default=512)
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -45,6 +50,21 @@ def main():
     def randn(*shape):
         return torch.randn(*shape, device="cuda", generator=g)
 
+    if a.case == "conv":
+        from . import vae
+        x = randn(1, a.T, a.HH, a.WW, a.Cin).to(torch.bfloat16)
+        w = (0.02 * randn(a.Cout, 27, a.Cin)).to(torch.bfloat16)
+        ms = _time(lambda: vae.conv3d_causal(x, w, want_stats=a.Cout % 32 == 0), a.iters)
+        fl = 2.0 * a.T * a.HH * a.WW * a.Cin * a.Cout * 27
+        print(f"conv3d {a.T}x{a.HH}x{a.WW} {a.Cin}->{a.Cout}: {ms:.3f} ms, {fl / ms / 1e9:.1f} TFLOP/s")
+        return
+    if a.case == "vae":
+        from . import vae
+        dec = vae.VAEDecoder(seed=0)
+        latent = randn(1, 16, a.T, a.HH, a.WW).to(torch.bfloat16)
+        ms = _time(lambda: dec.decode(latent), a.iters)
+        print(f"vae decode latent 16x{a.T}x{a.HH}x{a.WW}: {ms:.2f} ms, {dec.flops(a.T, a.HH, a.WW) / ms / 1e9:.1f} TFLOP/s")
+        return
     if a.case in ("attn", "prepass"):
         q = randn(a.L, a.H, 128).to(torch.bfloat16)
         k = (randn(a.L, a.H, 128) + 2 * randn(1, a.H, 128)).to(torch.bfloat16)

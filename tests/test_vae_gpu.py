@@ -1,0 +1,84 @@
+"""The conv3d implicit-GEMM kernel, GroupNorm + SiLU, upsampling and the whole decoder against the CPU
+oracle (oracle/vae.py; the reference has no convolutional decoder, so the oracle defines the contract).
+bf16 outputs: rel-L2 <= 1e-3 per op (fp32 accumulation order differs between the tensor core and the CPU)."""
+import pytest
+import torch
+
+from oracle import vae as ov
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-20)).item()
+
+
+@pytest.fixture(scope="module")
+def vae():
+    from rapid_h3_b200 import _lib, vae
+    assert torch.cuda.is_available()
+    return vae, _lib
+
+
+@pytest.mark.parametrize("shape", [(1, 3, 6, 21, 64, 64), (2, 4, 9, 10, 128, 256), (1, 2, 24, 42, 64, 512),
+                                   (1, 5, 7, 5, 192, 192), (1, 1, 1, 1, 64, 16)])
+def test_conv3d_causal_matches_oracle(vae, shape):
+    v, lib = vae
+    n, t, h, w, cin, cout = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(n, t, h, w, cin, generator=g).to(torch.bfloat16)
+    wt = (0.05 * torch.randn(cout, 27, cin, generator=g)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(cout, generator=g)).to(torch.bfloat16)
+    res = torch.randn(n, t, h, w, cout, generator=g).to(torch.bfloat16)
+    stats = cout % 32 == 0 and 32 % (cout // 32) == 0
+    y, part = v.conv3d_causal(x.cuda(), wt.cuda(), b.cuda(), res.cuda(), want_stats=stats)
+    lib.check_status()
+    ref = ov.conv3d_causal(x, wt, b, res)
+    assert rel_l2(y.cpu(), ref) <= 1e-3
+    y2, _ = v.conv3d_causal(x.cuda(), wt.cuda())
+    assert rel_l2(y2.cpu(), ov.conv3d_causal(x, wt)) <= 1e-3
+    if stats:
+        sums = v.gn_sums(part, n).cpu()
+        yd = y.cpu().double().reshape(n, -1, 32, cout // 32)
+        assert torch.allclose(sums[..., 0], yd.sum(dim=(1, 3)), rtol=1e-5, atol=1e-2)
+        assert torch.allclose(sums[..., 1], (yd * yd).sum(dim=(1, 3)), rtol=1e-5)
+
+
+def test_causality(vae):
+    """Changing frame t must leave every output frame before t untouched."""
+    v, lib = vae
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(1, 6, 8, 8, 64, generator=g).to(torch.bfloat16).cuda()
+    wt = (0.05 * torch.randn(64, 27, 64, generator=g)).to(torch.bfloat16).cuda()
+    y, _ = v.conv3d_causal(x, wt)
+    x2 = x.clone()
+    x2[:, 4] += 1
+    y2, _ = v.conv3d_causal(x2, wt)
+    assert torch.equal(y[:, :4], y2[:, :4]) and not torch.equal(y[:, 4], y2[:, 4])
+
+
+def test_gn_silu_and_upsample(vae):
+    v, lib = vae
+    g = torch.Generator().manual_seed(4)
+    x = (torch.randn(2, 3, 5, 7, 128, generator=g) * 2 + 0.5).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(128, generator=g)).to(torch.bfloat16)
+    beta = (0.1 * torch.randn(128, generator=g)).to(torch.bfloat16)
+    xd = x.cuda()
+    y = v.gn_silu(xd, v.gn_sums_from_tensor(xd), x.numel() // (2 * 32), gamma.cuda(), beta.cuda())
+    assert rel_l2(y.cpu(), ov.gn_silu(x, gamma, beta)) <= 2e-3
+    assert torch.equal(v.upsample(xd).cpu(), ov.upsample(x))
+
+
+def test_decoder_matches_oracle(vae):
+    v, lib = vae
+    dec = v.VAEDecoder(seed=1, widths=(128, 64, 64), blocks_per_stage=1)
+    g = torch.Generator().manual_seed(5)
+    latent = torch.randn(1, 16, 3, 3, 4, generator=g).to(torch.bfloat16)
+    rgb = dec.decode(latent.cuda())
+    lib.check_status()
+    assert rgb.shape == (1, 3, 9, 96, 128)
+    ref = ov.decode(dec.cpu, latent, widths=(128, 64, 64), blocks=1)
+    # every layer rounds to bf16 (2^-9 relative); rounding flips compound over the 9 layers, so the whole
+    # decoder is compared at a few bf16 ulps while each op alone is held to 1e-3 above
+    assert rel_l2(rgb.cpu(), ref) <= 2e-2
