@@ -73,17 +73,10 @@ __device__ __forceinline__ float block_sum_fixed(float v, float* red) {
   return r;
 }
 
-template <int KIND, int OUT_FP8, int T, int CPT>
-__global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
-  __shared__ float red[T / 32];
-  const int64_t row = blockIdx.x;
-  const int tid = threadIdx.x;
-  const int nchunk = static_cast<int>(p.K >> 3);
-
-  float v[CPT][8];
-  // ---- load (all loads issued before any use) ----
-  uint4 raw[CPT];
-  uint4 raw2[KIND == KIND_SWIGLU ? CPT : 1];
+// Issue the 128-bit loads of one row (CPT chunks per thread); nothing waits on them here.
+template <int KIND, int T, int CPT>
+__device__ __forceinline__ void load_row(const QuantParams& p, int64_t row, int tid, int nchunk, uint4* raw,
+                                         uint4* raw2) {
 #pragma unroll
   for (int i = 0; i < CPT; ++i) {
     const int c = tid + i * T;
@@ -102,6 +95,21 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
       if (KIND == KIND_SWIGLU) raw2[i] = __ldg(reinterpret_cast<const uint4*>(src + p.K));
     }
   }
+}
+
+// One CTA of T threads works on rows blockIdx.x, blockIdx.x + gridDim.x, ...; the loads of the next row
+// are issued before the current row is reduced and stored, so every CTA always has a row in flight.
+template <int KIND, int OUT_FP8, int T, int CPT>
+__global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
+  __shared__ float red[T / 32];
+  const int tid = threadIdx.x;
+  const int nchunk = static_cast<int>(p.K >> 3);
+  uint4 raw[CPT];
+  uint4 raw2[KIND == KIND_SWIGLU ? CPT : 1];
+  int64_t row = blockIdx.x;
+  if (row < p.M) load_row<KIND, T, CPT>(p, row, tid, nchunk, raw, raw2);
+  for (; row < p.M; row += gridDim.x) {
+  float v[CPT][8];
 #pragma unroll
   for (int i = 0; i < CPT; ++i) unpack8(raw[i], v[i]);
 
@@ -118,6 +126,8 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
       }
     }
   }
+  // the registers of `raw` are free again: start fetching the next row of this CTA
+  if (row + gridDim.x < p.M) load_row<KIND, T, CPT>(p, row + gridDim.x, tid, nchunk, raw, raw2);
 
   if (KIND == KIND_NORMMOD) {
     // sum of squares in a fixed order (thread-sequential over its chunks, then the block tree)
@@ -187,14 +197,22 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
       *reinterpret_cast<uint2*>(qrow + (static_cast<int64_t>(c) << 3)) = make_uint2(o[0], o[1]);
     }
   }
+  }  // rows of this CTA
 }
 
 template <int KIND, int OUT_FP8>
 int launch_quant(const QuantParams& p, cudaStream_t stream) {
   const int64_t nchunk = p.K >> 3;
   if (p.M == 0) return 0;
+  // as many CTAs as are resident at once (a multiple of the SM count), each looping over its rows
 #define RH3_Q(T_, CPT_)                                                                                \
-  quant_rows_kernel<KIND, OUT_FP8, T_, CPT_><<<static_cast<unsigned>(p.M), T_, 0, stream>>>(p)
+  do {                                                                                                 \
+    auto kern = quant_rows_kernel<KIND, OUT_FP8, T_, CPT_>;                                            \
+    int occ = 1;                                                                                       \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, T_, 0) != cudaSuccess || occ < 1) occ = 1; \
+    const int64_t resident = static_cast<int64_t>(device_sm_count()) * occ;                           \
+    kern<<<static_cast<unsigned>(p.M < resident ? p.M : resident), T_, 0, stream>>>(p);               \
+  } while (0)
   if (nchunk <= 128) RH3_Q(128, 1);
   else if (nchunk <= 256) RH3_Q(128, 2);
   else if (nchunk <= 512) RH3_Q(128, 4);
