@@ -175,8 +175,8 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     }
     for (int g = 0; g < QG; ++g) {
       mbar_init(&tail->s_full[g], 1);
-      mbar_init(&tail->s_empty[g], 128);
-      mbar_init(&tail->p_full[g], 128);
+      mbar_init(&tail->s_empty[g], 4);  // one arrival per softmax warp (128 separate arrivals on one
+      mbar_init(&tail->p_full[g], 4);   // barrier word serialise and cost more than the MMAs they gate)
       mbar_init(&tail->pv_done[g], 1);
     }
     tail->abort_flag = 0;
@@ -219,9 +219,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       auto issue_qk = [&](int g, int j) {
         const uint32_t q_addr = smem_u32(sQ + g * TILE_BYTES);
         const uint32_t k_addr = smem_u32(sKV + (j % KV_STAGES) * 2 * TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr + k * 32), make_desc_k128(k_addr + k * 32), idesc_qk, 1);
+        mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 1);
         mma_commit(&tail->s_full[g]);
       };
       bool ok = mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
@@ -253,10 +251,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
           if (!ok) break;
           tc_fence_after();
           const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr + k * 32), make_desc_k128(v_addr + k * 32),
-                      idesc_pv, (j | k) != 0);
+          mma4_f8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, j != 0);
           mma_commit(&tail->pv_done[g]);
         }
         if (ok) mma_commit(&tail->kv_empty[stage]);  // both query tiles have read this K / V^T stage
@@ -294,7 +289,8 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     tmem_st32_splat(t_row + 96, kMagicBits);
     tmem_st_wait();
     tc_fence_before();
-    mbar_arrive(s_empty);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(s_empty);
     float ks0 = ks_h[0], ks1 = ks_h[1];  // block scales of the tile ahead are fetched one tile early
 
     for (int j = 0; j < n_kv; ++j) {
@@ -324,7 +320,8 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       tmem_st32_splat(t_row + 96, kMagicBits);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(s_empty);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty);
       if (valid != BKV) {
         mask_tail(r0, 0, valid);
         mask_tail(r1, 32, valid);
@@ -367,7 +364,8 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       l += la + lb;
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
     }
     // ---- epilogue ----
     if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) {

@@ -170,6 +170,39 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+
+// Four MMAs over one 128-byte K slab (4 x 32 bytes) in a single instruction sequence: the issuing thread
+// is one lane, so every scalar instruction between two MMAs costs tensor-pipe time. The descriptors of
+// the K steps differ only by +2 in the 16-byte start-address field, so the whole slab costs six adds.
+// `acc_first` = 0 makes the first MMA overwrite D; the other three always accumulate.
+#define RH3_DEFINE_MMA4(NAME, KIND)                                                                            \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,       \
+                                       uint32_t acc_first) {                                                    \
+    asm volatile(                                                                                              \
+        "{\n\t"                                                                                                \
+        ".reg .pred p, q;\n\t"                                                                                 \
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                                                                \
+        "setp.ne.b32 p, %4, 0;\n\t"                                                                            \
+        "setp.eq.b32 q, 0, 0;\n\t"                                                                             \
+        "add.u64 a1, %1, 2;\n\t"                                                                               \
+        "add.u64 b1, %2, 2;\n\t"                                                                               \
+        "add.u64 a2, %1, 4;\n\t"                                                                               \
+        "add.u64 b2, %2, 4;\n\t"                                                                               \
+        "add.u64 a3, %1, 6;\n\t"                                                                               \
+        "add.u64 b3, %2, 6;\n\t"                                                                               \
+        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], %1, %2, %3, p;\n\t"                                     \
+        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], a1, b1, %3, q;\n\t"                                     \
+        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], a2, b2, %3, q;\n\t"                                     \
+        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], a3, b3, %3, q;\n\t"                                     \
+        "}\n" ::"r"(d_tmem),                                                                                   \
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc_first)                                                   \
+        : "memory");                                                                                           \
+  }
+RH3_DEFINE_MMA4(mma4_i8_ss, "i8")
+RH3_DEFINE_MMA4(mma4_f8_ss, "f8f6f4")
+RH3_DEFINE_MMA4(mma4_f16_ss, "f16")
+#undef RH3_DEFINE_MMA4
+
 // all previously issued MMAs of this thread arrive on `bar` when they retire
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

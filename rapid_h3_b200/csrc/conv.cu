@@ -98,7 +98,7 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->acc_full[b], 1);
-      mbar_init(&tail->acc_empty[b], 128);
+      mbar_init(&tail->acc_empty[b], 4);  // one arrival per epilogue warp
     }
     tail->abort_flag = 0;
     fence_barrier_init();
@@ -159,9 +159,8 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * CSTAGE_BYTES);
           const uint32_t b_addr = a_addr + CA_BYTES;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // 16 bf16 (32 bytes) per MMA along K
-            mma_f16_ss(d_tmem, make_desc_k128(a_addr + k * 32), make_desc_k128(b_addr + k * 32), idesc, (kb | k) != 0);
+          // four MMAs of 16 bf16 (32 bytes) each along K
+          mma4_f16_ss(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
           mma_commit(&tail->empty[stage]);
           if (++stage == CSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -253,7 +252,8 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive(&tail->acc_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }

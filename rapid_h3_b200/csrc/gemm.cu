@@ -92,7 +92,7 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tail->acc_full[b], 1);
-      mbar_init(&tail->acc_empty[b], 128);
+      mbar_init(&tail->acc_empty[b], 4);  // one arrival per epilogue warp
     }
     tail->abort_flag = 0;
     fence_barrier_init();
@@ -152,13 +152,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / 32; ++k) {
-            const uint64_t adesc = make_desc_k128(a_addr + k * 32);
-            const uint64_t bdesc = make_desc_k128(b_addr + k * 32);
-            if (KIND_F8) mma_f8_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
-            else mma_i8_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
-          }
+          if (KIND_F8) mma4_f8_ss(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
+          else mma4_i8_ss(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
           mma_commit(&tail->empty[stage]);  // the stage is free once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -269,7 +264,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
       tc_fence_before();
-      mbar_arrive(&tail->acc_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tail->acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }
