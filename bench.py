@@ -30,6 +30,7 @@ WORKLOADS = {
     "draft": ((36, 17, 29), 148, 2, 512, 48),
     "block": ((36, 24, 42), 148, 1, 512, 1),
 }
+VAE_LATENT = (16, 36, 24, 42)  # -> RGB 3 x 141 x 768 x 1344
 
 
 def peaks():
@@ -150,8 +151,41 @@ def cpu_baseline_record(workload):
                        "scaled linearly to all rows, heads, blocks and the CFG batch")}
 
 
+def vae_cpu_seconds():
+    """CPU port of the VAE decode (oracle/vae.py): one 512 -> 512 causal conv on a 3 x 24 x 42 slab, scaled by the
+    decoder's operation count (convolutions are >95 % of the decode)."""
+    from oracle import vae as ov
+    from rapid_h3_b200 import vae
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 3, 24, 42, 512, generator=g).to(torch.bfloat16)
+    w = (0.02 * torch.randn(512, 27, 512, generator=g)).to(torch.bfloat16)
+    ov.conv3d_causal(x[:, :1], w)
+    t0 = time.perf_counter()
+    ov.conv3d_causal(x, w)
+    dt = time.perf_counter() - t0
+    dec = vae.VAEDecoder.__new__(vae.VAEDecoder)
+    dec.widths, dec.blocks = (512, 256, 128), 2
+    return dt * dec.flops(*VAE_LATENT[1:]) / (2.0 * 3 * 24 * 42 * 512 * 512 * 27), dt
+
+
 def run_reference(args, rank):
     if rank != 0:
+        return
+    if args.workload == "vae":
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        vals = [vae_cpu_seconds() for _ in range(max(args.steps, 1))]
+        val = statistics.median(v for v, _ in vals)
+        sample = (f"one 512->512 causal conv3d on a 3x24x42 slab ({vals[0][1]:.1f} s of CPU work per step), scaled by "
+                  "the decoder's operation count")
+        print(json.dumps({"impl": "reference", "metric": "VAE decode seconds, latent 16x36x24x42 -> RGB 3x141x768x1344",
+                          "value": val, "unit": "s/decode", "n_gpus": args.gpus, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": val * 1e3, "higher_is_better": False,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+                          "config": {"workload": "vae_conv3d_decode", "latent": list(VAE_LATENT)},
+                          "cpu_baseline": {"value": val, "unit": "s/decode", "cores": cores, "kind": "port", "sample": sample},
+                          "e2e": {"value": val, "unit": "s/decode", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}),
+              flush=True)
         return
     grid, n_audio, batch, text_len, blocks = WORKLOADS[args.workload]
     cores = os.cpu_count() or 1
@@ -184,6 +218,77 @@ def workload_config(name, n):
             "l2": "every step streams >16 GB of weights and activations, far larger than the 126 MB L2"}
 
 
+def run_vae(args, rank, world, local):
+    """VAE decode of the benchmark latent (second workload of the hot path; time-sharded for N > 1)."""
+    import torch.distributed as dist
+    import rapid_h3_b200 as r
+    from rapid_h3_b200 import vae
+    c, t, h, w = VAE_LATENT
+    dec = vae.VAEDecoder(latent_ch=c, seed=0, device=f"cuda:{local}")
+    host = torch.randn(1, c, t, h, w, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).pin_memory()
+    sp = vae.TimeShards(t) if world > 1 else None
+    t0, t1 = (0, t) if sp is None else (sp.t0, sp.t1)
+    dev = host.cuda()[:, :, t0:t1].contiguous()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    out_host = None
+
+    def step_e2e():
+        nonlocal out_host
+        rgb = dec.decode(host[:, :, t0:t1].cuda(non_blocking=True).contiguous(), sp=sp)
+        if out_host is None:
+            out_host = torch.empty(rgb.shape, dtype=rgb.dtype).pin_memory()
+        out_host.copy_(rgb, non_blocking=True)
+
+    def timed(fn, k):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / k], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        dec.decode(dev, sp=sp)
+    sampler = ClockSampler(local)
+    sampler.start()
+    r._lib.launch_count = 0
+    ms = timed(lambda: dec.decode(dev, sp=sp), args.steps)
+    launches = r._lib.launch_count
+    clocks = sampler.stop()
+    step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    r._lib.check_status()
+    pk = peaks()
+    tflop = dec.flops(t, h, w) / 1e12
+    achieved = tflop / (ms / 1e3)
+    rec = {"metric": "VAE decode seconds, latent 16x36x24x42 -> RGB 3x141x768x1344", "value": ms / 1e3,
+           "unit": "s/decode", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+           "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "vae_conv3d_decode", "latent": list(VAE_LATENT), "widths": [512, 256, 128],
+                      "blocks_per_stage": 2, "parallelism": "single GPU" if world == 1 else f"time shards x{world}",
+                      "l2": "activations of 0.6-0.9 GB per layer, far larger than the 126 MB L2"},
+           "clocks": clocks,
+           "e2e": {"value": ms_e2e / 1e3, "unit": "s/decode", "h2d_bytes_per_step": dev.numel() * 2,
+                   "d2h_bytes_per_step": out_host.numel() * 2},
+           "gpu_launches": launches // max(args.steps, 1) * args.steps,
+           "roofline": {"bound": "tensor", "kernel": "conv3d_kernel (whole decode incl. GroupNorm/upsample)",
+                        "achieved": achieved * world, "peak": pk["bf16_tflops_sustained"] * world, "unit": "TFLOP/s",
+                        "frac": achieved / pk["bf16_tflops_sustained"], "traffic": None,
+                        "peak_note": f"{pk['source']} sustained cuBLAS bf16"}}
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+
+
 # ---------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -191,7 +296,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="full", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="full", choices=sorted(WORKLOADS) + ["vae"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -210,6 +315,11 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.workload == "vae":
+        run_vae(args, rank, world, local)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     grid, n_audio, batch, text_len, blocks = WORKLOADS[args.workload]
     cfg = H3Config(n_blocks=blocks)
     rt = r.step.H3Runtime.random(cfg, seed=0, device=f"cuda:{local}")
