@@ -64,6 +64,21 @@ int rh3_norm_mod_quant_rows_i8(const void* x, int64_t ldx, const void* w, float 
                                const float* shift, const float* scale, int64_t ld_tab, int64_t M, int64_t K,
                                void* q, int64_t ldq, float* s, cudaStream_t stream);
 
+/* The same four quantizers with the H256 ConvRot rotation (x . blockdiag(H256)^T over groups of 256 channels,
+ * H256 = Kronecker powers of the regular 4x4 Hadamard matrix / 16) applied before the abs-max: the `int8_rot`
+ * recipe, whose weights are stored as W . blockdiag(H256)^T. The rotated width must be a multiple of 256.
+ * Replace triton_fp8.rot_quant_rows_i8 / swiglu_rot_quant_rows_i8 / rot_quant_heads_i8 /
+ * norm_mod_rot_quant_rows_i8 (custom_nodes/rapid_h3/triton_fp8.py:424-446, rotation :70-112, :151-194). */
+int rh3_rot_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
+                          cudaStream_t stream);
+int rh3_swiglu_rot_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t F, void* q, int64_t ldq, float* s,
+                                 cudaStream_t stream);
+int rh3_rot_quant_groups_i8(const void* o, int64_t stride_g, int64_t G, int64_t gw, int64_t M, void* q, int64_t ldq,
+                            float* s, cudaStream_t stream);
+int rh3_norm_mod_rot_quant_rows_i8(const void* x, int64_t ldx, const void* w, float eps, const int32_t* idx,
+                                   const float* shift, const float* scale, int64_t ld_tab, int64_t M, int64_t K,
+                                   void* q, int64_t ldq, float* s, cudaStream_t stream);
+
 /* ---- W8A8 row-wise-scaled GEMMs (tensor-core bound) ---------------------------------------- */
 /* out[M,N] bf16 = ((acc * xs[m]) * ws[n]) + bias[n]; xq[M,K] (row stride lda), wq[N,K] contiguous.
  * bias may be NULL. acc_dump (optional, [M,N] int32 / fp32 bits) receives the raw accumulators.

@@ -20,7 +20,7 @@ def _qlinear(x, weight):
     return ol.int_mm(xq, wq), xs, ws
 
 
-def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None):
+def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None, mode="int8_rowwise"):
     s, d = x.shape
     a = block.attn
     hd = a.heads * a.head_dim
@@ -30,6 +30,8 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None)
         idx[lo:hi] = int(row)
     tab = rope_freqs.reshape(s, 48, 2, 2)
     x = x.clone()
+    rot = mode == "int8_rot"
+    norm_mod_q = oq.norm_mod_rot_quant_rows_i8 if rot else oq.norm_mod_quant_rows_i8
 
     def rec(name, value):
         if trace is not None:
@@ -42,10 +44,10 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None)
         return x
 
     def q_weight(lin):
-        return ol.quantize_weight(lin.weight.detach(), "int8_rowwise")
+        return ol.quantize_weight(lin.weight.detach(), mode)
 
     # self-attention
-    xq, xs = oq.norm_mod_quant_rows_i8(x, block.norm1.weight.detach(), block.norm1.eps, idx, sh1, sc1)
+    xq, xs = norm_mod_q(x, block.norm1.weight.detach(), block.norm1.eps, idx, sh1, sc1)
     rec("attn_in_q", xq), rec("attn_in_s", xs)
     wq, ws = q_weight(a.qkv_proj)
     qkv = ol.dequant(ol.int_mm(xq, wq), xs, ws)
@@ -56,7 +58,7 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None)
     rec("qkv_rr", torch.cat([q.reshape(s, hd), k.reshape(s, hd), v.reshape(s, hd)], 1))
     o = oa.attention(q, k, v)
     rec("attn_out", o)
-    oq8, os_ = ol.quantize_rows(o.reshape(s, hd), "int8_rowwise")
+    oq8, os_ = ol.quantize_rows(o.reshape(s, hd), mode)
     wq, ws = q_weight(a.out_proj)
     x = gated(ol.int_mm(oq8, wq), os_, ws, g1, x)
     rec("x_attn", x)
@@ -64,11 +66,11 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None)
     if hasattr(block, "cross"):
         c = block.cross
         zeros = torch.zeros(1, d)
-        xq, xs = oq.norm_mod_quant_rows_i8(x, block.norm_c.weight.detach(), block.norm_c.eps,
+        xq, xs = norm_mod_q(x, block.norm_c.weight.detach(), block.norm_c.eps,
                                            torch.zeros(s, dtype=torch.int32), zeros, zeros)
         wq, ws = q_weight(c.q_proj)
         qc = ol.dequant(ol.int_mm(xq, wq), xs, ws).reshape(s, c.heads, c.head_dim)
-        cq8, cs = ol.quantize_rows(ctx, "int8_rowwise")
+        cq8, cs = ol.quantize_rows(ctx, mode)
         wq, ws = q_weight(c.kv_proj)
         kv = ol.dequant(ol.int_mm(cq8, wq), cs, ws)
         kc, vc = (t.reshape(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
@@ -76,17 +78,17 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None)
         kc = oa.rmsnorm_rope(kc, c.k_norm.weight.detach(), c.k_norm.eps, None)
         oc = oa.attention(qc, kc, vc)
         rec("cross_out", oc)
-        oq8, os_ = ol.quantize_rows(oc.reshape(s, hd), "int8_rowwise")
+        oq8, os_ = ol.quantize_rows(oc.reshape(s, hd), mode)
         wq, ws = q_weight(c.out_proj)
         x = ol.gated_residual(ol.int_mm(oq8, wq), os_, ws, torch.ones(d, dtype=torch.bfloat16), x)
         rec("x_cross", x)
 
-    xq, xs = oq.norm_mod_quant_rows_i8(x, block.norm2.weight.detach(), block.norm2.eps, idx, sh2, sc2)
+    xq, xs = norm_mod_q(x, block.norm2.weight.detach(), block.norm2.eps, idx, sh2, sc2)
     wq, ws = q_weight(block.mlp.fc1)
     perm = ol.swiglu_perm(wq.shape[0])
     h = ol.swiglu_epilogue(ol.int_mm(xq, wq[perm]), xs, ws[:, perm])
     rec("mlp_h", h)
-    hq, hs = ol.quantize_rows(h, "int8_rowwise")
+    hq, hs = ol.quantize_rows(h, mode)
     wq, ws = q_weight(block.mlp.fc2)
     x = gated(ol.int_mm(hq, wq), hs, ws, g2, x)
     rec("x_out", x)

@@ -1,7 +1,10 @@
 """Oracle: per-row quantizers and the row-wise-scaled W8A8 linear (TEST INFRASTRUCTURE ONLY).
 
 Follows the reference's PyTorch emulation: custom_nodes/rapid_h3/kernels.py:52-72
-(quantize_weight), :75-82 (quantize_rows), :129-137 (linear), and the fused epilogues of
+(quantize_weight), :75-82 (quantize_rows), :129-137 (linear), the H256 ConvRot rotation of
+custom_nodes/rapid_h3/triton_fp8.py:70-92 (as radix-4 butterflies with a fixed rounding order; the
+reference's own expression is a matrix product whose summation order is not defined, so rotated codes are
+pinned only by a mismatch fraction: parity unpinned for `int8_rot` beyond that), and the fused epilogues of
 custom_nodes/rapid_h3/csrc/fp8_rowwise.cu:294-304 (dequant + bias), :333-336 (gated residual),
 :74-93 (SwiGLU store) with the row order of custom_nodes/rapid_h3/cutlass_fp8.py:55-62.
 """
@@ -9,10 +12,43 @@ import torch
 
 FP8 = torch.float8_e4m3fn
 FP8_MAX = 448.0
+ROT_GROUP = 256
+
+
+def regular_hadamard(n):
+    """Kronecker powers of the regular 4x4 Hadamard matrix, orthonormal (triton_fp8.py:70-82), fp64."""
+    h4 = torch.tensor([[1, 1, 1, -1], [1, 1, -1, 1], [1, -1, 1, 1], [-1, 1, 1, 1]], dtype=torch.float64)
+    h = h4
+    while h.shape[0] < n:
+        h = torch.kron(h, h4)
+    return h / n ** 0.5
+
+
+def convrot_matmul(x):
+    """x @ blockdiag(H256)^T as one fp64 matrix product (the expression of triton_fp8.py:88-92);
+    the yardstick the butterfly below is compared with."""
+    m, k = x.shape
+    return (x.double().reshape(-1, ROT_GROUP) @ regular_hadamard(ROT_GROUP).T).reshape(m, k)
+
+
+def rotate256(y):
+    """fp32 y [M, K] -> y @ blockdiag(H256)^T as four radix-4 stages over the base-4 digits of the
+    channel index inside its group of 256, lowest digit first. A stage maps the four values e0..e3 that
+    differ in that digit to 0.5 * ((e0 + e1) + (e2 + e3)) - e_(3-k): H4 / 2 with every rounding fixed."""
+    m, k = y.shape
+    assert k % ROT_GROUP == 0
+    v = y.float().reshape(m, k // ROT_GROUP, 4, 4, 4, 4)
+    for axis in (5, 4, 3, 2):
+        e = v.unbind(axis)
+        hs = ((e[0] + e[1]) + (e[2] + e[3])) * 0.5
+        v = torch.stack([hs - e[3 - d] for d in range(4)], dim=axis)
+    return v.reshape(m, k)
 
 
 def quantize_rows(x, mode):
     """(q, s[M,1]): kernels.py:75-82. int8: s = max(amax/127, 1e-12), q = clamp(round(x/s), +-127)."""
+    if mode == "int8_rot":  # kernels.py:115-117: rotate, then the int8 row quantizer
+        x, mode = rotate256(x.float()), "int8_rowwise"
     amax = x.abs().amax(dim=-1, keepdim=True).float()
     if mode == "int8_rowwise":
         s = (amax / 127.0).clamp_min(1e-12)
@@ -26,6 +62,8 @@ def quantize_rows(x, mode):
 def quantize_weight(w, mode):
     """(q [N,K], scale [1,N]): kernels.py:52-72, row-wise modes."""
     w = w.float()
+    if mode == "int8_rot":  # kernels.py:58-60: W . blockdiag(H256)^T, then int8 per output row
+        w, mode = rotate256(w), "int8_rowwise"
     if mode == "fp8_rowwise":
         s = (w.abs().amax(dim=1, keepdim=True) / FP8_MAX).clamp_min(1e-12)
         return (w / s).clamp(-FP8_MAX, FP8_MAX).to(FP8), s.t().contiguous()
@@ -63,7 +101,7 @@ def dequant(acc, xs, ws, bias=None):
 def linear(x, wq, ws, mode, bias=None):
     """x bf16 [M,K] through quantize_rows + the W8A8 product + dequant (kernels.py:129-137)."""
     xq, xs = quantize_rows(x, mode)
-    acc = int_mm(xq, wq) if mode == "int8_rowwise" else fp8_mm(xq, wq)
+    acc = int_mm(xq, wq) if mode in ("int8_rowwise", "int8_rot") else fp8_mm(xq, wq)
     return dequant(acc, xs, ws, bias)
 
 

@@ -1,14 +1,15 @@
 """Oracle: fused-prologue row quantizers (TEST INFRASTRUCTURE ONLY).
 
 Follows custom_nodes/rapid_h3/triton_fp8.py:128-148 (`_load_act` prologues) and :165-172 (RMS
-statistics), without the H256 rotation. The reference pins these only by a mismatch fraction
-against an fp32 expression (bench/rot_test.py:42-51), so the summation order of the sum of squares
-is defined here and mirrored by the CUDA kernel: parity unpinned beyond that reference expression.
+statistics), with and without the H256 rotation (:70-112). The reference pins these only by a
+mismatch fraction against an fp32 expression (bench/rot_test.py:42-51), so the summation order of the
+sum of squares and of the rotation butterflies is defined here and mirrored by the CUDA kernel:
+parity unpinned beyond that reference expression.
 """
 import numpy as np
 import torch
 
-from .linear import quantize_rows
+from .linear import ROT_GROUP, convrot_matmul, quantize_rows, regular_hadamard, rotate256  # noqa: F401
 
 
 def ieee_sqrt(t):
@@ -84,3 +85,26 @@ def quant_heads_i8(o):
     """o [H, M, 128] head-major -> rows [M, H*128] (triton_fp8.py:134-135), then the plain quantizer."""
     h, m, d = o.shape
     return quantize_rows(o.permute(1, 0, 2).reshape(m, h * d), "int8_rowwise")
+
+
+def rot_quant_rows_i8(x):
+    """int8 of rotate(x) with per-row scales (triton_fp8.py:424-426)."""
+    return _quant_fp32_rows(rotate256(x.float()))
+
+
+def rot_quant_heads_i8(o):
+    """o [H, M, 128] head-major -> rows [M, H*128], rotated and quantized (triton_fp8.py:429-434)."""
+    h, m, d = o.shape
+    return _quant_fp32_rows(rotate256(o.permute(1, 0, 2).reshape(m, h * d).float()))
+
+
+def swiglu_rot_quant_rows_i8(x):
+    """int8 of rotate(silu(gate) * up) (triton_fp8.py:437-439)."""
+    f = x.shape[1] // 2
+    g, u = x[:, :f].float(), x[:, f:].float()
+    return _quant_fp32_rows(rotate256(g * (1.0 / (1.0 + torch.exp(-g))) * u))
+
+
+def norm_mod_rot_quant_rows_i8(x, weight, eps, idx, shift, scale):
+    """int8 of rotate(rms_norm(x) * w * (1 + scale[idx]) + shift[idx]) (triton_fp8.py:442-446)."""
+    return _quant_fp32_rows(rotate256(norm_mod(x, weight, eps, idx, shift, scale)))

@@ -73,6 +73,47 @@ __device__ __forceinline__ float block_sum_fixed(float v, float* red) {
   return r;
 }
 
+// H256 ConvRot rotation of one 256-channel group held by a warp (lane l owns channels 8l..8l+7):
+// y = H256 x with H256 = (H4 (x) H4 (x) H4 (x) H4) / 16 and H4 the regular 4x4 Hadamard matrix, whose rows are
+// all ones except a -1 on the anti-diagonal, so one radix-4 stage is y_k = S/2 - e_(3-k) with S = e0+e1+e2+e3.
+// Four stages over the base-4 digits of the channel index (digit 0 = fastest): digit 0 and half of digit 1
+// live in the thread, the rest in the lane number (shuffles). Every sum is (e0 + e1) + (e2 + e3) in fp32;
+// the CPU oracle repeats exactly this order. (reference: triton_fp8.py:70-112 regular_hadamard / _rot256)
+__device__ __forceinline__ float rot_half_sum(float e0, float e1, float e2, float e3) {
+  return 0.5f * __fadd_rn(__fadd_rn(e0, e1), __fadd_rn(e2, e3));
+}
+__device__ __forceinline__ void rotate256(float* x, int lane) {
+  // digit 0: channels j & 3 inside the thread
+#pragma unroll
+  for (int b = 0; b < 8; b += 4) {
+    const float e0 = x[b], e1 = x[b + 1], e2 = x[b + 2], e3 = x[b + 3];
+    const float hs = rot_half_sum(e0, e1, e2, e3);
+    x[b] = __fsub_rn(hs, e3), x[b + 1] = __fsub_rn(hs, e2), x[b + 2] = __fsub_rn(hs, e1), x[b + 3] = __fsub_rn(hs, e0);
+  }
+  // digit 1 = (j >> 2) + 2 * (lane & 1): this lane holds one pair (e0,e1 or e2,e3), lane ^ 1 the other. The two
+  // pair sums are added in either order (fp addition commutes), so both lanes see the same total.
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float u = x[j], w = x[j + 4];
+    const float pu = __shfl_xor_sync(0xffffffffu, u, 1), pw = __shfl_xor_sync(0xffffffffu, w, 1);
+    const float hs = 0.5f * __fadd_rn(__fadd_rn(u, w), __fadd_rn(pu, pw));
+    x[j] = __fsub_rn(hs, pw);      // digit k pairs with 3 - k: (0,3) and (1,2) sit crosswise in the two lanes
+    x[j + 4] = __fsub_rn(hs, pu);
+  }
+  // digit 2 = (lane >> 1) & 3, digit 3 = lane >> 3: one value per lane, partners at lane ^ (1,2,3) << shift
+#pragma unroll
+  for (int stage = 0; stage < 2; ++stage) {
+    const int shift = stage == 0 ? 1 : 3;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float own = x[j];
+      const float t = __fadd_rn(own, __shfl_xor_sync(0xffffffffu, own, 1 << shift));   // e0+e1 or e2+e3
+      const float sum = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2 << shift));
+      x[j] = __fsub_rn(0.5f * sum, __shfl_xor_sync(0xffffffffu, own, 3 << shift));
+    }
+  }
+}
+
 // Issue the 128-bit loads of one row (CPT chunks per thread); nothing waits on them here.
 template <int KIND, int T, int CPT>
 __device__ __forceinline__ void load_row(const QuantParams& p, int64_t row, int tid, int nchunk, uint4* raw,
@@ -99,7 +140,7 @@ __device__ __forceinline__ void load_row(const QuantParams& p, int64_t row, int 
 
 // One CTA of T threads works on rows blockIdx.x, blockIdx.x + gridDim.x, ...; the loads of the next row
 // are issued before the current row is reduced and stored, so every CTA always has a row in flight.
-template <int KIND, int OUT_FP8, int T, int CPT>
+template <int KIND, int OUT_FP8, int T, int CPT, int ROT>
 __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
   __shared__ float red[T / 32];
   const int tid = threadIdx.x;
@@ -166,6 +207,13 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
     }
   }
 
+  if (ROT) {
+    // chunk c = tid + i * T: the 32 lanes of a warp hold one whole 256-channel group per i
+#pragma unroll
+    for (int i = 0; i < CPT; ++i)
+      if (tid - (tid & 31) + i * T < nchunk) rotate256(v[i], tid & 31);
+  }
+
   // ---- abs-max and scale ----
   float am = 0.f;
 #pragma unroll
@@ -200,14 +248,14 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
   }  // rows of this CTA
 }
 
-template <int KIND, int OUT_FP8>
+template <int KIND, int OUT_FP8, int ROT = 0>
 int launch_quant(const QuantParams& p, cudaStream_t stream) {
   const int64_t nchunk = p.K >> 3;
   if (p.M == 0) return 0;
   // as many CTAs as are resident at once (a multiple of the SM count), each looping over its rows
 #define RH3_Q(T_, CPT_)                                                                                \
   do {                                                                                                 \
-    auto kern = quant_rows_kernel<KIND, OUT_FP8, T_, CPT_>;                                            \
+    auto kern = quant_rows_kernel<KIND, OUT_FP8, T_, CPT_, ROT>;                                       \
     int occ = 1;                                                                                       \
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, T_, 0) != cudaSuccess || occ < 1) occ = 1; \
     const int64_t resident = static_cast<int64_t>(device_sm_count()) * occ;                           \
@@ -300,4 +348,57 @@ extern "C" int rh3_norm_mod_quant_rows_i8(const void* x, int64_t ldx, const void
   p.w = static_cast<const __nv_bfloat16*>(w); p.eps = eps; p.idx = idx; p.shift = shift; p.scale = scale;
   p.ld_tab = ld_tab;
   return launch_quant<KIND_NORMMOD, 0>(p, stream);
+}
+
+// ---- the same quantizers with the H256 ConvRot rotation applied before the abs-max (K % 256 == 0) ----
+#define RH3_ROT_CHECK(K, name) RH3_CHECK_ARG((K) % 256 == 0, name ": the rotated width must be a multiple of 256")
+
+extern "C" int rh3_rot_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
+                                     cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, K, q, ldq, s)) return e;
+  RH3_ROT_CHECK(K, "rot_quant_rows_i8");
+  RH3_CHECK_ARG(ldx >= K && ldq >= K, "rot_quant_rows_i8: row strides smaller than K");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = K; p.q = q; p.ldq = ldq; p.s = s;
+  return launch_quant<KIND_PLAIN, 0, 1>(p, stream);
+}
+
+extern "C" int rh3_swiglu_rot_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t F, void* q, int64_t ldq,
+                                            float* s, cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, F, q, ldq, s)) return e;
+  RH3_ROT_CHECK(F, "swiglu_rot_quant_rows_i8");
+  RH3_CHECK_ARG(ldx >= 2 * F && ldq >= F, "swiglu_rot_quant_rows_i8: row strides too small");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = F; p.q = q; p.ldq = ldq; p.s = s;
+  return launch_quant<KIND_SWIGLU, 0, 1>(p, stream);
+}
+
+extern "C" int rh3_rot_quant_groups_i8(const void* o, int64_t stride_g, int64_t G, int64_t gw, int64_t M, void* q,
+                                       int64_t ldq, float* s, cudaStream_t stream) {
+  RH3_CHECK_ARG(G > 0 && gw > 0 && gw % 8 == 0 && gw < (1ll << 30), "rot_quant_groups_i8: bad group shape");
+  if (int e = check_common(o, stride_g, M, G * gw, q, ldq, s)) return e;
+  RH3_ROT_CHECK(G * gw, "rot_quant_groups_i8");
+  RH3_CHECK_ARG(stride_g >= M * gw && ldq >= G * gw, "rot_quant_groups_i8: strides too small");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(o); p.ldx = stride_g; p.M = M; p.K = G * gw; p.q = q; p.ldq = ldq; p.s = s;
+  p.gw = static_cast<int>(gw);
+  return launch_quant<KIND_HEADS, 0, 1>(p, stream);
+}
+
+extern "C" int rh3_norm_mod_rot_quant_rows_i8(const void* x, int64_t ldx, const void* w, float eps, const int32_t* idx,
+                                              const float* shift, const float* scale, int64_t ld_tab, int64_t M,
+                                              int64_t K, void* q, int64_t ldq, float* s, cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, K, q, ldq, s)) return e;
+  RH3_ROT_CHECK(K, "norm_mod_rot_quant_rows_i8");
+  RH3_CHECK_ARG(ldx >= K && ldq >= K, "norm_mod_rot_quant_rows_i8: row strides smaller than K");
+  RH3_CHECK_ARG(M == 0 || (idx && shift && scale), "norm_mod_rot_quant_rows_i8: null modulation pointer");
+  RH3_CHECK_ARG(ld_tab % 4 == 0 && (reinterpret_cast<uintptr_t>(shift) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(scale) & 15) == 0,
+                "norm_mod_rot_quant_rows_i8: shift/scale must be 16-byte aligned, row stride a multiple of 4");
+  RH3_CHECK_ARG(!w || (reinterpret_cast<uintptr_t>(w) & 15) == 0, "norm_mod_rot_quant_rows_i8: w must be 16-byte aligned");
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = K; p.q = q; p.ldq = ldq; p.s = s;
+  p.w = static_cast<const __nv_bfloat16*>(w); p.eps = eps; p.idx = idx; p.shift = shift; p.scale = scale;
+  p.ld_tab = ld_tab;
+  return launch_quant<KIND_NORMMOD, 0, 1>(p, stream);
 }

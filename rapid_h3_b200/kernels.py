@@ -1,7 +1,7 @@
 """Quantized linear front end; same surface as the reference's custom_nodes/rapid_h3/kernels.py
 (`QWeight`, `quantize_weight`, `quantize_rows`, `linear`, `gemm_config`), with every mode routed to
 the CUDA kernels of this package. Unknown modes raise ValueError as in the reference; modes the
-reference only emulates (nvfp4 fakes) or that need the H256 rotation raise NotImplementedError.
+reference only emulates (nvfp4 fakes) and its per-tensor fp8 mode raise NotImplementedError.
 """
 from dataclasses import dataclass
 
@@ -21,17 +21,19 @@ class QWeight:
 
 
 _ROWWISE_I8 = ("int8_rowwise", "int8_fast")
+_ROT_I8 = ("int8_rot",)
 _ROWWISE_F8 = ("fp8_rowwise", "fp8_rowwise_torch")
-_UNSUPPORTED = ("int8_rot", "nvfp4_fake", "nvfp4_rot_fake", "fp8_tensor")
+_UNSUPPORTED = ("nvfp4_fake", "nvfp4_rot_fake", "fp8_tensor")
 
 
 def quantize_weight(w, mode):
     """Per-output-row weight quantization (one-off, at load): W [N,K] -> QWeight(q [N,K], scale [1,N]).
     Runs through the same row quantizer kernels as the activations (same arithmetic as the reference's
-    kernels.py:52-72 for the row-wise modes)."""
+    kernels.py:52-72 for the row-wise modes). `int8_rot` stores int8(W . blockdiag(H256)^T): the rotation is
+    orthonormal, so rotated activations times rotated weights give x W^T (kernels.py:58-60)."""
     if mode in _UNSUPPORTED:
         raise NotImplementedError(f"mode {mode!r} is not implemented in rapid_h3_b200")
-    if mode not in _ROWWISE_I8 + _ROWWISE_F8:
+    if mode not in _ROWWISE_I8 + _ROWWISE_F8 + _ROT_I8:
         raise ValueError(mode)
     w = w.detach()
     if w.dtype != torch.bfloat16:
@@ -39,7 +41,8 @@ def quantize_weight(w, mode):
         if not torch.equal(w.to(torch.bfloat16).to(w.dtype), w):
             raise RuntimeError("quantize_weight: weight is not bf16-representable")
         w = w.to(torch.bfloat16)
-    q, s = (_tq.quant_rows_i8 if mode in _ROWWISE_I8 else _tq.quant_rows)(w.contiguous())
+    fn = _tq.rot_quant_rows_i8 if mode in _ROT_I8 else (_tq.quant_rows_i8 if mode in _ROWWISE_I8 else _tq.quant_rows)
+    q, s = fn(w.contiguous())
     return QWeight(q, s.t().contiguous())
 
 
@@ -47,6 +50,8 @@ def quantize_rows(x, mode):
     """Per-token (row) dynamic quantization -> (q, scale[M, 1] fp32)."""
     if mode in _ROWWISE_I8:
         return _tq.quant_rows_i8(x)
+    if mode in _ROT_I8:
+        return _tq.rot_quant_rows_i8(x)
     if mode in _ROWWISE_F8:
         return _tq.quant_rows(x)
     raise ValueError(mode)

@@ -44,9 +44,22 @@ class _QuantLinear:
         self.qweight = None
         self.calls = 0
 
+    def _make_qweight(self, w):
+        """Quantize a bf16 weight, or adopt as is a weight that is already stored the way `int8_rot` needs it
+        (ComfyUI's int8_convrot layout: `_qdata` int8 [N,K] rotated in groups of 256, `_params.scale` per output
+        row), so such checkpoints run without a bf16 copy (reference __init__.py:107-117)."""
+        p = getattr(w, "_params", None)
+        if (p is not None and hasattr(w, "_qdata") and self.mode == "int8_rot" and getattr(p, "convrot", False)
+                and getattr(p, "convrot_groupsize", 0) == tq.ROT_GROUP and not getattr(p, "transposed", False)
+                and w._qdata.dtype == torch.int8):
+            return kernels.QWeight(w._qdata.contiguous(), p.scale.float().reshape(1, -1).contiguous())
+        if p is not None and hasattr(w, "dequantize"):
+            w = w.dequantize()
+        return kernels.quantize_weight(w.detach(), self.mode)
+
     def qweight_for(self, x=None):
         if self.qweight is None:
-            self.qweight = kernels.quantize_weight(self.module.weight.detach(), self.mode)
+            self.qweight = self._make_qweight(self.module.weight)
         return self.qweight
 
     def __call__(self, x):
@@ -81,6 +94,8 @@ class FusedBlock:
         self.block = block
         self.qkv_q, self.out_q, self.fc1_q, self.fc2_q = qkv_q, out_q, fc1_q, fc2_q
         self.cq_q, self.ckv_q, self.co_q = cq_q, ckv_q, co_q
+        # `int8_rot`: every quantizer rotates its row with H256 and every weight is stored rotated
+        self.rotate = qkv_q.mode == "int8_rot"
         self._const = {}
 
     # -- helpers -----------------------------------------------------------------------------
@@ -131,13 +146,14 @@ class FusedBlock:
         shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = blk.adaln_proj(t_emb)
         idx = _row_index(mod_segments, s, x.device)
         tab = rope_freqs.reshape(s, 48, 2, 2)
+        rot = self.rotate
 
         def rec(name, value):
             if trace is not None:
                 trace[name] = value.clone() if torch.is_tensor(value) else value
 
         # ---- self-attention ----
-        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm1), self._eps(blk.norm1), idx, shift_msa, scale_msa)
+        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm1), self._eps(blk.norm1), idx, shift_msa, scale_msa, rotate=rot)
         rec("attn_in_q", xq), rec("attn_in_s", xs)
         qw = self.qkv_q.qweight_for()
         qkv = cf.int8_gemm(xq, xs, qw.q, qw.scale)
@@ -149,12 +165,12 @@ class FusedBlock:
         if sp is None:
             o = attn_int8.attention(q, k, v)                       # [S, H, 128] token-major
             rec("attn_out", o)
-            oq, os_ = tq.quant_rows_i8(o.view(s, hd))
+            oq, os_ = tq.rot_quant_rows_i8(o.view(s, hd), rotate=rot)
         else:
             qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
             og = attn_int8.attention(qg, kg, vg)
             o = sp.heads_to_tokens(og)                              # [P, S_local, (H/P)*128] group-major
-            oq, os_ = tq.quant_groups_i8(o)
+            oq, os_ = tq.quant_groups_i8(o, rotate=rot)
         del qkv, q, k, v
         x = self._gemm_gated(oq, os_, self.out_q, x, gate_msa, mod_segments)
         rec("x_attn", x)
@@ -164,10 +180,10 @@ class FusedBlock:
             c = blk.cross
             zeros, ones = self._zeros_tab(d, x.device)
             idx0 = self._const.setdefault(("idx0", s, str(x.device)), torch.zeros(s, dtype=torch.int32, device=x.device))
-            xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm_c), self._eps(blk.norm_c), idx0, zeros, zeros)
+            xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm_c), self._eps(blk.norm_c), idx0, zeros, zeros, rotate=rot)
             qw = self.cq_q.qweight_for()
             qc = cf.int8_gemm(xq, xs, qw.q, qw.scale).view(s, c.heads, c.head_dim)
-            cq8, cs = tq.quant_rows_i8(ctx)
+            cq8, cs = tq.rot_quant_rows_i8(ctx, rotate=rot)
             qw = self.ckv_q.qweight_for()
             kv = cf.int8_gemm(cq8, cs, qw.q, qw.scale)
             kc, vc = (t.view(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
@@ -175,16 +191,16 @@ class FusedBlock:
             attn_int8.rms_rope(kc, self._norm_w(c.k_norm), c.k_norm.eps, None, out=kc)
             oc = attn_int8.attention(qc, kc, vc)
             rec("cross_out", oc)
-            oq, os_ = tq.quant_rows_i8(oc.view(s, hd))
+            oq, os_ = tq.rot_quant_rows_i8(oc.view(s, hd), rotate=rot)
             qw = self.co_q.qweight_for()
             cf.int8_gemm_gated_residual(oq, os_, qw.q, qw.scale, ones, x)
             rec("x_cross", x)
 
         # ---- MLP ----
-        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm2), self._eps(blk.norm2), idx, shift_mlp, scale_mlp)
+        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm2), self._eps(blk.norm2), idx, shift_mlp, scale_mlp, rotate=rot)
         h = cf.int8_gemm_swiglu(xq, xs, *self._fc1_swiglu_weight())
         rec("mlp_h", h)
-        hq, hs = tq.rot_quant_rows_i8(h)
+        hq, hs = tq.rot_quant_rows_i8(h, rotate=rot)
         del h
         out = self._gemm_gated(hq, hs, self.fc2_q, x, gate_mlp, mod_segments)
         rec("x_out", out)
@@ -222,7 +238,7 @@ def _parse_blocks(spec):
 class RapidH3LinearQuant:
     """Node adapter: quantize the DiT's linears and fuse the blocks (reference __init__.py:352-417)."""
 
-    MODES = ["bf16", "fp8_rowwise", "int8_rowwise", "int8_fast"]
+    MODES = ["bf16", "fp8_rowwise", "int8_rowwise", "int8_fast", "int8_rot"]
 
     def patch(self, model, mode="int8_rowwise", targets="qkv_proj,out_proj,fc1,fc2,q_proj,kv_proj",
               keep_bf16_blocks="", measure_every=0, fuse_block=True):
@@ -243,7 +259,7 @@ class RapidH3LinearQuant:
             n = f"blocks.{i}"
             parts = [by_name.get(f"{n}.{m}") for m in ("attn.qkv_proj", "attn.out_proj", "mlp.fc1", "mlp.fc2")]
             cross = [by_name.get(f"{n}.{m}") for m in ("cross.q_proj", "cross.kv_proj", "cross.out_proj")]
-            if all(parts) and fuse_block and mode in ("int8_rowwise", "int8_fast"):
+            if all(parts) and fuse_block and mode in ("int8_rowwise", "int8_fast", "int8_rot"):
                 if hasattr(blk, "cross") and not all(cross):
                     raise NotImplementedError("fused block needs the cross-attention linears quantized as well")
                 forwards.append(_fused_block(blk, *parts, *(cross if hasattr(blk, "cross") else ())))

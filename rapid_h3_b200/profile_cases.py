@@ -2,7 +2,7 @@
 
     python -m rapid_h3_b200.profile_cases attn  --L 16384 --H 8  [--iters 3]
     python -m rapid_h3_b200.profile_cases gemm  --M 8192 --N 12288 --K 4096 [--epi plain|gated|swiglu]
-    python -m rapid_h3_b200.profile_cases quant --M 36436 --K 4096 [--kind plain|fp8|normmod]
+    python -m rapid_h3_b200.profile_cases quant --M 36436 --K 4096 [--kind plain|fp8|normmod|rot|normmod_rot]
     python -m rapid_h3_b200.profile_cases prepass --L 16384 --H 8
 
 Each case builds seeded random inputs on the device, runs the kernel `--iters` times and prints the mean time
@@ -98,11 +98,14 @@ def main():
         x = randn(a.M, a.K).to(torch.bfloat16)
         if a.kind == "fp8":
             fn = lambda: quantizers.quant_rows(x)  # noqa: E731
-        elif a.kind == "normmod":
+        elif a.kind == "rot":
+            fn = lambda: quantizers.rot_quant_rows_i8(x)  # noqa: E731
+        elif a.kind in ("normmod", "normmod_rot"):
             tab = randn(2, 6 * a.K) * 0.1
             idx = torch.zeros(a.M, dtype=torch.int32, device="cuda")
             w = torch.ones(a.K, device="cuda", dtype=torch.bfloat16)
-            fn = lambda: quantizers.norm_mod_rot_quant_rows_i8(x, w, 1e-6, idx, tab[:, :a.K], tab[:, a.K:2 * a.K])  # noqa: E731
+            fn = lambda: quantizers.norm_mod_rot_quant_rows_i8(x, w, 1e-6, idx, tab[:, :a.K], tab[:, a.K:2 * a.K],
+                                                                rotate=a.kind == "normmod_rot")  # noqa: E731
         else:
             fn = lambda: quantizers.quant_rows_i8(x)  # noqa: E731
         ms = _time(fn, a.iters)

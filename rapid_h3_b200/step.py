@@ -31,7 +31,7 @@ class H3Runtime:
                 q.module.weight.data = torch.empty(0, device=q.module.weight.device, dtype=torch.bfloat16)
 
     @staticmethod
-    def random(cfg, seed, device="cuda", release_bf16=True):
+    def random(cfg, seed, device="cuda", release_bf16=True, mode="int8_rowwise"):
         """Random-init model of the benchmark configurations, generated and quantized block by block on `device`."""
         with torch.device("meta"):
             model = M.H3Transformer(cfg)
@@ -49,7 +49,7 @@ class H3Runtime:
                 if name.startswith("cross") and not cfg.cross_attention:
                     continue
                 mod = blk.get_submodule(name)
-                q = nodes._QuantLinear(mod, f"blocks.{i}.{name}", mode="int8_rowwise")
+                q = nodes._QuantLinear(mod, f"blocks.{i}.{name}", mode=mode)
                 q.qweight_for()
                 if release_bf16:
                     mod.weight.data = torch.empty(0, device=device, dtype=torch.bfloat16)

@@ -90,3 +90,24 @@ def test_norm_mod_matches_fp32_expression():
     assert torch.allclose(y, ref, rtol=1e-5, atol=1e-6)
     q, s = oq.norm_mod_quant_rows_i8(x, w, 1e-6, idx, shift, scale)
     assert q.abs().max() == 127 and s.shape == (m, 1)
+
+
+def test_rotation_butterfly_equals_hadamard_product():
+    """The oracle's radix-4 butterflies against the reference's definition of the rotation, x @ blockdiag(H256)^T
+    with H256 the Kronecker power of the regular 4x4 Hadamard matrix (triton_fp8.py:70-92), and its orthonormality
+    (which is what lets rotated activations meet rotated weights)."""
+    from oracle import linear as ol
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(7, 768, generator=g)
+    y = ol.rotate256(x)
+    assert (y.double() - ol.convrot_matmul(x)).abs().max() < 2e-6
+    h = ol.regular_hadamard(256)
+    assert torch.allclose(h @ h.T, torch.eye(256, dtype=torch.float64), atol=1e-12)
+    assert torch.allclose(y.double().norm(dim=1), x.double().norm(dim=1), rtol=1e-6)
+    # int8_rot linear == int8 arithmetic on rotated operands, and stays close to the exact product
+    w = torch.randn(32, 768, generator=g).to(torch.bfloat16)
+    xb = x.to(torch.bfloat16)
+    wq, ws = ol.quantize_weight(w, "int8_rot")
+    out = ol.linear(xb, wq, ws, "int8_rot").double()
+    ref = xb.double() @ w.double().t()
+    assert ((out - ref).norm() / ref.norm()).item() < 2e-2
