@@ -297,6 +297,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="full", choices=sorted(WORKLOADS) + ["vae"])
+    ap.add_argument("--mode", default="int8_rowwise", choices=["int8_rowwise", "int8_rot"],
+                    help="linear recipe of the step: un-rotated row-wise int8 (the benchmark configuration) or the "
+                         "H256-rotated recipe")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -322,7 +325,7 @@ def main():
         return
     grid, n_audio, batch, text_len, blocks = WORKLOADS[args.workload]
     cfg = H3Config(n_blocks=blocks)
-    rt = r.step.H3Runtime.random(cfg, seed=0, device=f"cuda:{local}")
+    rt = r.step.H3Runtime.random(cfg, seed=0, device=f"cuda:{local}", mode=args.mode)
     s_total = grid[0] * grid[1] * grid[2] + n_audio
     sp = r.sp.Ulysses(s_total) if world > 1 else None
     host = [t.pin_memory() for t in r.step.make_inputs(cfg, grid, n_audio, batch, text_len, seed=0)]
@@ -395,7 +398,7 @@ def main():
     rec = {"metric": "H3 DiT step seconds @768x1344x141f", "value": ms_step / 1e3, "unit": "s/step", "n_gpus": world,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False,
            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-           "config": workload_config(args.workload, world), "clocks": clocks,
+           "config": dict(workload_config(args.workload, world), linear_mode=args.mode), "clocks": clocks,
            "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
            "gpu_launches": launches, "roofline": roof}
     if rank == 0:
