@@ -22,7 +22,7 @@
 //   warp group 0  service: warp 0 = TMA producer (Q once, then K tile 128 keys x 128 B + V^T tile 128
 //                 channels x 128 keys per step), warp 1 = MMA issuer (for both query tiles, Q.K^T of
 //                 key tile j+1 is issued before P.V of tile j); gives its registers away (setmaxnreg)
-//   warp groups 1, 2  softmax of query tile 0 / 1, one query row per thread, 240 registers each so a
+//   warp groups 1, 2  softmax of query tile 0 / 1, one query row per thread, 232 registers each so a
 //                 whole row of S (128 values) lives in registers: the accumulator is pre-biased with
 //                 1.5*2^23 so its int32 bits are a float (no conversion); the row is read from TMEM
 //                 ONCE and S is handed straight back, so the next Q.K^T runs under the whole softmax;
@@ -149,8 +149,13 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, float cc, fl
 }
 
 // Register reallocation between warp groups (one instruction per warp, all four warps of the group).
-__device__ __forceinline__ void reg_dealloc_24() { asm volatile("setmaxnreg.dec.sync.aligned.u32 24;"); }
-__device__ __forceinline__ void reg_alloc_240() { asm volatile("setmaxnreg.inc.sync.aligned.u32 240;"); }
+// The kernel is compiled for 168 registers per thread (384 threads, one CTA per SM); the service group
+// drops to 40 and each softmax thread rises to 232: 128 * 40 + 256 * 232 = 384 * 168 exactly. The two numbers
+// must keep that equality: a request for more registers than the CTA's pool holds never returns.
+constexpr int REGS_COMPILED = 168, REGS_SERVICE = 40, REGS_SOFTMAX = 232;  // 65536 / 384 rounded down to 8
+static_assert(128 * REGS_SERVICE + 256 * REGS_SOFTMAX == ATTN_THREADS * REGS_COMPILED, "register pool must balance");
+__device__ __forceinline__ void reg_release_service() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+__device__ __forceinline__ void reg_take_softmax() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
 
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -193,7 +198,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
 
   if (warp < 4) {
     // ============================ service warp group: TMA + MMA issue ============================
-    reg_dealloc_24();
+    reg_release_service();
     if (warp == 0 && lane == 0) {
       // ------------------------------ TMA producer ------------------------------
       tma_prefetch_desc(&tma_q);
@@ -263,7 +268,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
     // t = fma(bits, c, off) needs no int->float conversion and the row maximum is a 3-input float max
     // on the raw values. The row is read from TMEM once and S is handed back to the MMA warp right
     // away, so the next Q.K^T of this query tile runs under the whole softmax of the current one.
-    reg_alloc_240();
+    reg_take_softmax();
     const int g = (warp >> 2) - 1;     // query tile of this warp group
     const int quad = warp & 3;         // TMEM lane quadrant this warp may access
     const int row = quad * 32 + lane;  // row of the tile = TMEM lane
