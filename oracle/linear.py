@@ -33,16 +33,17 @@ def convrot_matmul(x):
 
 def rotate256(y):
     """fp32 y [M, K] -> y @ blockdiag(H256)^T as four radix-4 stages over the base-4 digits of the
-    channel index inside its group of 256, lowest digit first. A stage maps the four values e0..e3 that
-    differ in that digit to 0.5 * ((e0 + e1) + (e2 + e3)) - e_(3-k): H4 / 2 with every rounding fixed."""
+    channel index inside its group of 256, lowest digit first, then one multiplication by 1/16. With
+    a = e0+e1, b = e2+e3, c = e0-e1, d = e2-e3 a stage maps the four values that differ in that digit to
+    (a+d, a-d, b+c, b-c): H4 with every rounding fixed, the order the CUDA kernel uses."""
     m, k = y.shape
     assert k % ROT_GROUP == 0
     v = y.float().reshape(m, k // ROT_GROUP, 4, 4, 4, 4)
     for axis in (5, 4, 3, 2):
-        e = v.unbind(axis)
-        hs = ((e[0] + e[1]) + (e[2] + e[3])) * 0.5
-        v = torch.stack([hs - e[3 - d] for d in range(4)], dim=axis)
-    return v.reshape(m, k)
+        e0, e1, e2, e3 = v.unbind(axis)
+        a, b, c, d = e0 + e1, e2 + e3, e0 - e1, e2 - e3
+        v = torch.stack([a + d, a - d, b + c, b - c], dim=axis)
+    return (v * 0.0625).reshape(m, k)
 
 
 def quantize_rows(x, mode):

@@ -341,6 +341,55 @@ __device__ __forceinline__ uint32_t quant_code_e4m3(float y, float s, float inv)
   if (fabsf(yq) < 0.015625f || (drop - 0x7FFF0u) < 0x20u) yq = fminf(fmaxf(__fdiv_rn(y, s), -448.f), 448.f);
   return static_cast<uint32_t>(__nv_cvt_float_to_fp8(yq, __NV_SATFINITE, __NV_E4M3)) & 0xFFu;
 }
+// Eight int8 codes at once (bytes 0..7 of the result in memory order). Same arithmetic as quant_code_i8,
+// but the "near a tie" tests of the eight values are OR-ed into one predicate, so the exact-division path is
+// a single rarely taken branch per 8 values instead of one per value. Recomputing all eight exactly is
+// harmless: away from a tie the fast and the exact code agree.
+__device__ __forceinline__ uint2 quant8_i8(const float* y, float s, float inv) {
+  const float kMagic = 12582912.f;
+  float t[8];
+  bool near = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float yq = __fmul_rn(y[j], inv);
+    t[j] = __fadd_rn(yq, kMagic);
+    near |= fabsf(__fsub_rn(yq, __fsub_rn(t[j], kMagic))) > 0.499f;  // |yq - round(yq)| <= 0.5 always
+  }
+  if (near) {
+#pragma unroll  // static indices: a rolled loop would push the caller's register array to local memory
+    for (int j = 0; j < 8; ++j) t[j] = __fadd_rn(__fdiv_rn(y[j], s), kMagic);
+  }
+  uint2 o;
+  o.x = __byte_perm(__byte_perm(__float_as_uint(t[0]), __float_as_uint(t[1]), 0x0040),
+                    __byte_perm(__float_as_uint(t[2]), __float_as_uint(t[3]), 0x0040), 0x5410);
+  o.y = __byte_perm(__byte_perm(__float_as_uint(t[4]), __float_as_uint(t[5]), 0x0040),
+                    __byte_perm(__float_as_uint(t[6]), __float_as_uint(t[7]), 0x0040), 0x5410);
+  return o;
+}
+// Eight e4m3 codes at once; the arithmetic of quant_code_e4m3 with one shared exact path per 8 values and the
+// two-at-a-time hardware conversion (which saturates at +-448 itself).
+__device__ __forceinline__ uint2 quant8_e4m3(const float* y, float s, float inv) {
+  float yq[8];
+  bool near = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    yq[j] = __fmul_rn(y[j], inv);
+    const uint32_t drop = __float_as_uint(yq[j]) & 0xFFFFFu;
+    near |= (fabsf(yq[j]) < 0.015625f) | ((drop - 0x7FFF0u) < 0x20u);
+  }
+  if (near) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) yq[j] = __fdiv_rn(y[j], s);
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint16_t h;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(h) : "f"(yq[2 * j]), "f"(yq[2 * j + 1]));
+    w[j] = h;
+  }
+  return make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
+}
 // pack the low bytes of four words into one word (a -> byte 0 ... d -> byte 3)
 __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);

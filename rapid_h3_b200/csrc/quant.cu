@@ -74,44 +74,46 @@ __device__ __forceinline__ float block_sum_fixed(float v, float* red) {
 }
 
 // H256 ConvRot rotation of one 256-channel group held by a warp (lane l owns channels 8l..8l+7):
-// y = H256 x with H256 = (H4 (x) H4 (x) H4 (x) H4) / 16 and H4 the regular 4x4 Hadamard matrix, whose rows are
-// all ones except a -1 on the anti-diagonal, so one radix-4 stage is y_k = S/2 - e_(3-k) with S = e0+e1+e2+e3.
-// Four stages over the base-4 digits of the channel index (digit 0 = fastest): digit 0 and half of digit 1
-// live in the thread, the rest in the lane number (shuffles). Every sum is (e0 + e1) + (e2 + e3) in fp32;
-// the CPU oracle repeats exactly this order. (reference: triton_fp8.py:70-112 regular_hadamard / _rot256)
-__device__ __forceinline__ float rot_half_sum(float e0, float e1, float e2, float e3) {
-  return 0.5f * __fadd_rn(__fadd_rn(e0, e1), __fadd_rn(e2, e3));
-}
+// y = H256 x with H256 = (H4 (x) H4 (x) H4 (x) H4) / 16 and H4 the regular 4x4 Hadamard matrix (all ones except
+// a -1 on the anti-diagonal). One radix-4 stage over the four values e0..e3 that differ in one base-4 digit of
+// the channel index is, unscaled,
+//     y_k = (e_k + e_(k^1)) + (e_(k^2) - e_(k^3))
+// i.e. with a = e0+e1, b = e2+e3, c = e0-e1, d = e2-e3:  y0 = a+d, y1 = a-d, y2 = b+c, y3 = b-c.
+// Four stages (digit 0 = fastest first), then one multiplication by 1/16. Digit 0 and the low bit of digit 1
+// live in the thread, the rest in the lane number; written this way a cross-lane stage costs two shuffles per
+// value (the partner of the pair, then the other pair's difference) and the half-in-thread stage one shuffle per
+// pair. Every operation is a single rounded fp32 add, so the CPU oracle repeats it bit for bit.
+// (reference: triton_fp8.py:70-112 regular_hadamard / _rot256)
 __device__ __forceinline__ void rotate256(float* x, int lane) {
   // digit 0: channels j & 3 inside the thread
 #pragma unroll
   for (int b = 0; b < 8; b += 4) {
-    const float e0 = x[b], e1 = x[b + 1], e2 = x[b + 2], e3 = x[b + 3];
-    const float hs = rot_half_sum(e0, e1, e2, e3);
-    x[b] = __fsub_rn(hs, e3), x[b + 1] = __fsub_rn(hs, e2), x[b + 2] = __fsub_rn(hs, e1), x[b + 3] = __fsub_rn(hs, e0);
+    const float sa = __fadd_rn(x[b], x[b + 1]), sb = __fadd_rn(x[b + 2], x[b + 3]);
+    const float dc = __fsub_rn(x[b], x[b + 1]), dd = __fsub_rn(x[b + 2], x[b + 3]);
+    x[b] = __fadd_rn(sa, dd), x[b + 1] = __fsub_rn(sa, dd), x[b + 2] = __fadd_rn(sb, dc), x[b + 3] = __fsub_rn(sb, dc);
   }
-  // digit 1 = (j >> 2) + 2 * (lane & 1): this lane holds one pair (e0,e1 or e2,e3), lane ^ 1 the other. The two
-  // pair sums are added in either order (fp addition commutes), so both lanes see the same total.
+  // digit 1 = (j >> 2) + 2 * (lane & 1): the pair (e_k, e_(k^1)) is (x[j], x[j+4]); the other pair sits in lane ^ 1
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float u = x[j], w = x[j + 4];
-    const float pu = __shfl_xor_sync(0xffffffffu, u, 1), pw = __shfl_xor_sync(0xffffffffu, w, 1);
-    const float hs = 0.5f * __fadd_rn(__fadd_rn(u, w), __fadd_rn(pu, pw));
-    x[j] = __fsub_rn(hs, pw);      // digit k pairs with 3 - k: (0,3) and (1,2) sit crosswise in the two lanes
-    x[j + 4] = __fsub_rn(hs, pu);
+    const float t = __fadd_rn(x[j], x[j + 4]);
+    const float v = __shfl_xor_sync(0xffffffffu, __fsub_rn(x[j], x[j + 4]), 1);
+    x[j] = __fadd_rn(t, v);
+    x[j + 4] = __fsub_rn(t, v);
   }
-  // digit 2 = (lane >> 1) & 3, digit 3 = lane >> 3: one value per lane, partners at lane ^ (1,2,3) << shift
+  // digit 2 = (lane >> 1) & 3, digit 3 = lane >> 3: one value per lane
 #pragma unroll
   for (int stage = 0; stage < 2; ++stage) {
     const int shift = stage == 0 ? 1 : 3;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float own = x[j];
-      const float t = __fadd_rn(own, __shfl_xor_sync(0xffffffffu, own, 1 << shift));   // e0+e1 or e2+e3
-      const float sum = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2 << shift));
-      x[j] = __fsub_rn(0.5f * sum, __shfl_xor_sync(0xffffffffu, own, 3 << shift));
+      const float p1 = __shfl_xor_sync(0xffffffffu, own, 1 << shift);                      // e_(k^1)
+      const float v = __shfl_xor_sync(0xffffffffu, __fsub_rn(own, p1), 2 << shift);        // e_(k^2) - e_(k^3)
+      x[j] = __fadd_rn(__fadd_rn(own, p1), v);
     }
   }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], 0.0625f);
 }
 
 // Issue the 128-bit loads of one row (CPT chunks per thread); nothing waits on them here.
@@ -233,16 +235,8 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
   for (int i = 0; i < CPT; ++i) {
     const int c = tid + i * T;
     if (c < nchunk) {
-      uint32_t o[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t code[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          code[j] = OUT_FP8 ? quant_code_e4m3(v[i][4 * h + j], s, inv) : quant_code_i8(v[i][4 * h + j], s, inv);
-        o[h] = pack_low_bytes(code[0], code[1], code[2], code[3]);
-      }
-      *reinterpret_cast<uint2*>(qrow + (static_cast<int64_t>(c) << 3)) = make_uint2(o[0], o[1]);
+      const uint2 o = OUT_FP8 ? quant8_e4m3(v[i], s, inv) : quant8_i8(v[i], s, inv);
+      *reinterpret_cast<uint2*>(qrow + (static_cast<int64_t>(c) << 3)) = o;
     }
   }
   }  // rows of this CTA
