@@ -167,6 +167,29 @@ int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const void* gamma, 
 int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t T, int64_t H, int64_t W, int64_t C,
                           cudaStream_t stream);
 
+/* ---- fp16 ops of the VAE transformer decoder (the callers of the int8 path at fp16 activations) ----
+ * rh3_vae_out_quant: o [B, H, S, D] fp16 head-major attention output -> q int8 [B*S, H*D], scales fp32 [B*S]:
+ *   nan_to_num on load, H256 rotation in comfy-kitchen's stage order, int8 with value / scale / quotient rounded
+ *   through fp16. Replaces vae_ops.vae_out_quant (custom_nodes/rapid_h3/csrc/vae_ops.cu:63-142,366-385).
+ * rh3_vae_gemm: out fp16 [M, N] = fp16(fp16((acc * xs[m]) * ws[n] + bias[n]) * rscale[n] + resid[m, n]) when a
+ *   residual is given, else fp16((acc * xs[m]) * ws[n] + bias[n]). Replaces vae_ops.vae_gemm
+ *   (vae_ops.cu:150-227,387-403; called from vae_fast._linear, vae_fast.py:118-169).
+ * rh3_vae_gemm_swiglu: weight rows interleaved [g 4j..4j+3 | u 4j..4j+3]; g, u = fp16((acc*xs)*ws + bias),
+ *   out fp16 [M, N/2] = fp16(g / (1 + e^-g) * u). Replaces vae_ops.vae_gemm_swiglu (vae_ops.cu:228-345,405-420). */
+int rh3_vae_out_quant(const void* o_f16, int64_t B, int64_t H, int64_t S, int64_t D, void* q, float* scales,
+                      cudaStream_t stream);
+/* rh3_vae_quant_rows: the row arithmetic of rh3_vae_out_quant on a row-major fp16 matrix x [M, K] (the plain
+ * activation case of the quantizer the decoder's linears run on their inputs, vae_fast._quantize,
+ * custom_nodes/rapid_h3/vae_fast.py:71-85). */
+int rh3_vae_quant_rows(const void* x_f16, int64_t ldx, int64_t M, int64_t K, void* q, float* scales,
+                       cudaStream_t stream);
+int rh3_vae_gemm(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws, const void* bias_f16,
+                 const void* rscale_f16, const void* resid_f16, int64_t ldr, int64_t M, int64_t N, int64_t K,
+                 void* out_f16, int64_t ldo, cudaStream_t stream);
+int rh3_vae_gemm_swiglu(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws,
+                        const void* bias_f16, int64_t M, int64_t N, int64_t K, void* out_f16, int64_t ldo,
+                        cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,6 +30,10 @@ SIGNATURES = {
     "rh3_swiglu_rot_quant_rows_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_rot_quant_groups_i8": [_P, _I64, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_norm_mod_rot_quant_rows_i8": [_P, _I64, _P, _F, _P, _P, _P, _I64, _I64, _I64, _P, _I64, _P, _P],
+    "rh3_vae_out_quant": [_P, _I64, _I64, _I64, _I64, _P, _P, _P],
+    "rh3_vae_quant_rows": [_P, _I64, _I64, _I64, _P, _P, _P],
+    "rh3_vae_gemm": [_P, _I64, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _I64, _P],
+    "rh3_vae_gemm_swiglu": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I64, _P, _I64, _P],
     "rh3_gemm_w8a8": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I64, _P, _P],
     "rh3_gemm_w8a8_gated_residual": [_P, _I64, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _P],
     "rh3_gemm_w8a8_swiglu": [_P, _I64, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I64, _P],

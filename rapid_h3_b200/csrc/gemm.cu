@@ -16,6 +16,7 @@
 //   warps 2..5  epilogue: tcgen05.ld 32 columns at a time, dequantize, fused epilogue, 64-byte
 //               contiguous bf16 stores per thread-row
 // Tensor-core bound: 2*M*N*K operations per call.
+
 #include "common.cuh"
 #include "rapidh3_b200.h"
 
@@ -32,7 +33,7 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int GROUP_M = 16;  // tile rasterisation: 16 row-tiles share each column-tile in L2
 
-enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_SWIGLU = 2 };
+enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_SWIGLU = 2, EPI_F16 = 3, EPI_SWIGLU_F16 = 4 };
 
 struct GemmParams {
   int M, N, K;
@@ -45,6 +46,11 @@ struct GemmParams {
   const __nv_bfloat16* gate;  // EPI_GATED
   __nv_bfloat16* resid;       // EPI_GATED
   int64_t ldr;
+  // fp16 epilogues of the VAE transformer decoder (EPI_F16 / EPI_SWIGLU_F16)
+  const __half* bias_h;    // [N]
+  const __half* rscale_h;  // [N] or null (EPI_F16 with residual)
+  const __half* resid_h;   // [M, N] row stride ldr, or null
+  __half* out_h;           // row stride ldo
   int* status;
 };
 
@@ -56,7 +62,8 @@ struct __align__(8) GemmSmemTail {
   uint32_t tmem_base;
   int abort_flag;
   float ws[BN];
-  float aux[BN];  // bias or gate as fp32
+  float aux[BN];   // bias or gate as fp32
+  float aux2[BN];  // residual scale as fp32 (EPI_F16)
 };
 
 constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + sizeof(GemmSmemTail) + 1024;  // +1024 alignment slack
@@ -179,6 +186,8 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tail->ws[c] = n < p.N ? p.ws[n] : 0.f;
         if (EPI == EPI_PLAIN) tail->aux[c] = (p.bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
         if (EPI == EPI_GATED) tail->aux[c] = n < p.N ? __bfloat162float(p.gate[n]) : 0.f;
+        if (EPI == EPI_F16 || EPI == EPI_SWIGLU_F16) tail->aux[c] = n < p.N ? __half2float(p.bias_h[n]) : 0.f;
+        if (EPI == EPI_F16) tail->aux2[c] = (p.rscale_h && n < p.N) ? __half2float(p.rscale_h[n]) : 0.f;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) break;
@@ -236,6 +245,57 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                   w[j] = pack_bf16x2(v0, v1);
                 }
                 *reinterpret_cast<uint4*>(o + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          } else if (EPI == EPI_F16) {
+            // y1 = fp16(y + bias); with a residual: out = fp16(float(y1) * rscale + resid), two separate roundings
+            __half* o = p.out_h + static_cast<int64_t>(row) * p.ldo + col0;
+            const __half* rs = p.resid_h ? p.resid_h + static_cast<int64_t>(row) * p.ldr + col0 : nullptr;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 + 8 <= p.N) {
+                uint4 old = make_uint4(0, 0, 0, 0);
+                if (rs) old = *reinterpret_cast<const uint4*>(rs + g * 8);
+                const __half2* oh = reinterpret_cast<const __half2*>(&old);
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int e = g * 8 + 2 * j;
+                  float v0 = __half2float(__float2half_rn(__fadd_rn(y[e], tail->aux[c * 32 + e])));
+                  float v1 = __half2float(__float2half_rn(__fadd_rn(y[e + 1], tail->aux[c * 32 + e + 1])));
+                  if (rs) {
+                    const float2 r2 = __half22float2(oh[j]);
+                    v0 = __fadd_rn(__fmul_rn(v0, tail->aux2[c * 32 + e]), r2.x);
+                    v1 = __fadd_rn(__fmul_rn(v1, tail->aux2[c * 32 + e + 1]), r2.y);
+                  }
+                  const __half2 h2 = __floats2half2_rn(v0, v1);
+                  w[j] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+                *reinterpret_cast<uint4*>(o + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          } else if (EPI == EPI_SWIGLU_F16) {
+            // columns in groups of 8 = [g0..g3 | u0..u3]; g, u = fp16(y + bias); out = fp16(g / (1 + e^-g) * u)
+            __half* o = p.out_h + static_cast<int64_t>(row) * p.ldo + (col0 >> 1);
+#pragma unroll
+            for (int hgrp = 0; hgrp < 2; ++hgrp) {
+              if (col0 + hgrp * 16 + 16 <= p.N) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  const int b = hgrp * 16 + q * 8;
+                  float h[4];
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float gv = __half2float(__float2half_rn(__fadd_rn(y[b + j], tail->aux[c * 32 + b + j])));
+                    const float uv = __half2float(__float2half_rn(__fadd_rn(y[b + 4 + j], tail->aux[c * 32 + b + 4 + j])));
+                    h[j] = gv / (1.f + __expf(-gv)) * uv;
+                  }
+                  const __half2 h01 = __floats2half2_rn(h[0], h[1]), h23 = __floats2half2_rn(h[2], h[3]);
+                  w[q * 2] = *reinterpret_cast<const uint32_t*>(&h01);
+                  w[q * 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);
+                }
+                *reinterpret_cast<uint4*>(o + hgrp * 8) = make_uint4(w[0], w[1], w[2], w[3]);
               }
             }
           } else {  // EPI_SWIGLU: 32 columns = 4 groups of [g0..g3 | u0..u3] -> 16 outputs
@@ -364,4 +424,43 @@ extern "C" int rh3_gemm_w8a8_swiglu(const void* xq, int64_t lda, const void* wq,
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
   p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.status = device_status_word();
   return kind == RH3_KIND_F8 ? launch_gemm<1, EPI_SWIGLU>(ta, tb, p, stream) : launch_gemm<0, EPI_SWIGLU>(ta, tb, p, stream);
+}
+
+// ---- fp16 epilogues: the reference's VAE transformer-decoder GEMMs (custom_nodes/rapid_h3/csrc/vae_ops.cu:150-227
+// plain + bias and residual addcmul, :228-345 w1 + SwiGLU) ----
+extern "C" int rh3_vae_gemm(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws,
+                            const void* bias_f16, const void* rscale_f16, const void* resid_f16, int64_t ldr,
+                            int64_t M, int64_t N, int64_t K, void* out_f16, int64_t ldo, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (int e = gemm_common(xq, lda, wq, xs, ws, M, N, K, RH3_KIND_I8, &ta, &tb)) return e;
+  if (M == 0) return 0;
+  RH3_CHECK_ARG(bias_f16, "vae_gemm: bias is required (pass zeros for none)");
+  RH3_CHECK_ARG(out_f16 && ldo >= N && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out_f16) & 15) == 0,
+                "vae_gemm: out must be 16-byte aligned with a row stride >= N that is a multiple of 8");
+  RH3_CHECK_ARG((rscale_f16 == nullptr) == (resid_f16 == nullptr), "vae_gemm: rscale and resid come together");
+  RH3_CHECK_ARG(!resid_f16 || (ldr >= N && ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(resid_f16) & 15) == 0),
+                "vae_gemm: resid must be 16-byte aligned with a row stride >= N that is a multiple of 8");
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
+  p.bias_h = static_cast<const __half*>(bias_f16); p.rscale_h = static_cast<const __half*>(rscale_f16);
+  p.resid_h = static_cast<const __half*>(resid_f16); p.ldr = ldr;
+  p.out_h = static_cast<__half*>(out_f16); p.ldo = ldo; p.status = device_status_word();
+  return launch_gemm<0, EPI_F16>(ta, tb, p, stream);
+}
+
+extern "C" int rh3_vae_gemm_swiglu(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws,
+                                   const void* bias_f16, int64_t M, int64_t N, int64_t K, void* out_f16, int64_t ldo,
+                                   cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  if (int e = gemm_common(xq, lda, wq, xs, ws, M, N, K, RH3_KIND_I8, &ta, &tb)) return e;
+  RH3_CHECK_ARG(N % 16 == 0, "vae_gemm_swiglu: N=%lld must be a multiple of 16", (long long)N);
+  if (M == 0) return 0;
+  RH3_CHECK_ARG(bias_f16, "vae_gemm_swiglu: bias is required (pass zeros for none)");
+  RH3_CHECK_ARG(out_f16 && ldo >= N / 2 && ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out_f16) & 15) == 0,
+                "vae_gemm_swiglu: out must be 16-byte aligned with a row stride >= N/2 that is a multiple of 8");
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
+  p.bias_h = static_cast<const __half*>(bias_f16);
+  p.out_h = static_cast<__half*>(out_f16); p.ldo = ldo; p.status = device_status_word();
+  return launch_gemm<0, EPI_SWIGLU_F16>(ta, tb, p, stream);
 }
