@@ -322,14 +322,15 @@ __device__ __forceinline__ float warp_sum_xor(float v) {
 // exact quantizer steps without the conversion unit
 // ---------------------------------------------------------------------------------------------
 // int8 code of round_half_even(y / s) (|y / s| <= 127 by construction of s), returned in the low byte.
-// y * (1/s) is rounded by adding 1.5 * 2^23; only when the product lands within 1e-3 of a tie is the exact
-// IEEE quotient computed, so the code always equals the one a true division would give.
+// y * (1/s) is rounded by adding 1.5 * 2^23; only when the product lands within 2^-14 of a tie (its distance from
+// the exact quotient is at most 1.5e-5) is the exact IEEE quotient computed, so the code always equals the one a
+// true division would give.
 __device__ __forceinline__ uint32_t quant_code_i8(float y, float s, float inv) {
   const float kMagic = 12582912.f;
   const float yq = __fmul_rn(y, inv);
   float t = __fadd_rn(yq, kMagic);
   const float r = __fsub_rn(t, kMagic);
-  if (fabsf(fabsf(yq - r) - 0.5f) < 1e-3f) t = __fadd_rn(__fdiv_rn(y, s), kMagic);
+  if (fabsf(yq - r) > 0.5f - 6.103515625e-5f) t = __fadd_rn(__fdiv_rn(y, s), kMagic);
   return __float_as_uint(t);  // low byte = two's complement code
 }
 // e4m3 code of clamp(y / s, +-448) rounded to nearest even. The fast path converts y * (1/s); the exact
@@ -353,7 +354,10 @@ __device__ __forceinline__ uint2 quant8_i8(const float* y, float s, float inv) {
   for (int j = 0; j < 8; ++j) {
     const float yq = __fmul_rn(y[j], inv);
     t[j] = __fadd_rn(yq, kMagic);
-    near |= fabsf(__fsub_rn(yq, __fsub_rn(t[j], kMagic))) > 0.499f;  // |yq - round(yq)| <= 0.5 always
+    // |yq - round(yq)| <= 0.5 always. y * (1/s) differs from the exact quotient by at most 127 * 2^-23 = 1.5e-5
+    // (one rounding in 1/s, one in the product), so only values within 2^-14 of a tie can round differently;
+    // a wider window would send most warps down the division path (any of 256 values triggers it).
+    near |= fabsf(__fsub_rn(yq, __fsub_rn(t[j], kMagic))) > 0.5f - 6.103515625e-5f;
   }
   if (near) {
 #pragma unroll  // static indices: a rolled loop would push the caller's register array to local memory
