@@ -135,15 +135,18 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, float cc, fl
                                           uint64_t& lsum2) {
   const uint64_t cc2 = pack2(cc, cc), off2 = pack2(off, off);
   uint32_t w[8];
+  uint64_t ls0 = pack2(0.f, 0.f), ls1 = pack2(0.f, 0.f);  // two chains per chunk keep the adds off the critical path
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     float pa, pb, pc, pd;
     unpack2(fma2(pack2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), cc2, off2), pa, pb);
     unpack2(fma2(pack2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), cc2, off2), pc, pd);
     pa = ex2_approx(pa); pb = ex2_approx(pb); pc = ex2_approx(pc); pd = ex2_approx(pd);
-    lsum2 = add2(lsum2, add2(pack2(pa, pb), pack2(pc, pd)));
+    if (i & 1) ls1 = add2(ls1, add2(pack2(pa, pb), pack2(pc, pd)));
+    else ls0 = add2(ls0, add2(pack2(pa, pb), pack2(pc, pd)));
     w[i] = pack_e4m3x4(pa, pb, pc, pd);
   }
+  lsum2 = add2(lsum2, add2(ls0, ls1));
   *reinterpret_cast<uint4*>(p_row + (((2 * k) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
   *reinterpret_cast<uint4*>(p_row + (((2 * k + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
