@@ -387,8 +387,14 @@ def main():
         tflop = 4.0 * lq * lk * 128 * h / 1e12
         achieved = tflop / (ms_launch / 1e3)
         peak = 2.0 * pk["bf16_tflops_sustained"]
+        # DRAM bytes of one launch: dram__bytes_read.sum + dram__bytes_write.sum of this kernel captured with ncu on
+        # the one-block workload (Lq = Lk = 36,436, H = 32: 451.3 MB read + 268.2 MB written), scaled to this launch
+        # by its operand + output bytes (which that capture matched within 4 %)
+        def alg_bytes(lq_, lk_, h_):
+            return h_ * 128 * (lq_ + 2 * lk_) + h_ * 128 * 2 * lq_
+        traffic = 719.53e6 * alg_bytes(lq, lk, h) / alg_bytes(36436, 36436, 32)
         roof = {"bound": "tensor", "kernel": "attn_int8_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None, "ms_per_launch": ms_launch, "launches": len(self_attn),
+                "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu, scaled)", "ms_per_launch": ms_launch, "launches": len(self_attn),
                 "share_of_step": sum(t for t, *_ in self_attn) / (ms_step * args.steps),
                 "peak_note": f"2 x {pk['source']} sustained cuBLAS bf16 ({pk['bf16_tflops_sustained']} TF/s): "
                              "8-bit operands run at twice the bf16 rate; nominal dense INT8/FP8 peak is 4500",
