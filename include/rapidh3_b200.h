@@ -167,6 +167,23 @@ int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const void* gamma, 
 int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t T, int64_t H, int64_t W, int64_t C,
                           cudaStream_t stream);
 
+/* ---- sequence parallelism: the two exchanges of Ulysses attention done by the kernels themselves ----
+ * No reference counterpart (the reference is single-GPU). Both write with plain stores into buffers that may be
+ * on peer GPUs (pointers obtained by the host through CUDA IPC / symmetric memory); neither waits on a peer:
+ * the caller orders producers and consumers with a stream-ordered barrier (e.g. a one-element all-reduce).
+ * rh3_rope_scatter_heads: RMSNorm + 3-D RoPE of q and k (as rh3_rmsnorm_rope3d) of this rank's S tokens, rows
+ *   [S, 3*H*128] = q | k | v; head h goes to dst[h / (H/P)], laid out [total tokens, 3, (H/P)*128], at token
+ *   row0 + s. v is copied unchanged.
+ * rh3_attn_int8_scatter: rh3_attn_int8 whose output rows [dst_start[r], dst_start[r+1]) are stored to
+ *   dst[r] + (row - dst_start[r]) * o_ss + head * o_sh (1 <= n_dst <= 8, dst_start[0] = 0, dst_start[n_dst] >= Lq). */
+int rh3_rope_scatter_heads(const void* qkv, int64_t ld, int64_t S, int64_t H, int64_t P, int64_t row0,
+                           const void* q_weight, const void* k_weight, float eps, const void* rope_table,
+                           void* const* dst, cudaStream_t stream);
+int rh3_attn_int8_scatter(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                          const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk,
+                          int64_t Lk_pad, int64_t H, float softmax_scale, void* const* dst, const int64_t* dst_start,
+                          int64_t n_dst, int64_t o_ss, int64_t o_sh, cudaStream_t stream);
+
 /* ---- fp16 ops of the VAE transformer decoder (the callers of the int8 path at fp16 activations) ----
  * rh3_vae_out_quant: o [B, H, S, D] fp16 head-major attention output -> q int8 [B*S, H*D], scales fp32 [B*S]:
  *   nan_to_num on load, H256 rotation in comfy-kitchen's stage order, int8 with value / scale / quotient rounded

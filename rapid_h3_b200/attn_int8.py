@@ -7,6 +7,7 @@ head (K mean-smoothed), V e4m3 per (head, channel), fp32 base-2 online softmax, 
 `config`, `rotate` and `smooth_v` of the reference are accepted for signature compatibility;
 K and V smoothing are always on and the Hadamard rotation is not part of this variant.
 """
+import ctypes
 import math
 from dataclasses import dataclass
 
@@ -102,22 +103,34 @@ def int8_prepass(q, k, v):
     return Prepass(q8, qs, k8, ks, vt, vscale, vmean, kmean, lq, lk)
 
 
-def attention_pre(pre, scale=None, out=None):
-    """Main kernel on pre-quantized operands -> out [Lq, H, 128] bf16 (strided `out` allowed)."""
+def attention_pre(pre, scale=None, out=None, scatter=None):
+    """Main kernel on pre-quantized operands -> out [Lq, H, 128] bf16 (strided `out` allowed).
+    `scatter` = (device pointers, row starts [n+1], row stride, head stride) sends query rows
+    [start[r], start[r+1]) to buffer r instead (rh3_attn_int8_scatter); nothing is returned then."""
     h = pre.q8.shape[0]
     if scale is None:
         scale = 1.0 / math.sqrt(D)
-    if out is None:
-        out = torch.empty((pre.lq, h, D), device=pre.q8.device, dtype=torch.bfloat16)
-    _check_qkv(out, "out")
-    if out.shape[0] != pre.lq or out.shape[1] != h:
-        raise RuntimeError("out must be [Lq, H, 128]")
+    if scatter is None:
+        if out is None:
+            out = torch.empty((pre.lq, h, D), device=pre.q8.device, dtype=torch.bfloat16)
+        _check_qkv(out, "out")
+        if out.shape[0] != pre.lq or out.shape[1] != h:
+            raise RuntimeError("out must be [Lq, H, 128]")
     if TIMING is not None:
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
-    _lib.call("rh3_attn_int8", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
-              pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
-              pre.k8.shape[1], h, float(scale), out.data_ptr(), out.stride(0), out.stride(1), _lib.stream())
+    if scatter is None:
+        _lib.call("rh3_attn_int8", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
+                  pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
+                  pre.k8.shape[1], h, float(scale), out.data_ptr(), out.stride(0), out.stride(1), _lib.stream())
+    else:
+        ptrs, starts, o_ss, o_sh = scatter
+        n = len(ptrs)
+        c_ptrs = (ctypes.c_void_p * n)(*ptrs)
+        c_starts = (ctypes.c_int64 * (n + 1))(*starts)
+        _lib.call("rh3_attn_int8_scatter", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
+                  pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
+                  pre.k8.shape[1], h, float(scale), c_ptrs, c_starts, n, o_ss, o_sh, _lib.stream())
     if TIMING is not None:
         ev1.record()
         TIMING.append((ev0, ev1, pre.lq, pre.lk, h))

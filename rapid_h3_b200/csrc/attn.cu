@@ -55,6 +55,11 @@ struct AttnParams {
   int Lq, Lk, Lq_pad, Lk_pad, H;
   float sl2;  // softmax_scale * log2(e)
   int* status;
+  // sequence-parallel output: query rows [dst_start[r], dst_start[r+1]) go to dst_ptr[r] (this GPU's or a peer's
+  // memory), addressed relative to the start of the range; n_dst == 0 selects the single buffer `out`
+  int n_dst;
+  long long dst_start[9];
+  __nv_bfloat16* dst_ptr[8];
 };
 
 struct __align__(8) AttnSmemTail {
@@ -381,7 +386,14 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       const float inv_l = __fdiv_rn(1.f, l);
       const float* vs = p.vscale + h * HD;
       const float* vm = p.vmean + h * HD;
-      __nv_bfloat16* o = p.out + q_row * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
+      __nv_bfloat16* o;
+      if (p.n_dst == 0) {
+        o = p.out + q_row * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
+      } else {
+        int r = 0;
+        while (r + 1 < p.n_dst && q_row >= p.dst_start[r + 1]) ++r;
+        o = p.dst_ptr[r] + (q_row - p.dst_start[r]) * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
+      }
 #pragma unroll 1
       for (int c = 0; c < 16; ++c) {
         uint32_t r[8];
@@ -421,19 +433,36 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 using namespace rh3;
 
-extern "C" int rh3_attn_int8(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
-                             const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk,
-                             int64_t Lk_pad, int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh,
-                             cudaStream_t stream) {
+namespace {
+int attn_launch(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt, const float* vscale,
+                const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk, int64_t Lk_pad, int64_t H,
+                float softmax_scale, void* out, void* const* dst, const int64_t* dst_start, int n_dst, int64_t o_ss,
+                int64_t o_sh, cudaStream_t stream) {
   RH3_CHECK_ARG(Lq > 0 && Lk > 0 && H > 0 && H < 65536, "attn_int8: bad shape Lq=%lld Lk=%lld H=%lld", (long long)Lq,
                 (long long)Lk, (long long)H);
   RH3_CHECK_ARG(Lq_pad >= Lq && Lk_pad >= Lk && Lq_pad % 256 == 0 && Lk_pad % 128 == 0,
                 "attn_int8: Lq_pad must be a multiple of 256 and Lk_pad a multiple of 128, covering Lq / Lk");
   RH3_CHECK_ARG(H * Lq_pad < (1ll << 31) && H * Lk_pad < (1ll << 31), "attn_int8: H * Lpad too large");
-  RH3_CHECK_ARG(q8 && qs && k8 && ks && vt && vscale && vmean && out, "attn_int8: null pointer");
-  RH3_CHECK_ARG(aligned16(q8) && aligned16(k8) && aligned16(vt) && aligned16(out) && o_ss % 8 == 0 && o_sh % 8 == 0,
+  RH3_CHECK_ARG(q8 && qs && k8 && ks && vt && vscale && vmean, "attn_int8: null pointer");
+  RH3_CHECK_ARG(aligned16(q8) && aligned16(k8) && aligned16(vt) && o_ss % 8 == 0 && o_sh % 8 == 0,
                 "attn_int8: operands must be 16-byte aligned, output strides multiples of 8 elements");
   RH3_CHECK_ARG(softmax_scale > 0.f, "attn_int8: softmax scale must be positive");
+  AttnParams p{};
+  if (n_dst == 0) {
+    RH3_CHECK_ARG(out && aligned16(out), "attn_int8: out must be a 16-byte aligned pointer");
+    p.out = static_cast<__nv_bfloat16*>(out);
+  } else {
+    RH3_CHECK_ARG(n_dst >= 1 && n_dst <= 8 && dst && dst_start, "attn_int8_scatter: 1..8 destinations");
+    RH3_CHECK_ARG(dst_start[0] == 0 && dst_start[n_dst] >= Lq, "attn_int8_scatter: ranges must cover [0, Lq)");
+    for (int r = 0; r < n_dst; ++r) {
+      RH3_CHECK_ARG(dst[r] && aligned16(dst[r]) && dst_start[r + 1] >= dst_start[r],
+                    "attn_int8_scatter: destination %d is null, misaligned or its range is negative", r);
+      p.dst_ptr[r] = static_cast<__nv_bfloat16*>(dst[r]);
+      p.dst_start[r] = dst_start[r];
+    }
+    p.dst_start[n_dst] = dst_start[n_dst];
+    p.n_dst = n_dst;
+  }
   CUtensorMap tq, tk, tv;
   if (int e = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q8, HD, H * Lq_pad, HD, HD, QG * BQ,
                            CU_TENSOR_MAP_SWIZZLE_128B))
@@ -444,9 +473,8 @@ extern "C" int rh3_attn_int8(const void* q8, const float* qs, const void* k8, co
   if (int e = make_tmap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, vt, Lk_pad, H * HD, Lk_pad, BKV, HD,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return e;
-  AttnParams p{};
   p.qs = qs; p.ks = ks; p.vscale = vscale; p.vmean = vmean;
-  p.out = static_cast<__nv_bfloat16*>(out); p.o_ss = o_ss; p.o_sh = o_sh;
+  p.o_ss = o_ss; p.o_sh = o_sh;
   p.Lq = (int)Lq; p.Lk = (int)Lk; p.Lq_pad = (int)Lq_pad; p.Lk_pad = (int)Lk_pad; p.H = (int)H;
   p.sl2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
   p.status = device_status_word();
@@ -458,4 +486,25 @@ extern "C" int rh3_attn_int8(const void* q8, const float* qs, const void* k8, co
   kern<<<grid, ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
   return check_cuda(cudaGetLastError(), "attn_int8 launch");
 }
+}  // namespace
 
+extern "C" int rh3_attn_int8(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                             const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk,
+                             int64_t Lk_pad, int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh,
+                             cudaStream_t stream) {
+  return attn_launch(q8, qs, k8, ks, vt, vscale, vmean, Lq, Lq_pad, Lk, Lk_pad, H, softmax_scale, out, nullptr, nullptr,
+                     0, o_ss, o_sh, stream);
+}
+
+// The same kernel with its output rows scattered over up to 8 buffers: rows [dst_start[r], dst_start[r+1]) go to
+// dst[r] + (row - dst_start[r]) * o_ss + head * o_sh. The buffers may live on peer GPUs (plain stores over NVLink):
+// this is the head -> token exchange of sequence parallelism done by the attention epilogue itself.
+extern "C" int rh3_attn_int8_scatter(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                                     const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk,
+                                     int64_t Lk_pad, int64_t H, float softmax_scale, void* const* dst,
+                                     const int64_t* dst_start, int64_t n_dst, int64_t o_ss, int64_t o_sh,
+                                     cudaStream_t stream) {
+  RH3_CHECK_ARG(n_dst >= 1 && n_dst <= 8, "attn_int8_scatter: n_dst=%lld must be 1..8", (long long)n_dst);
+  return attn_launch(q8, qs, k8, ks, vt, vscale, vmean, Lq, Lq_pad, Lk, Lk_pad, H, softmax_scale, nullptr, dst,
+                     dst_start, (int)n_dst, o_ss, o_sh, stream);
+}

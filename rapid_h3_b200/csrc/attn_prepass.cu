@@ -33,18 +33,12 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float* x) {
 // ---------------------------------------------------------------------------------------------
 // RMSNorm + 3-D RoPE. One warp per (token, head) row; lane l owns channels 4l..4l+3.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_ss,
-                                                           int64_t x_sh, __nv_bfloat16* __restrict__ y, int64_t y_ss,
-                                                           int64_t y_sh, int64_t S, int H,
-                                                           const __nv_bfloat16* __restrict__ w, float eps,
-                                                           const __nv_bfloat16* __restrict__ tab) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t g = static_cast<int64_t>(blockIdx.x) * 8 + warp;
-  if (g >= S * H) return;
-  const int64_t s = g / H;
-  const int h = static_cast<int>(g - s * H);
+// RMSNorm + rope of the four channels lane*4..lane*4+3 of one (token, head) row; returns the packed bf16 result.
+__device__ __forceinline__ uint2 rmsnorm_rope_row(const __nv_bfloat16* __restrict__ xrow,
+                                                  const __nv_bfloat16* __restrict__ w, float eps,
+                                                  const __nv_bfloat16* __restrict__ tab_row, int lane) {
   float v[4], wv[4];
-  load4(x + s * x_ss + h * x_sh + lane * 4, v);
+  load4(xrow + lane * 4, v);
   load4(w + lane * 4, wv);
   float ss = 0.f;
 #pragma unroll
@@ -55,7 +49,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* 
 #pragma unroll
   for (int j = 0; j < 4; ++j) n[j] = bf16_round(__fmul_rn(__fmul_rn(r, v[j]), wv[j]));
   float o[4] = {n[0], n[1], n[2], n[3]};
-  if (tab != nullptr) {
+  if (tab_row != nullptr) {
     // partner lane holds the other half of the rotary pair (channels +-48 = 12 lanes away)
     const int partner = lane < 12 ? lane + 12 : (lane < 24 ? lane - 12 : lane);
     float pn[4];
@@ -63,7 +57,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* 
     for (int j = 0; j < 4; ++j) pn[j] = __shfl_sync(0xffffffffu, n[j], partner);
     if (lane < 24) {
       const int i0 = (lane < 12 ? lane : lane - 12) * 4;  // index of the pair in the table row
-      const __nv_bfloat16* t = tab + (s * 48 + i0) * 4;
+      const __nv_bfloat16* t = tab_row + i0 * 4;
       const uint4 t0 = __ldg(reinterpret_cast<const uint4*>(t));
       const uint4 t1 = __ldg(reinterpret_cast<const uint4*>(t + 8));
       const uint32_t tw[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
@@ -78,7 +72,56 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* 
       }
     }
   }
-  *reinterpret_cast<uint2*>(y + s * y_ss + h * y_sh + lane * 4) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+  return make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+}
+
+__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_ss,
+                                                           int64_t x_sh, __nv_bfloat16* __restrict__ y, int64_t y_ss,
+                                                           int64_t y_sh, int64_t S, int H,
+                                                           const __nv_bfloat16* __restrict__ w, float eps,
+                                                           const __nv_bfloat16* __restrict__ tab) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t g = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  if (g >= S * H) return;
+  const int64_t s = g / H;
+  const int h = static_cast<int>(g - s * H);
+  const uint2 o = rmsnorm_rope_row(x + s * x_ss + h * x_sh, w, eps, tab ? tab + s * 48 * 4 : nullptr, lane);
+  *reinterpret_cast<uint2*>(y + s * y_ss + h * y_sh + lane * 4) = o;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sequence-parallel form: RMSNorm + RoPE of q and k fused with the token -> head exchange. The qkv rows of
+// this rank's tokens are normalised, rotated and stored straight into the buffer of the rank that owns the
+// head (its own memory or a peer's over NVLink): dst[r] is [total tokens, 3, (H/P)*128] on rank r, row0 is
+// the global index of this rank's first token. Plain stores only; ordering against the readers is the
+// caller's stream-ordered barrier. One warp per (token, head): q row, k row, v row (copied unchanged).
+// ---------------------------------------------------------------------------------------------
+struct ScatterDst {
+  __nv_bfloat16* ptr[8];
+};
+
+__global__ void __launch_bounds__(256) rope_scatter_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t ld, int64_t S,
+                                                           int H, int heads_per_rank, int64_t row0,
+                                                           const __nv_bfloat16* __restrict__ qw,
+                                                           const __nv_bfloat16* __restrict__ kw, float eps,
+                                                           const __nv_bfloat16* __restrict__ tab, const ScatterDst dst) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t g = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  if (g >= S * H) return;
+  const int64_t s = g / H;
+  const int h = static_cast<int>(g - s * H);
+  const int r = h / heads_per_rank, hh = h - r * heads_per_rank;
+  const int64_t w = static_cast<int64_t>(heads_per_rank) * D;
+  const __nv_bfloat16* row = qkv + s * ld + h * D;
+  const __nv_bfloat16* tab_row = tab ? tab + s * 48 * 4 : nullptr;
+  __nv_bfloat16* out = dst.ptr[r] + (row0 + s) * 3 * w + hh * D + lane * 4;
+  const int64_t hd = static_cast<int64_t>(H) * D;
+  const uint2 qo = rmsnorm_rope_row(row, qw, eps, tab_row, lane);
+  const uint2 ko = rmsnorm_rope_row(row + hd, kw, eps, tab_row, lane);
+  const uint2 vo = __ldg(reinterpret_cast<const uint2*>(row + 2 * hd + lane * 4));
+  *reinterpret_cast<uint2*>(out) = qo;
+  *reinterpret_cast<uint2*>(out + w) = ko;
+  *reinterpret_cast<uint2*>(out + 2 * w) = vo;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -247,6 +290,30 @@ extern "C" int rh3_rmsnorm_rope3d(const void* x, int64_t x_ss, int64_t x_sh, voi
       static_cast<const __nv_bfloat16*>(x), x_ss, x_sh, static_cast<__nv_bfloat16*>(y), y_ss, y_sh, S, (int)H,
       static_cast<const __nv_bfloat16*>(weight), eps, static_cast<const __nv_bfloat16*>(rope_table));
   return check_cuda(cudaGetLastError(), "rmsnorm_rope3d launch");
+}
+
+extern "C" int rh3_rope_scatter_heads(const void* qkv, int64_t ld, int64_t S, int64_t H, int64_t P, int64_t row0,
+                                      const void* q_weight, const void* k_weight, float eps, const void* rope_table,
+                                      void* const* dst, cudaStream_t stream) {
+  RH3_CHECK_ARG(S >= 0 && H > 0 && H < 65536 && P > 0 && P <= 8 && H % P == 0 && row0 >= 0,
+                "rope_scatter_heads: bad shape S=%lld H=%lld P=%lld", (long long)S, (long long)H, (long long)P);
+  if (S == 0) return 0;
+  RH3_CHECK_ARG(qkv && q_weight && k_weight && dst, "rope_scatter_heads: null pointer");
+  RH3_CHECK_ARG(aligned(qkv, 8) && aligned(q_weight, 8) && aligned(k_weight, 8) && ld % 4 == 0 && ld >= 3 * H * D,
+                "rope_scatter_heads: rows must be 8-byte aligned and hold q | k | v");
+  RH3_CHECK_ARG(!rope_table || aligned(rope_table, 16), "rope_scatter_heads: rope table must be 16-byte aligned");
+  ScatterDst d{};
+  for (int r = 0; r < P; ++r) {
+    RH3_CHECK_ARG(dst[r] && aligned(dst[r], 8), "rope_scatter_heads: destination %d is null or misaligned", r);
+    d.ptr[r] = static_cast<__nv_bfloat16*>(dst[r]);
+  }
+  const int64_t rows = S * H;
+  RH3_CHECK_ARG((rows + 7) / 8 < (1ll << 31), "rope_scatter_heads: too many rows");
+  rope_scatter_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(qkv), ld, S, (int)H, (int)(H / P), row0,
+      static_cast<const __nv_bfloat16*>(q_weight), static_cast<const __nv_bfloat16*>(k_weight), eps,
+      static_cast<const __nv_bfloat16*>(rope_table), d);
+  return check_cuda(cudaGetLastError(), "rope_scatter_heads launch");
 }
 
 extern "C" int64_t rh3_attn_kv_stats_scratch_bytes(int64_t L, int64_t H) {

@@ -159,18 +159,27 @@ class FusedBlock:
         qkv = cf.int8_gemm(xq, xs, qw.q, qw.scale)
         rec("qkv", qkv)
         q, k, v = (t.view(s, a.heads, a.head_dim) for t in qkv.split(hd, dim=-1))
-        attn_int8.rms_rope(q, self._norm_w(a.q_norm), a.q_norm.eps, tab, out=q)
-        attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
-        rec("qkv_rr", qkv)
-        if sp is None:
-            o = attn_int8.attention(q, k, v)                       # [S, H, 128] token-major
-            rec("attn_out", o)
-            oq, os_ = tq.rot_quant_rows_i8(o.view(s, hd), rotate=rot)
-        else:
-            qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
-            og = attn_int8.attention(qg, kg, vg)
-            o = sp.heads_to_tokens(og)                              # [P, S_local, (H/P)*128] group-major
+        if sp is not None and sp.fused:
+            # both exchanges done by the kernels: rope + scatter to the head owners, attention epilogue scatters back
+            if a.q_norm.eps != a.k_norm.eps:
+                raise NotImplementedError("fused exchange: q and k norms must share eps")
+            qg, kg, vg = sp.rope_scatter(qkv, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps,
+                                         tab.contiguous())
+            o = sp.attention_scatter(qg, kg, vg)                    # [P, S_local, (H/P)*128] group-major
             oq, os_ = tq.quant_groups_i8(o, rotate=rot)
+        else:
+            attn_int8.rms_rope(q, self._norm_w(a.q_norm), a.q_norm.eps, tab, out=q)
+            attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
+            rec("qkv_rr", qkv)
+            if sp is None:
+                o = attn_int8.attention(q, k, v)                       # [S, H, 128] token-major
+                rec("attn_out", o)
+                oq, os_ = tq.rot_quant_rows_i8(o.view(s, hd), rotate=rot)
+            else:
+                qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
+                og = attn_int8.attention(qg, kg, vg)
+                o = sp.heads_to_tokens(og)                              # [P, S_local, (H/P)*128] group-major
+                oq, os_ = tq.quant_groups_i8(o, rotate=rot)
         del qkv, q, k, v
         x = self._gemm_gated(oq, os_, self.out_q, x, gate_msa, mod_segments)
         rec("x_attn", x)

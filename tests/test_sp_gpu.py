@@ -33,16 +33,37 @@ def _worker(rank, world, port, ret):
         sp = r.sp.Ulysses(grid[0] * grid[1] * grid[2] + n_audio)
         v, a = rt.step(*inputs, sp=sp)
         r._lib.check_status()
-        ret[rank] = bool(torch.equal(v, ref_v) and torch.equal(a, ref_a))
+        ok = bool(torch.equal(v, ref_v) and torch.equal(a, ref_a))
+        # the same step with both exchanges done by the kernels (stores into peer buffers + stream-ordered barriers)
+        how = sp.enable_fused(cfg.heads, 128, torch.device("cuda", rank))
+        for _ in range(2):  # twice: the exchange buffers are reused from call to call
+            v2, a2 = rt.step(*inputs, sp=sp)
+        r._lib.check_status()
+        ret[rank] = (ok, bool(torch.equal(v2, ref_v) and torch.equal(a2, ref_a)), how)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.timeout(600)
+@pytest.mark.timeout(300)
 def test_two_rank_step_equals_single_gpu_step():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
-    assert dict(ret) == {0: True, 1: True}
+    out = dict(ret)
+    print("peer buffers via", out[0][2])
+    assert [out[r][:2] for r in (0, 1)] == [(True, True), (True, True)], out
+
+
+@pytest.mark.timeout(300)
+def test_fused_exchange_kernels_on_one_rank():
+    """World size 1: the scatter kernels write this GPU's own buffers, so their addressing (token rows, head
+    groups, q | k | v planes, output ranges) is checked against the unfused step without a second GPU."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    import torch.multiprocessing as mp
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(1, _free_port(), ret), nprocs=1, join=True)
+    out = dict(ret)
+    assert out[0][:2] == (True, True), out
