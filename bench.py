@@ -300,6 +300,9 @@ def main():
     ap.add_argument("--mode", default="int8_rowwise", choices=["int8_rowwise", "int8_rot"],
                     help="linear recipe of the step: un-rotated row-wise int8 (the benchmark configuration) or the "
                          "H256-rotated recipe")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "fused"],
+                    help="N > 1: token <-> head exchanges as NCCL all-to-all, or done by the rope and attention kernels "
+                         "themselves (stores into peer buffers)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -328,6 +331,11 @@ def main():
     rt = r.step.H3Runtime.random(cfg, seed=0, device=f"cuda:{local}", mode=args.mode)
     s_total = grid[0] * grid[1] * grid[2] + n_audio
     sp = r.sp.Ulysses(s_total) if world > 1 else None
+    exchange = "none"
+    if sp is not None:
+        exchange = "nccl all_to_all_single"
+        if args.exchange == "fused":
+            exchange = "kernel stores into peer buffers (" + sp.enable_fused(cfg.heads, cfg.head_dim, torch.device("cuda", local)) + ")"
     host = [t.pin_memory() for t in r.step.make_inputs(cfg, grid, n_audio, batch, text_len, seed=0)]
     dev = [t.cuda(non_blocking=True) for t in host]
     rope_dev = dev[3]
@@ -404,7 +412,7 @@ def main():
     rec = {"metric": "H3 DiT step seconds @768x1344x141f", "value": ms_step / 1e3, "unit": "s/step", "n_gpus": world,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False,
            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-           "config": dict(workload_config(args.workload, world), linear_mode=args.mode), "clocks": clocks,
+           "config": dict(workload_config(args.workload, world), linear_mode=args.mode, exchange=exchange), "clocks": clocks,
            "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
            "gpu_launches": launches, "roofline": roof}
     if rank == 0:

@@ -6,6 +6,7 @@ The reference is single-GPU (its only mention of sequence parallelism is a dropp
 docs/kernels.md:180), so this module has no reference counterpart.
 """
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -51,6 +52,8 @@ class PeerBuffers:
         nbytes = (int(nbytes) + 255) // 256 * 256
         self.how, self._keep = None, []
         errors = []
+        # plain peer mappings are all that is needed: keep the buffers out of NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         try:
             import torch.distributed._symmetric_memory as symm
             t = symm.empty(nbytes, dtype=torch.uint8, device=device)
