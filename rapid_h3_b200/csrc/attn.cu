@@ -217,7 +217,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       for (int j = 0; j < n_kv; ++j) {
         const int stage = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
-        if (!mbar_wait(&tail->kv_empty[stage], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY)) break;
+        if (!mbar_wait_relaxed(&tail->kv_empty[stage], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY, 400)) break;
         uint8_t* sk = sKV + stage * 2 * TILE_BYTES;
         mbar_arrive_expect_tx(&tail->kv_full[stage], 2 * TILE_BYTES);
         tma_load_2d(sk, &tma_k, 0, h * p.Lk_pad + j * BKV, &tail->kv_full[stage]);
@@ -247,9 +247,9 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) {
           const int ns = (j + 1) % KV_STAGES;
-          ok = mbar_wait(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
+          ok = mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 32);
           for (int g = 0; g < QG && ok; ++g) {
-            ok = mbar_wait(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
+            ok = mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 32);
             if (ok) {
               tc_fence_after();
               issue_qk(g, j + 1);
@@ -260,7 +260,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         const int stage = j % KV_STAGES;
         const uint32_t v_addr = smem_u32(sKV + stage * 2 * TILE_BYTES + TILE_BYTES);
         for (int g = 0; g < QG && ok; ++g) {
-          ok = mbar_wait(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY);
+          ok = mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 32);
           if (!ok) break;
           tc_fence_after();
           const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);

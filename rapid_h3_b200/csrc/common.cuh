@@ -87,6 +87,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// The same bounded wait for roles that share a scheduler with busy compute warps (a TMA producer, an MMA issuer):
+// between polls the thread sleeps `ns` nanoseconds, so its polling does not take issue slots from those warps.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code, unsigned ns) {
+  for (uint32_t it = 0; it < (1u << 24); ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(ns);
+    if (it > 64 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  if (status) atomicCAS(status, 0, code);
+  return false;
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), CTA-local destination, completion on an mbarrier
 // ---------------------------------------------------------------------------------------------
