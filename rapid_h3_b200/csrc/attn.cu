@@ -247,9 +247,9 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) {
           const int ns = (j + 1) % KV_STAGES;
-          ok = mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 32);
+          ok = mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 64);
           for (int g = 0; g < QG && ok; ++g) {
-            ok = mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 32);
+            ok = mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64);
             if (ok) {
               tc_fence_after();
               issue_qk(g, j + 1);
@@ -260,7 +260,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         const int stage = j % KV_STAGES;
         const uint32_t v_addr = smem_u32(sKV + stage * 2 * TILE_BYTES + TILE_BYTES);
         for (int g = 0; g < QG && ok; ++g) {
-          ok = mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 32);
+          ok = mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 64);
           if (!ok) break;
           tc_fence_after();
           const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);
@@ -314,7 +314,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       }
       const float b0 = __fmul_rn(kMagic, c0), b1 = __fmul_rn(kMagic, c1);
       const int valid = min(BKV, p.Lk - j * BKV);
-      if (!mbar_wait(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) { ok = false; break; }
+      if (!mbar_wait_relaxed(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_FULL, 32)) { ok = false; break; }
       tc_fence_after();
       // ---- the whole row of S (128 raw values) into registers, once ----
       uint32_t r0[32], r1[32], r2[32], r3[32];
@@ -348,7 +348,7 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       const bool grow = j > 0 && M_new > M;
       if (j > 0) {
         // P.V of the previous tile has finished: O is complete up to tile j-1 and the P buffer is free
-        if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) { ok = false; break; }
+        if (!mbar_wait_relaxed(pv_done, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE, 32)) { ok = false; break; }
         if (__any_sync(0xffffffffu, grow)) {
           tc_fence_after();
           const float f = grow ? ex2_approx(M - M_new) : 1.f;  // exact power of two
