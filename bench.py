@@ -300,9 +300,10 @@ def main():
     ap.add_argument("--mode", default="int8_rowwise", choices=["int8_rowwise", "int8_rot"],
                     help="linear recipe of the step: un-rotated row-wise int8 (the benchmark configuration) or the "
                          "H256-rotated recipe")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "fused"],
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "fused", "auto"],
                     help="N > 1: token <-> head exchanges as NCCL all-to-all, or done by the rope and attention kernels "
-                         "themselves (stores into peer buffers)")
+                         "themselves (stores into peer buffers); auto = fused, falling back to nccl if the peer "
+                         "buffers cannot be set up")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -334,8 +335,14 @@ def main():
     exchange = "none"
     if sp is not None:
         exchange = "nccl all_to_all_single"
-        if args.exchange == "fused":
-            exchange = "kernel stores into peer buffers (" + sp.enable_fused(cfg.heads, cfg.head_dim, torch.device("cuda", local)) + ")"
+        if args.exchange in ("fused", "auto"):
+            try:
+                how = sp.enable_fused(cfg.heads, cfg.head_dim, torch.device("cuda", local))
+                exchange = f"kernel stores into peer buffers ({how})"
+            except Exception as e:  # noqa: BLE001
+                if args.exchange == "fused":
+                    raise
+                print(f"[bench] peer buffers unavailable ({type(e).__name__}: {e}); using NCCL all-to-all", file=sys.stderr)
     host = [t.pin_memory() for t in r.step.make_inputs(cfg, grid, n_audio, batch, text_len, seed=0)]
     dev = [t.cuda(non_blocking=True) for t in host]
     rope_dev = dev[3]

@@ -167,6 +167,12 @@ int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const void* gamma, 
 int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t T, int64_t H, int64_t W, int64_t C,
                           cudaStream_t stream);
 
+/* Second int8 pass of the text encoder's `int8_rot` linears on its outlier rows: for i < n and r = rows[i],
+ * q2[i], s2[i] = int8 row quantizer of rotate(x[r]) - q1[r] * s1[r]  (x fp32 [*, K], q1 / s1 the first pass's codes and
+ * scales). Replaces the torch expression of te_quant._TELinear.__call__ (custom_nodes/rapid_h3/te_quant.py:96-105). */
+int rh3_rot_residual_quant_rows_i8(const float* x, int64_t ldx, const void* q1, int64_t ldq1, const float* s1,
+                                   const int32_t* rows, int64_t n, int64_t K, void* q2, float* s2, cudaStream_t stream);
+
 /* ---- sequence parallelism: the two exchanges of Ulysses attention done by the kernels themselves ----
  * No reference counterpart (the reference is single-GPU). Both write with plain stores into buffers that may be
  * on peer GPUs (pointers obtained by the host through CUDA IPC / symmetric memory); neither waits on a peer:

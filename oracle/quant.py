@@ -108,3 +108,10 @@ def swiglu_rot_quant_rows_i8(x):
 def norm_mod_rot_quant_rows_i8(x, weight, eps, idx, shift, scale):
     """int8 of rotate(rms_norm(x) * w * (1 + scale[idx]) + shift[idx]) (triton_fp8.py:442-446)."""
     return _quant_fp32_rows(rotate256(norm_mod(x, weight, eps, idx, shift, scale)))
+
+
+def rot_residual_quant_rows_i8(x, q1, s1, rows):
+    """Second pass of the text encoder's int8_rot linear on rows `rows` (te_quant.py:100-103):
+    r = rotate(x[rows]) - q1[rows] * s1[rows] in fp32 (x fp32), then the int8 row quantizer."""
+    r = rotate256(x[rows].float()) - q1[rows].float() * s1[rows].reshape(-1, 1)
+    return _quant_fp32_rows(r)

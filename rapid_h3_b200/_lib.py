@@ -30,6 +30,7 @@ SIGNATURES = {
     "rh3_swiglu_rot_quant_rows_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_rot_quant_groups_i8": [_P, _I64, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_norm_mod_rot_quant_rows_i8": [_P, _I64, _P, _F, _P, _P, _P, _I64, _I64, _I64, _P, _I64, _P, _P],
+    "rh3_rot_residual_quant_rows_i8": [_P, _I64, _P, _I64, _P, _P, _I64, _I64, _P, _P, _P],
     "rh3_rope_scatter_heads": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _F, _P, _P, _P],
     "rh3_attn_int8_scatter": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _P, _I64, _I64, _I64, _P],
     "rh3_vae_out_quant": [_P, _I64, _I64, _I64, _I64, _P, _P, _P],

@@ -242,6 +242,49 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
   }  // rows of this CTA
 }
 
+// Second int8 pass on the quantization residual of selected rows (the text encoder's outlier rows):
+//   r = rotate(x[rows[i]]) - q1[rows[i]] * s1[rows[i]]   (x fp32, so the residual also carries the bf16 rounding
+//   of the first pass's input), then the plain int8 row quantizer on r. One CTA of K/8 threads per selected row.
+// (reference: custom_nodes/rapid_h3/te_quant.py:96-105)
+template <int T>
+__global__ void __launch_bounds__(T) rot_residual_quant_kernel(const float* __restrict__ x, int64_t ldx,
+                                                               const int8_t* __restrict__ q1, int64_t ldq1,
+                                                               const float* __restrict__ s1,
+                                                               const int32_t* __restrict__ rows, int64_t n, int K,
+                                                               int8_t* __restrict__ q2, float* __restrict__ s2) {
+  __shared__ float red[T / 32];
+  const int tid = threadIdx.x;
+  const int col = tid << 3;
+  const bool active = col < K;
+  for (int64_t i = blockIdx.x; i < n; i += gridDim.x) {
+    const int64_t r = rows[i];
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (active) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(x + r * ldx + col));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(x + r * ldx + col + 4));
+      v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    }
+    if (tid - (tid & 31) < (K >> 3)) rotate256(v, tid & 31);
+    if (active) {
+      const uint2 c = __ldg(reinterpret_cast<const uint2*>(q1 + r * ldq1 + col));
+      const float sc = s1[r];
+      const int8_t* cb = reinterpret_cast<const int8_t*>(&c);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __fsub_rn(v[j], __fmul_rn(static_cast<float>(cb[j]), sc));
+    }
+    float am = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(v[j]));
+    am = block_max<T>(am, red);
+    const float s = fmaxf(__fdiv_rn(am, 127.f), 1e-12f);
+    const float inv = __fdiv_rn(1.f, s);
+    if (tid == 0) s2[i] = s;
+    if (active) *reinterpret_cast<uint2*>(q2 + i * K + col) = quant8_i8(v, s, inv);
+  }
+}
+
 template <int KIND, int OUT_FP8, int ROT = 0>
 int launch_quant(const QuantParams& p, cudaStream_t stream) {
   const int64_t nchunk = p.K >> 3;
@@ -395,4 +438,29 @@ extern "C" int rh3_norm_mod_rot_quant_rows_i8(const void* x, int64_t ldx, const 
   p.w = static_cast<const __nv_bfloat16*>(w); p.eps = eps; p.idx = idx; p.shift = shift; p.scale = scale;
   p.ld_tab = ld_tab;
   return launch_quant<KIND_NORMMOD, 0, 1>(p, stream);
+}
+
+// ---- residual pass of the text encoder's int8_rot linears (no rotation-free form exists) ----
+extern "C" int rh3_rot_residual_quant_rows_i8(const float* x, int64_t ldx, const void* q1, int64_t ldq1, const float* s1,
+                                              const int32_t* rows, int64_t n, int64_t K, void* q2, float* s2,
+                                              cudaStream_t stream) {
+  RH3_CHECK_ARG(n >= 0 && K > 0 && K % 256 == 0 && K <= 8192, "rot_residual_quant: K=%lld must be a multiple of 256, <= 8192",
+                (long long)K);
+  RH3_CHECK_ARG(ldx >= K && ldx % 4 == 0 && ldq1 >= K && ldq1 % 8 == 0, "rot_residual_quant: bad row strides");
+  if (n == 0) return 0;
+  RH3_CHECK_ARG(x && q1 && s1 && rows && q2 && s2, "rot_residual_quant: null pointer");
+  RH3_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q1) & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(q2) & 7) == 0,
+                "rot_residual_quant: x must be 16-byte aligned, q1 and q2 8-byte aligned");
+  const int64_t threads = K / 8;
+  const unsigned grid = static_cast<unsigned>(n < 4 * device_sm_count() ? n : 4 * device_sm_count());
+#define RH3_RR(T_)                                                                                       \
+  rot_residual_quant_kernel<T_><<<grid, T_, 0, stream>>>(x, ldx, static_cast<const int8_t*>(q1), ldq1, s1, rows, n, \
+                                                         (int)K, static_cast<int8_t*>(q2), s2)
+  if (threads <= 128) RH3_RR(128);
+  else if (threads <= 256) RH3_RR(256);
+  else if (threads <= 512) RH3_RR(512);
+  else RH3_RR(1024);
+#undef RH3_RR
+  return check_cuda(cudaGetLastError(), "rot_residual_quant launch");
 }
