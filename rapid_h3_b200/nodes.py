@@ -39,8 +39,9 @@ class _QuantLinear:
     """Replacement forward bound to one Linear: row quantizer + W8A8 GEMM, bias added afterwards in bf16
     (reference: __init__.py:132-167). The quantized weight is made once and cached."""
 
-    def __init__(self, module, name, mode):
+    def __init__(self, module, name, mode, measure_every=0, stats=None):
         self.module, self.name, self.mode = module, name, mode
+        self.measure_every, self.stats = measure_every, stats if stats is not None else {}
         self.qweight = None
         self.calls = 0
 
@@ -72,8 +73,15 @@ class _QuantLinear:
             y = y[:, torch.argsort(cf.swiglu_perm(y.shape[-1], y.device))]
         if self.module.bias is not None:
             y = y + self.module.bias.to(y.dtype)
+        y = y.reshape(*shape[:-1], y.shape[-1])
         self.calls += 1
-        return y.reshape(*shape[:-1], y.shape[-1])
+        if self.measure_every and self.calls % self.measure_every == 0 and self.module.weight.numel():
+            # error of this call against the unquantized linear (a measurement, not part of the path;
+            # reference __init__.py:160-164)
+            ref = torch.nn.functional.linear(x, self.module.weight.to(x.dtype), self.module.bias)
+            err = ((y.float() - ref.float()).norm() / ref.float().norm().clamp_min(1e-12)).item()
+            self.stats.setdefault(self.name, []).append(err)
+        return y
 
 
 class FusedBlock:
@@ -218,6 +226,24 @@ class FusedBlock:
     __call__ = forward
 
 
+def _fused_mlp(mlp, fc2q):
+    """MLP forward for blocks whose attention linears stay unquantized: fc1 through whatever forward it has, then
+    SwiGLU fused into the quantizer of fc2's input and the W8A8 GEMM (reference __init__.py:170-186)."""
+
+    def forward(x):
+        if x.dtype != torch.bfloat16 or x.device.type != "cuda":
+            raise NotImplementedError("_fused_mlp: only CUDA bf16 activations are supported (no fallback path)")
+        hdn = mlp.fc1(x)
+        shape = hdn.shape
+        qw = fc2q.qweight_for(x)
+        xq, sa = tq.swiglu_rot_quant_rows_i8(hdn.reshape(-1, shape[-1]).contiguous(), rotate=fc2q.mode == "int8_rot")
+        y = cf.int8_gemm(xq, sa, qw.q, qw.scale)
+        if fc2q.module.bias is not None:
+            y = y + fc2q.module.bias.to(y.dtype)
+        return y.reshape(*shape[:-1], y.shape[-1])
+    return forward
+
+
 def _fused_block(block, qkv_q, out_q, fc1_q, fc2_q, cq_q=None, ckv_q=None, co_q=None):
     """The reference's factory name: returns the fused forward bound to `block`."""
     return FusedBlock(block, qkv_q, out_q, fc1_q, fc2_q, cq_q, ckv_q, co_q)
@@ -226,11 +252,25 @@ def _fused_block(block, qkv_q, out_q, fc1_q, fc2_q, cq_q=None, ckv_q=None, co_q=
 class PatchedModel:
     """What `RapidH3LinearQuant.patch` returns in place of ComfyUI's patched MODEL clone."""
 
-    def __init__(self, model, linears, block_forward):
+    def __init__(self, model, linears, block_forward, wrappers=(), stats=None):
         self.model, self.linears, self.block_forward = model, linears, block_forward
+        self.wrappers, self.stats = list(wrappers), stats if stats is not None else {}
 
     def __call__(self, latent, audio, t_emb, rope_freqs, ctx):
-        return self.model(latent, audio, t_emb, rope_freqs, ctx, block_forward=self.block_forward)
+        """Runs the model with the replacement forwards installed on the modules that are not covered by a fused
+        block, and removes them afterwards (the reference's wrapper, __init__.py:396-413)."""
+        saved = []
+        for mod, fwd in self.wrappers:
+            saved.append((mod, mod.__dict__.get("forward")))
+            mod.forward = fwd
+        try:
+            return self.model(latent, audio, t_emb, rope_freqs, ctx, block_forward=self.block_forward)
+        finally:
+            for mod, prev in saved:
+                if prev is None:
+                    mod.__dict__.pop("forward", None)
+                else:
+                    mod.forward = prev
 
 
 def _parse_blocks(spec):
@@ -257,24 +297,31 @@ class RapidH3LinearQuant:
             kernels.quantize_weight(torch.zeros(1, 8), mode)  # raises ValueError / NotImplementedError by name
         want = {t.strip() for t in targets.split(",") if t.strip()}
         keep = _parse_blocks(keep_bf16_blocks)
-        by_name = {}
+        by_name, stats = {}, {}
         for name, mod in model.named_modules():
             hit = NAME_RE.match(name)
             if not hit or hit.group(3) not in want or int(hit.group(1)) in keep:
                 continue
-            by_name[name] = _QuantLinear(mod, name, mode)
-        forwards = []
+            by_name[name] = _QuantLinear(mod, name, mode, measure_every, stats)
+        forwards, wrappers = [], []
         for i, blk in enumerate(model.blocks):
             n = f"blocks.{i}"
             parts = [by_name.get(f"{n}.{m}") for m in ("attn.qkv_proj", "attn.out_proj", "mlp.fc1", "mlp.fc2")]
             cross = [by_name.get(f"{n}.{m}") for m in ("cross.q_proj", "cross.kv_proj", "cross.out_proj")]
-            if all(parts) and fuse_block and mode in ("int8_rowwise", "int8_fast", "int8_rot"):
+            int8 = mode in ("int8_rowwise", "int8_fast", "int8_rot")
+            if all(parts) and fuse_block and int8 and not measure_every:
                 if hasattr(blk, "cross") and not all(cross):
                     raise NotImplementedError("fused block needs the cross-attention linears quantized as well")
                 forwards.append(_fused_block(blk, *parts, *(cross if hasattr(blk, "cross") else ())))
             else:
-                forwards.append(blk)  # stock forward (bf16 blocks kept on request)
-        return (PatchedModel(model, by_name, forwards),)
+                # stock block forward; its quantized linears (if any) replace the modules' forwards during the call,
+                # and an MLP with both linears quantized gets SwiGLU fused into fc2's quantizer
+                forwards.append(blk)
+                mine = [(nm, q) for nm, q in by_name.items() if nm.startswith(n + ".")]
+                wrappers.extend((q.module, q) for _, q in mine)
+                if parts[2] and parts[3] and int8 and not measure_every:
+                    wrappers.append((blk.mlp, _fused_mlp(blk.mlp, parts[3])))
+        return (PatchedModel(model, by_name, forwards, wrappers, stats),)
 
 
 class RapidH3Int8Attention:

@@ -146,3 +146,36 @@ def test_quant_linear_adopts_prerotated_int8_weight(pkg):
     assert torch.equal(q.qweight.q, own.q) and torch.equal(q.qweight.scale, own.scale)
     assert torch.equal(y, r.kernels.linear(x, own, "int8_rot"))
     assert rel_l2(y, torch.nn.functional.linear(x, lin.weight)) < 0.05
+
+
+def test_unfused_patch_paths_and_error_statistics(pkg):
+    """Blocks that are not fused run their stock forward with the quantized linears installed on the modules
+    for the duration of the call: `measure_every` records per-linear errors, `targets="fc1,fc2"` fuses only the
+    MLP (SwiGLU inside fc2's quantizer), `keep_bf16_blocks` leaves whole blocks alone."""
+    r = pkg
+    cfg = r.model.H3Config.tiny(n_blocks=2, text_dim=256)
+    model = r.model.init_weights(r.model.H3Transformer(cfg), seed=4).cuda()
+    latent, audio, t_emb, rope, ctx = (t.cuda() for t in r.step.make_inputs(cfg, (4, 4, 4), 5, 1, 24, seed=6))
+    args = (latent[0], audio[0], t_emb[0], rope, ctx[0])
+    with torch.no_grad():
+        ref_v, _ = model(*args)
+
+        patched, = r.nodes.RapidH3LinearQuant().patch(model, "int8_rot", measure_every=1)
+        assert not any(isinstance(f, r.nodes.FusedBlock) for f in patched.block_forward)
+        v, _ = patched(*args)
+        assert rel_l2(v, ref_v) < 0.05
+        assert len(patched.stats) == len(patched.linears) and all(0 < e[0] < 0.05 for e in patched.stats.values())
+        assert "forward" not in model.blocks[0].attn.qkv_proj.__dict__  # the replacement forwards are removed again
+
+        patched, = r.nodes.RapidH3LinearQuant().patch(model, "int8_rowwise", targets="fc1,fc2")
+        assert len(patched.linears) == 4 and len(patched.wrappers) == 6  # 4 linears + 2 fused MLPs
+        v2, _ = patched(*args)
+        assert rel_l2(v2, ref_v) < 0.05
+        assert all(q.calls == 1 for n, q in patched.linears.items() if n.endswith("fc1"))
+        assert all(q.calls == 0 for n, q in patched.linears.items() if n.endswith("fc2"))  # fc2 ran inside the fused MLP
+
+        patched, = r.nodes.RapidH3LinearQuant().patch(model, "int8_rowwise", keep_bf16_blocks="0")
+        assert not isinstance(patched.block_forward[0], r.nodes.FusedBlock)
+        assert isinstance(patched.block_forward[1], r.nodes.FusedBlock)
+        v3, _ = patched(*args)
+        assert rel_l2(v3, ref_v) < 0.05
