@@ -300,7 +300,7 @@ def main():
     ap.add_argument("--mode", default="int8_rowwise", choices=["int8_rowwise", "int8_rot"],
                     help="linear recipe of the step: un-rotated row-wise int8 (the benchmark configuration) or the "
                          "H256-rotated recipe")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "fused", "auto"],
+    ap.add_argument("--exchange", default="auto", choices=["nccl", "fused", "auto"],
                     help="N > 1: token <-> head exchanges as NCCL all-to-all, or done by the rope and attention kernels "
                          "themselves (stores into peer buffers); auto = fused, falling back to nccl if the peer "
                          "buffers cannot be set up")
