@@ -39,6 +39,15 @@ def shard_segments(segments, lo, hi):
     return out
 
 
+def scatter_plan(bounds, rank, w, elem_bytes=2):
+    """Where the attention epilogue of `rank` (owner of one head group of width `w`) stores the output rows of
+    every token range: rank r's buffer is [P, count_r, w], slot `rank` of it belongs to this head group.
+    Returns (byte offset into rank r's buffer for r = 0..P-1, row starts [P + 1])."""
+    offsets = [rank * (b - a) * w * elem_bytes for a, b in bounds]
+    starts = [a for a, _ in bounds] + [bounds[-1][1]]
+    return offsets, starts
+
+
 class PeerBuffers:
     """One device buffer of `nbytes` per rank, mapped into every rank of the group (ranks on one node): `local` is
     this rank's buffer as a uint8 tensor, `ptrs[r]` the address of rank r's buffer in this process. Tried in
@@ -141,8 +150,8 @@ class Ulysses:
         from . import attn_int8
         pre = attn_int8.int8_prepass(q, k, v)
         w = self._w
-        ptrs = [self._o_buf.ptrs[r] + self.rank * self.counts[r] * w * 2 for r in range(self.world)]
-        starts = [a for a, _ in self.bounds] + [self.total]
+        offsets, starts = scatter_plan(self.bounds, self.rank, w)
+        ptrs = [self._o_buf.ptrs[r] + offsets[r] for r in range(self.world)]
         attn_int8.attention_pre(pre, scale, scatter=(ptrs, starts, w, self._head_dim))
         self._barrier()
         s_loc = self.counts[self.rank]

@@ -60,3 +60,24 @@ def test_ulysses_exchanges_are_exact_permutations():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), total, heads, hd, ret), nprocs=world, join=True)
     assert dict(ret) == {0: True, 1: True}
+
+
+def test_scatter_plan_tiles_every_destination_buffer():
+    """The output rows that the P head groups store into rank r's exchange buffer must tile [P, count_r, w]
+    exactly (no gap, no overlap), for even and ragged shard sizes and every world size the step supports."""
+    from rapid_h3_b200 import sp
+    for total in (36436, 17896, 221, 4096):
+        for world in (1, 2, 4, 8):
+            bounds = sp.shard_bounds(total, world)
+            assert bounds[0][0] == 0 and bounds[-1][1] == total
+            w = (32 // world) * 128
+            for r in range(world):
+                count = bounds[r][1] - bounds[r][0]
+                spans = []
+                for g in range(world):  # source rank g = head group g
+                    offsets, starts = sp.scatter_plan(bounds, g, w)
+                    assert starts == [a for a, _ in bounds] + [total]
+                    spans.append((offsets[r], offsets[r] + count * w * 2))
+                spans.sort()
+                assert spans[0][0] == 0 and spans[-1][1] == world * count * w * 2
+                assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
