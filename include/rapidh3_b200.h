@@ -152,10 +152,13 @@ int rh3_attn_int8(const void* q8, const float* qs, const void* k8, const float* 
 /* out = bf16(conv3x3x3(x, w) + bias (+ residual)); w is [Cout, 27, Cin] with tap = (dt*3 + dh)*3 + dw; zero
  * padding of one pixel in H and W and of two frames before t = 0 (causal). Cin % 64 == 0, Cout % 16 == 0.
  * bias, residual and gn_part may be NULL. gn_part (fp32 [rh3_conv3d_gn_part_rows(), 32, 2]) receives
- * per-row-block partial (sum, sum of squares) of the stored outputs for each of 32 GroupNorm groups. */
+ * per-row-block partial (sum, sum of squares) of the stored outputs for each of 32 GroupNorm groups.
+ * halo_frames = 2: x holds T + 2 frames per sample, the first two being the frames that precede output frame 0
+ * (the previous time shard's last frames) in place of the causal zero padding; out, residual and the statistics
+ * still cover T frames. halo_frames = 0: plain causal padding. */
 int rh3_conv3d_causal(const void* x, const void* w, const void* bias, const void* residual, void* out,
                       float* gn_part, int64_t N, int64_t T, int64_t H, int64_t W, int64_t Cin, int64_t Cout,
-                      cudaStream_t stream);
+                      int64_t halo_frames, cudaStream_t stream);
 /* Number of row blocks (first dimension of gn_part) for an output of N x T x H x W sites (a size, not a status). */
 int64_t rh3_conv3d_gn_part_rows(int64_t N, int64_t T, int64_t H, int64_t W);
 /* sums (fp64 [N, 32, 2]) = per-sample, per-group (sum, sum of squares) over rows_per_sample row blocks. */

@@ -34,6 +34,7 @@ constexpr int GN_GROUPS = 32;
 
 struct ConvParams {
   int N, T, H, W, Cin, Cout;
+  int halo;            // frames that precede output frame 0 inside x (0: causal zero padding, 2: a time shard's halo)
   int bh, bw;          // tile of output sites inside a frame
   int tiles_h, tiles_w;
   int BN;              // output channels per tile (multiple of 16, <= 256)
@@ -132,7 +133,7 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
           uint8_t* sa = smem + stage * CSTAGE_BYTES;
           mbar_arrive_expect_tx(&tail->full[stage], a_bytes + b_bytes);
           // out-of-range coordinates (negative or past the edge) read zeros: spatial and causal padding
-          tma_load_5d(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2, c.n, &tail->full[stage]);
+          tma_load_5d(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2 + p.halo, c.n, &tail->full[stage]);
           tma_load_2d(sa + CA_BYTES, &tma_w, tap * p.Cin + cc * CBK, c.n_blk * p.BN, &tail->full[stage]);
           if (++stage == CSTAGES) { stage = 0; phase ^= 1; }
         }
@@ -387,8 +388,9 @@ extern "C" int64_t rh3_conv3d_gn_part_rows(int64_t N, int64_t T, int64_t H, int6
 
 extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias, const void* residual, void* out,
                                  float* gn_part, int64_t N, int64_t T, int64_t H, int64_t W, int64_t Cin,
-                                 int64_t Cout, cudaStream_t stream) {
+                                 int64_t Cout, int64_t halo_frames, cudaStream_t stream) {
   RH3_CHECK_ARG(N > 0 && T > 0 && H > 0 && W > 0 && N * T * H * W < (1ll << 31), "conv3d_causal: bad shape");
+  RH3_CHECK_ARG(halo_frames == 0 || halo_frames == 2, "conv3d_causal: halo_frames must be 0 or 2");
   RH3_CHECK_ARG(Cin > 0 && Cin % 64 == 0, "conv3d_causal: Cin=%lld must be a multiple of 64", (long long)Cin);
   RH3_CHECK_ARG(Cout > 0 && Cout % 16 == 0, "conv3d_causal: Cout=%lld must be a multiple of 16", (long long)Cout);
   RH3_CHECK_ARG(!gn_part || (Cout % GN_GROUPS == 0 && 32 % (Cout / GN_GROUPS) == 0),
@@ -397,6 +399,7 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
                 "conv3d_causal: null or misaligned pointer");
   ConvParams p{};
   p.N = (int)N; p.T = (int)T; p.H = (int)H; p.W = (int)W; p.Cin = (int)Cin; p.Cout = (int)Cout;
+  p.halo = (int)halo_frames;
   choose_tile(p.H, p.W, &p.bh, &p.bw);
   p.tiles_h = (p.H + p.bh - 1) / p.bh;
   p.tiles_w = (p.W + p.bw - 1) / p.bw;
@@ -409,9 +412,10 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
   p.gn_part = gn_part;
   p.status = device_status_word();
   CUtensorMap tx, tw;
-  const uint64_t dims[5] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, (uint64_t)T, (uint64_t)N};
+  const uint64_t Tin = (uint64_t)(T + halo_frames);  // frames held by x
+  const uint64_t dims[5] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, Tin, (uint64_t)N};
   const uint64_t strides[4] = {(uint64_t)Cin * 2, (uint64_t)W * Cin * 2, (uint64_t)H * W * Cin * 2,
-                               (uint64_t)T * H * W * Cin * 2};
+                               Tin * H * W * Cin * 2};
   const uint32_t box[5] = {CBK, (uint32_t)p.bw, (uint32_t)p.bh, 1, 1};
   if (int e = make_tmap_nd(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, 5, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
     return e;

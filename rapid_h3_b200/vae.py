@@ -25,30 +25,27 @@ GROUPS = 32
 EPS = 1e-6
 
 
-def conv3d_causal(x, w, bias=None, residual=None, want_stats=False, halo=None):
+def conv3d_causal(x, w, bias=None, residual=None, want_stats=False, halo=None, halo_frames=0):
     """x [N,T,H,W,Cin] bf16 channels-last, w [Cout,27,Cin] bf16 -> (out [N,T,H,W,Cout], partial GN sums or None).
-    `halo` ([N,2,H,W,Cin], the two frames preceding x on the previous time shard) replaces the causal zero
-    padding: the convolution then runs on the concatenation and the first two output frames are dropped."""
+    `halo_frames=2`: x is [N,T+2,H,W,Cin] and its first two frames are the frames that precede output frame 0 (the
+    previous time shard's last two) instead of the causal zero padding; the output still has T frames.
+    `halo` ([N,2,H,W,Cin]) is the same thing passed separately (one concatenation copy is made)."""
     _lib.require_cuda(x, w)
     if halo is not None:
-        x = torch.cat([halo, x], 1)
-        if residual is not None:
-            residual = torch.cat([torch.zeros_like(residual[:, :2]), residual], 1)
-    n, t, h, wd, cin = x.shape
+        x, halo_frames = torch.cat([halo, x], 1), 2
+    n, t_in, h, wd, cin = x.shape
+    t = t_in - halo_frames
     cout = w.shape[0]
     assert x.is_contiguous() and w.is_contiguous() and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    assert w.shape[1] == 27 and w.shape[2] == cin
+    assert w.shape[1] == 27 and w.shape[2] == cin and halo_frames in (0, 2) and t > 0
+    assert residual is None or (residual.is_contiguous() and residual.shape == (n, t, h, wd, cout))
     out = torch.empty((n, t, h, wd, cout), device=x.device, dtype=torch.bfloat16)
     part = None
-    if want_stats and halo is None:
+    if want_stats:
         rows = _lib.lib().rh3_conv3d_gn_part_rows(n, t, h, wd)
         part = torch.empty((rows, GROUPS, 2), device=x.device, dtype=torch.float32)
     _lib.call("rh3_conv3d_causal", x.data_ptr(), w.data_ptr(), _lib.ptr(bias), _lib.ptr(residual), out.data_ptr(),
-              _lib.ptr(part), n, t, h, wd, cin, cout, _lib.stream())
-    if halo is not None:
-        out = out[:, 2:].contiguous()
-        if want_stats:  # statistics of the kept frames only: recomputed from the output (halo frames excluded)
-            return out, None
+              _lib.ptr(part), n, t, h, wd, cin, cout, halo_frames, _lib.stream())
     return out, part
 
 
@@ -66,21 +63,24 @@ def gn_sums_from_tensor(x):
     return torch.stack([xf.sum(dim=(1, 3)), (xf * xf).sum(dim=(1, 3))], -1)
 
 
-def gn_silu(x, sums, count, gamma, beta):
-    """GroupNorm(32 groups) + SiLU of x [N,T,H,W,C] given its (sum, sum of squares) per (sample, group)."""
+def gn_silu(x, sums, count, gamma, beta, out=None):
+    """GroupNorm(32 groups) + SiLU of x [N,T,H,W,C] given its (sum, sum of squares) per (sample, group);
+    `out` may be a contiguous buffer of x's shape (e.g. the data frames of a halo-padded buffer)."""
     n, c = x.shape[0], x.shape[-1]
     mean = sums[..., 0] / count
     var = (sums[..., 1] / count - mean * mean).clamp_min(0.0)
     mr = torch.stack([mean, torch.rsqrt(var + EPS)], -1).float().contiguous()
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if out is None else out
+    assert y.shape == x.shape and y.is_contiguous() and y.dtype == x.dtype
     _lib.call("rh3_gn_silu_apply", x.data_ptr(), mr.data_ptr(), gamma.data_ptr(), beta.data_ptr(), n,
               x.numel() // (n * c), c, y.data_ptr(), _lib.stream())
     return y
 
 
-def upsample(x):
+def upsample(x, out=None):
     n, t, h, w, c = x.shape
-    y = torch.empty((n, 2 * t - 1, 2 * h, 2 * w, c), device=x.device, dtype=x.dtype)
+    y = torch.empty((n, 2 * t - 1, 2 * h, 2 * w, c), device=x.device, dtype=x.dtype) if out is None else out
+    assert y.shape == (n, 2 * t - 1, 2 * h, 2 * w, c) and y.is_contiguous()
     _lib.call("rh3_upsample_causal2x", x.data_ptr(), y.data_ptr(), n, t, h, w, c, _lib.stream())
     return y
 
@@ -100,29 +100,44 @@ class TimeShards:
             a = b
         self.t0, self.t1 = self.bounds[self.rank]
 
-    def halo(self, x):
-        """The last two frames of the previous rank's slab ([N,2,H,W,C]; zeros on rank 0 = causal padding)."""
-        recv = torch.zeros_like(x[:, :2])
-        ops = []
+    def frames_per_rank(self, upsamples):
+        """Frames every rank holds after `upsamples` causal 2x upsamplings (rank 0: 2t-1 each time, others 2t)."""
+        out = []
+        for r, (a, b) in enumerate(self.bounds):
+            f = b - a
+            for _ in range(upsamples):
+                f = 2 * f - 1 if r == 0 else 2 * f
+            out.append(f)
+        return out
+
+    def padded(self, n, t, h, w, c, device):
+        """A buffer [N, t+2, H, W, C] and the view of its last t frames: producers write the view, `exchange`
+        fills the two leading frames, and the convolution reads the whole buffer with halo_frames=2."""
+        buf = torch.empty((n, t + 2, h, w, c), device=device, dtype=torch.bfloat16)
+        return buf, buf[:, 2:]
+
+    def exchange(self, buf):
+        """Fill frames 0, 1 of a padded buffer with the previous rank's last two frames (zeros on rank 0: causal
+        padding) and send this rank's last two to the next one."""
+        n = buf.shape[0]
+        ops, recv = [], None
         if self.rank + 1 < self.world:
-            ops.append(dist.P2POp(dist.isend, x[:, -2:].contiguous(), self.rank + 1, self.group))
+            ops.append(dist.P2POp(dist.isend, buf[:, -2:].contiguous(), self.rank + 1, self.group))
         if self.rank > 0:
+            recv = buf[:, :2] if n == 1 else torch.empty_like(buf[:, :2].contiguous())
             ops.append(dist.P2POp(dist.irecv, recv, self.rank - 1, self.group))
+        else:
+            buf[:, :2].zero_()
         if ops:
             for req in dist.batch_isend_irecv(ops):
                 req.wait()
-        return recv
+        if recv is not None and n != 1:
+            buf[:, :2] = recv
+        return buf
 
     def all_reduce(self, t):
         dist.all_reduce(t, group=self.group)
         return t
-
-    def upsample(self, x):
-        """Causal 2x upsampling of a slab: every rank but the first also repeats its first frame."""
-        y = upsample(x)
-        if self.rank == 0:
-            return y
-        return torch.cat([y[:, :1], y], 1)
 
 
 class VAEDecoder:
@@ -172,37 +187,66 @@ class VAEDecoder:
         return total + 2 * sites * self.widths[-1] * 192 * 27
 
     def decode(self, latent, sp=None):
-        """latent [N, C, T, H, W] bf16 -> RGB [N, 3, 4T-3, 32H, 32W] bf16 (with `sp`: this rank's frames)."""
+        """latent [N, C, T, H, W] bf16 -> RGB [N, 3, 4T-3, 32H, 32W] bf16 (with `sp`: this rank's frames).
+        With `sp` every activation that feeds a convolution is produced straight into a halo-padded buffer, the
+        two halo frames arrive from the previous rank, and nothing is copied or recomputed for the halo."""
         p = self.p
         n, c, t, h, w = latent.shape
-        x = torch.zeros((n, t, h, w, 64), device=latent.device, dtype=torch.bfloat16)
-        x[..., :c] = latent.permute(0, 2, 3, 4, 1)
+        dev = latent.device
+        ups = 0  # causal upsamplings so far (for the global element count of the GroupNorm statistics)
 
-        def conv(name, x, residual=None, stats=True):
-            halo = sp.halo(x) if sp is not None else None
-            y, part = conv3d_causal(x, p[name + ".w"], p[name + ".b"], residual, want_stats=stats, halo=halo)
+        def new_act(t_, h_, w_, c_):
+            """(buffer handed to the next convolution, view the producer writes)."""
+            if sp is None:
+                y = torch.empty((n, t_, h_, w_, c_), device=dev, dtype=torch.bfloat16)
+                return y, y
+            return sp.padded(n, t_, h_, w_, c_, dev)
+
+        def conv(name, buf, residual=None, stats=True):
+            if sp is not None:
+                sp.exchange(buf)
+            y, part = conv3d_causal(buf, p[name + ".w"], p[name + ".b"], residual, want_stats=stats,
+                                    halo_frames=0 if sp is None else 2)
             if not stats:
                 return y, None
-            sums = gn_sums(part, n) if part is not None else gn_sums_from_tensor(y)
+            sums = gn_sums(part, n)
             count = y.numel() // (n * GROUPS)
             if sp is not None:
                 sums = sp.all_reduce(sums)
-                cnt = torch.tensor([float(count)], device=y.device, dtype=torch.float64)
-                count = sp.all_reduce(cnt).item()
+                count = sum(sp.frames_per_rank(ups)) * (count // y.shape[1])
             return y, (sums, count)
 
-        x, st = conv("conv_in", x)
+        def norm_act(x, st, name):
+            """GroupNorm + SiLU of x written where the next convolution reads it."""
+            buf, view = new_act(*x.shape[1:])
+            if view.is_contiguous():
+                gn_silu(x, *st, p[name + ".g"], p[name + ".be"], out=view)
+            else:  # several samples in a padded buffer: the data frames of a sample are not adjacent to the next one's
+                view.copy_(gn_silu(x, *st, p[name + ".g"], p[name + ".be"]))
+            return buf
+
+        buf, view = new_act(t, h, w, 64)
+        view.zero_()
+        view[..., :c] = latent.permute(0, 2, 3, 4, 1)
+        x, st = conv("conv_in", buf)
         for si in range(len(self.widths)):
             for bi in range(self.blocks):
-                hdn = gn_silu(x, *st, p[f"s{si}.b{bi}.n1.g"], p[f"s{si}.b{bi}.n1.be"])
-                hdn, st2 = conv(f"s{si}.b{bi}.c1", hdn)
-                hdn = gn_silu(hdn, *st2, p[f"s{si}.b{bi}.n2.g"], p[f"s{si}.b{bi}.n2.be"])
-                x, st = conv(f"s{si}.b{bi}.c2", hdn, residual=x)
+                hdn, st2 = conv(f"s{si}.b{bi}.c1", norm_act(x, st, f"s{si}.b{bi}.n1"))
+                x, st = conv(f"s{si}.b{bi}.c2", norm_act(hdn, st2, f"s{si}.b{bi}.n2"), residual=x)
             if si + 1 < len(self.widths):
-                x = upsample(x) if sp is None else sp.upsample(x)
-                x, st = conv(f"s{si}.up", x)
-        x = gn_silu(x, *st, p["head.n.g"], p["head.n.be"])
-        y, _ = conv("head.c", x, stats=False)                      # [N, T', H', W', 3*8*8]
+                _, tx, hx, wx, cx = x.shape
+                dup = 0 if sp is None or sp.rank == 0 else 1  # later shards also repeat their first frame
+                buf, view = new_act(2 * tx - 1 + dup, 2 * hx, 2 * wx, cx)
+                if view.is_contiguous():
+                    upsample(x, out=view[:, dup:])
+                else:
+                    view[:, dup:] = upsample(x)
+                if dup:
+                    view[:, 0] = view[:, 1]
+                ups += 1
+                x, st = conv(f"s{si}.up", buf)
+        buf = norm_act(x, st, "head.n")
+        y, _ = conv("head.c", buf, stats=False)                    # [N, T', H', W', 3*8*8]
         n, t2, h2, w2, _ = y.shape
         y = y.view(n, t2, h2, w2, 3, 8, 8).permute(0, 4, 1, 2, 5, 3, 6)  # depth-to-space: pure data movement
         return y.reshape(n, 3, t2, h2 * 8, w2 * 8)
