@@ -25,14 +25,11 @@ GROUPS = 32
 EPS = 1e-6
 
 
-def conv3d_causal(x, w, bias=None, residual=None, want_stats=False, halo=None, halo_frames=0):
+def conv3d_causal(x, w, bias=None, residual=None, want_stats=False, halo_frames=0):
     """x [N,T,H,W,Cin] bf16 channels-last, w [Cout,27,Cin] bf16 -> (out [N,T,H,W,Cout], partial GN sums or None).
     `halo_frames=2`: x is [N,T+2,H,W,Cin] and its first two frames are the frames that precede output frame 0 (the
-    previous time shard's last two) instead of the causal zero padding; the output still has T frames.
-    `halo` ([N,2,H,W,Cin]) is the same thing passed separately (one concatenation copy is made)."""
+    previous time shard's last two) instead of the causal zero padding; the output still has T frames."""
     _lib.require_cuda(x, w)
-    if halo is not None:
-        x, halo_frames = torch.cat([halo, x], 1), 2
     n, t_in, h, wd, cin = x.shape
     t = t_in - halo_frames
     cout = w.shape[0]

@@ -58,6 +58,32 @@ def test_causality(vae):
     assert torch.equal(y[:, :4], y2[:, :4]) and not torch.equal(y[:, 4], y2[:, 4])
 
 
+def test_halo_frames_replace_the_causal_padding(vae):
+    """A time shard's convolution: with halo_frames=2 the first two frames of the input buffer are the frames
+    before the shard, so output, residual and GroupNorm partials equal those frames of the unsharded convolution
+    bit for bit (same kernel, same tiles, same accumulation order)."""
+    v, lib = vae
+    g = torch.Generator().manual_seed(7)
+    n, t, h, w, cin, cout = 2, 7, 6, 10, 64, 64
+    x = torch.randn(n, t, h, w, cin, generator=g).to(torch.bfloat16).cuda()
+    wt = (0.05 * torch.randn(cout, 27, cin, generator=g)).to(torch.bfloat16).cuda()
+    b = (0.1 * torch.randn(cout, generator=g)).to(torch.bfloat16).cuda()
+    res = torch.randn(n, t, h, w, cout, generator=g).to(torch.bfloat16).cuda()
+    full, _ = v.conv3d_causal(x, wt, b, res)
+    t0 = 3  # the shard owns frames 3..6; frames 1, 2 are its halo
+    shard, part = v.conv3d_causal(x[:, t0 - 2:].contiguous(), wt, b, res[:, t0:].contiguous(), want_stats=True,
+                                  halo_frames=2)
+    lib.check_status()
+    assert shard.shape == (n, t - t0, h, w, cout) and torch.equal(shard, full[:, t0:])
+    sums = v.gn_sums(part, n)
+    ref = v.gn_sums_from_tensor(full[:, t0:].contiguous())
+    assert torch.allclose(sums, ref, rtol=1e-6)
+    # a zero halo is the causal padding itself
+    first, _ = v.conv3d_causal(torch.cat([torch.zeros_like(x[:, :2]), x[:, :t0]], 1), wt, b, res[:, :t0].contiguous(),
+                               halo_frames=2)
+    assert torch.equal(first, full[:, :t0])
+
+
 def test_gn_silu_and_upsample(vae):
     v, lib = vae
     g = torch.Generator().manual_seed(4)
