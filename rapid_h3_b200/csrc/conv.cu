@@ -301,40 +301,59 @@ __global__ void __launch_bounds__(256) gn_reduce_kernel(const float* __restrict_
   }
 }
 
-// y = silu((x - mean[g]) * rstd[g] * gamma[c] + beta[c]); 8 channels per thread.
+// y = silu((x - mean[g]) * rstd[g] * gamma[c] + beta[c]). A thread keeps one group of 8 channels for the whole
+// launch (the block's 256 threads cover 256 / (C/8) sites per iteration), so the per-channel scale
+// a = rstd * gamma and offset b = beta - mean * a are computed once and the loop body is one FMA and one
+// tanh per value: silu(t) = t * (0.5 + 0.5 * tanh(t / 2)). Launched as (blocks, N); C/8 <= 256 (threads beyond
+// the last whole site of the block idle).
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __global__ void __launch_bounds__(256) gn_silu_kernel(const __nv_bfloat16* __restrict__ x,
                                                       const float* __restrict__ mean_rstd,  // [N][32][2]
                                                       const __nv_bfloat16* __restrict__ gamma,
                                                       const __nv_bfloat16* __restrict__ beta, int64_t sites_per_sample,
-                                                      int C, int64_t total_vec, __nv_bfloat16* __restrict__ y) {
-  const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-  if (v >= total_vec) return;
-  const int vec_per_site = C >> 3;
-  const int64_t site = v / vec_per_site;
-  const int c0 = static_cast<int>(v - site * vec_per_site) << 3;
-  const int n = static_cast<int>(site / sites_per_sample);
+                                                      int C, __nv_bfloat16* __restrict__ y) {
+  const int vps = C >> 3;                       // 16-byte vectors per site
+  const int lane_vec = threadIdx.x % vps;       // this thread's vector inside a site
+  const int site_in_block = threadIdx.x / vps;
+  const int sites_per_iter = 256 / vps;
+  if (site_in_block >= sites_per_iter) return;
+  const int n = blockIdx.y;
+  const int c0 = lane_vec << 3;
   const int gs = C / GN_GROUPS;
-  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + site * C + c0));
-  const uint4 gr = __ldg(reinterpret_cast<const uint4*>(gamma + c0));
-  const uint4 br = __ldg(reinterpret_cast<const uint4*>(beta + c0));
-  const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w}, bw[4] = {br.x, br.y, br.z, br.w};
-  uint32_t o[4];
+  float a[8], b[8];
+  {
+    const uint4 gr = __ldg(reinterpret_cast<const uint4*>(gamma + c0));
+    const uint4 br = __ldg(reinterpret_cast<const uint4*>(beta + c0));
+    const uint32_t gw[4] = {gr.x, gr.y, gr.z, gr.w}, bw[4] = {br.x, br.y, br.z, br.w};
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float r[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int c = c0 + 2 * j + e;
-      const float2 mr = *reinterpret_cast<const float2*>(mean_rstd + (static_cast<int64_t>(n) * GN_GROUPS + c / gs) * 2);
-      const float xv = e ? bf16_hi(xw[j]) : bf16_lo(xw[j]);
-      const float gv = e ? bf16_hi(gw[j]) : bf16_lo(gw[j]);
-      const float bv = e ? bf16_hi(bw[j]) : bf16_lo(bw[j]);
-      const float t = (xv - mr.x) * mr.y * gv + bv;
-      r[e] = t / (1.f + __expf(-t));
+    for (int j = 0; j < 8; ++j) {
+      const float2 mr = *reinterpret_cast<const float2*>(mean_rstd + (static_cast<int64_t>(n) * GN_GROUPS + (c0 + j) / gs) * 2);
+      const float gv = (j & 1) ? bf16_hi(gw[j >> 1]) : bf16_lo(gw[j >> 1]);
+      const float bv = (j & 1) ? bf16_hi(bw[j >> 1]) : bf16_lo(bw[j >> 1]);
+      a[j] = mr.y * gv;
+      b[j] = fmaf(-mr.x, a[j], bv);
     }
-    o[j] = pack_bf16x2(r[0], r[1]);
   }
-  *reinterpret_cast<uint4*>(y + site * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+  const __nv_bfloat16* xs = x + static_cast<int64_t>(n) * sites_per_sample * C;
+  __nv_bfloat16* ys = y + static_cast<int64_t>(n) * sites_per_sample * C;
+  for (int64_t site = static_cast<int64_t>(blockIdx.x) * sites_per_iter + site_in_block; site < sites_per_sample;
+       site += static_cast<int64_t>(gridDim.x) * sites_per_iter) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xs + site * C + c0));
+    const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float t0 = fmaf(bf16_lo(xw[j]), a[2 * j], b[2 * j]);
+      const float t1 = fmaf(bf16_hi(xw[j]), a[2 * j + 1], b[2 * j + 1]);
+      const float h0 = 0.5f * t0, h1 = 0.5f * t1;
+      o[j] = pack_bf16x2(fmaf(h0, tanh_approx(h0), h0), fmaf(h1, tanh_approx(h1), h1));
+    }
+    *reinterpret_cast<uint4*>(ys + site * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
 }
 
 // out[n, u, yy, xx, :] = in[n, (u + 1) / 2, yy / 2, xx / 2, :]: nearest 2x in space, causal 2x in time
@@ -444,11 +463,16 @@ extern "C" int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const vo
   RH3_CHECK_ARG(x && mean_rstd && gamma && beta && y && a16(x) && a16(y) && a16(gamma) && a16(beta),
                 "gn_silu_apply: null or misaligned pointer");
   RH3_CHECK_ARG(N > 0 && sites_per_sample > 0 && C > 0 && C % 8 == 0 && C % GN_GROUPS == 0, "gn_silu_apply: bad shape");
-  const int64_t total_vec = N * sites_per_sample * (C / 8);
-  RH3_CHECK_ARG((total_vec + 255) / 256 < (1ll << 31), "gn_silu_apply: tensor too large");
-  gn_silu_kernel<<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), mean_rstd, static_cast<const __nv_bfloat16*>(gamma),
-      static_cast<const __nv_bfloat16*>(beta), sites_per_sample, (int)C, total_vec, static_cast<__nv_bfloat16*>(y));
+  RH3_CHECK_ARG(C / 8 <= 256, "gn_silu_apply: C=%lld is larger than 2048", (long long)C);
+  RH3_CHECK_ARG(N < 65536, "gn_silu_apply: too many samples");
+  const int64_t sites_per_iter = 256 / (C / 8);
+  const int64_t want = (sites_per_sample + sites_per_iter - 1) / sites_per_iter;
+  const int64_t cap = static_cast<int64_t>(device_sm_count()) * 16;  // a few waves of resident blocks, grid-stride beyond
+  const dim3 grid(static_cast<unsigned>(want < cap ? want : cap), static_cast<unsigned>(N));
+  gn_silu_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), mean_rstd,
+                                          static_cast<const __nv_bfloat16*>(gamma),
+                                          static_cast<const __nv_bfloat16*>(beta), sites_per_sample, (int)C,
+                                          static_cast<__nv_bfloat16*>(y));
   return check_cuda(cudaGetLastError(), "gn_silu_apply launch");
 }
 
