@@ -144,7 +144,7 @@ def cpu_baseline_record(workload):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cpu_port_step_seconds(workload, rows=128, attn_rows=32)  # warm-up
-    val, info = cpu_port_step_seconds(workload, rows=8192, attn_rows=2048)  # ~10-20 s of CPU work
+    val, info = cpu_port_step_seconds(workload, rows=12288, attn_rows=4096)  # ~10-20 s of CPU work
     return {"value": val, "unit": "s/step", "cores": cores, "kind": "port",
             "sample": (f"row-local ops of one block on {info['rows']} of the tokens, attention of 1 head on "
                        f"{info['attn_rows']} query rows x all keys ({info['sample_seconds']:.1f} s of CPU work), "
