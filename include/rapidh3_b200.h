@@ -169,6 +169,8 @@ int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const void* gamma, 
 /* y[N, 2T-1, 2H, 2W, C]: nearest-neighbour 2x in space, causal 2x in time (the first frame is not repeated). */
 int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t T, int64_t H, int64_t W, int64_t C,
                           cudaStream_t stream);
+/* Depth-to-space by 8 of the decoder head: y [N, T, H, W, 192] (channel = (ch*8 + dy)*8 + dx) -> rgb [N, 3, T, 8H, 8W]. */
+int rh3_depth_to_space8(const void* y, void* rgb, int64_t N, int64_t T, int64_t H, int64_t W, cudaStream_t stream);
 
 /* Second int8 pass of the text encoder's `int8_rot` linears on its outlier rows: for i < n and r = rows[i],
  * q2[i], s2[i] = int8 row quantizer of rotate(x[r]) - q1[r] * s1[r]  (x fp32 [*, K], q1 / s1 the first pass's codes and

@@ -476,6 +476,26 @@ extern "C" int rh3_gn_silu_apply(const void* x, const float* mean_rstd, const vo
   return check_cuda(cudaGetLastError(), "gn_silu_apply launch");
 }
 
+// Depth-to-space by 8 of the decoder head: y [N, T, H, W, 3*8*8] (channel = (ch*8 + dy)*8 + dx) ->
+// rgb [N, 3, T, 8H, 8W]. One thread moves the 8 pixels of one (site, ch, dy): 16 bytes in, 16 bytes out; threads
+// run along the output row so the stores are contiguous.
+__global__ void __launch_bounds__(256) depth_to_space8_kernel(const __nv_bfloat16* __restrict__ y, int T, int H, int W,
+                                                              int64_t total, __nv_bfloat16* __restrict__ rgb) {
+  const int64_t v = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;  // index over [N][3][T][8H][W]
+  if (v >= total) return;
+  const int w = static_cast<int>(v % W);
+  int64_t r = v / W;
+  const int Y = static_cast<int>(r % (8 * H));
+  r /= 8 * H;
+  const int t = static_cast<int>(r % T);
+  r /= T;
+  const int ch = static_cast<int>(r % 3);
+  const int64_t n = r / 3;
+  const int h = Y >> 3, dy = Y & 7;
+  const int64_t src = (((n * T + t) * H + h) * W + w) * 192 + (ch * 8 + dy) * 8;
+  *reinterpret_cast<uint4*>(rgb + v * 8) = __ldg(reinterpret_cast<const uint4*>(y + src));
+}
+
 extern "C" int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t T, int64_t H, int64_t W, int64_t C,
                                      cudaStream_t stream) {
   RH3_CHECK_ARG(x && y && a16(x) && a16(y) && N > 0 && T > 0 && H > 0 && W > 0 && C > 0 && C % 8 == 0,
@@ -485,4 +505,14 @@ extern "C" int rh3_upsample_causal2x(const void* x, void* y, int64_t N, int64_t 
   upsample_kernel<<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), (int)T, (int)H, (int)W, (int)C, total_vec, static_cast<__nv_bfloat16*>(y));
   return check_cuda(cudaGetLastError(), "upsample_causal2x launch");
+}
+
+extern "C" int rh3_depth_to_space8(const void* y, void* rgb, int64_t N, int64_t T, int64_t H, int64_t W,
+                                   cudaStream_t stream) {
+  RH3_CHECK_ARG(y && rgb && a16(y) && a16(rgb) && N > 0 && T > 0 && H > 0 && W > 0, "depth_to_space8: bad argument");
+  const int64_t total = N * 3 * T * 8 * H * W;
+  RH3_CHECK_ARG((total + 255) / 256 < (1ll << 31), "depth_to_space8: tensor too large");
+  depth_to_space8_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(y), (int)T, (int)H, (int)W, total, static_cast<__nv_bfloat16*>(rgb));
+  return check_cuda(cudaGetLastError(), "depth_to_space8 launch");
 }

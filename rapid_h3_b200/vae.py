@@ -82,6 +82,15 @@ def upsample(x, out=None):
     return y
 
 
+def depth_to_space8(y):
+    """y [N, T, H, W, 192] (channel = (ch*8 + dy)*8 + dx) -> [N, 3, T, 8H, 8W]."""
+    n, t, h, w, c = y.shape
+    assert c == 192 and y.is_contiguous() and y.dtype == torch.bfloat16
+    rgb = torch.empty((n, 3, t, 8 * h, 8 * w), device=y.device, dtype=torch.bfloat16)
+    _lib.call("rh3_depth_to_space8", y.data_ptr(), rgb.data_ptr(), n, t, h, w, _lib.stream())
+    return rgb
+
+
 class TimeShards:
     """Frames of the decoder's activations split over ranks (contiguous slabs of LATENT frames). The slab of
     rank r > 0 starts after a causal upsampling at frame 2*t0 - 1, so slabs stay contiguous at every stage."""
@@ -244,6 +253,4 @@ class VAEDecoder:
                 x, st = conv(f"s{si}.up", buf)
         buf = norm_act(x, st, "head.n")
         y, _ = conv("head.c", buf, stats=False)                    # [N, T', H', W', 3*8*8]
-        n, t2, h2, w2, _ = y.shape
-        y = y.view(n, t2, h2, w2, 3, 8, 8).permute(0, 4, 1, 2, 5, 3, 6)  # depth-to-space: pure data movement
-        return y.reshape(n, 3, t2, h2 * 8, w2 * 8)
+        return depth_to_space8(y)

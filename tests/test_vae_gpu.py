@@ -108,3 +108,14 @@ def test_decoder_matches_oracle(vae):
     # every layer rounds to bf16 (2^-9 relative); rounding flips compound over the 9 layers, so the whole
     # decoder is compared at a few bf16 ulps while each op alone is held to 1e-3 above
     assert rel_l2(rgb.cpu(), ref) <= 2e-2
+
+
+def test_depth_to_space_is_the_head_permutation(vae):
+    v, lib = vae
+    g = torch.Generator().manual_seed(9)
+    n, t, h, w = 2, 3, 5, 7
+    y = torch.randn(n, t, h, w, 192, generator=g).to(torch.bfloat16).cuda()
+    rgb = v.depth_to_space8(y)
+    lib.check_status()
+    ref = y.view(n, t, h, w, 3, 8, 8).permute(0, 4, 1, 2, 5, 3, 6).reshape(n, 3, t, h * 8, w * 8)
+    assert torch.equal(rgb, ref)
