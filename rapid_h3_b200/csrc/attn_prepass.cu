@@ -33,13 +33,21 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float* x) {
 // ---------------------------------------------------------------------------------------------
 // RMSNorm + 3-D RoPE. One warp per (token, head) row; lane l owns channels 4l..4l+3.
 // ---------------------------------------------------------------------------------------------
-// RMSNorm + rope of the four channels lane*4..lane*4+3 of one (token, head) row; returns the packed bf16 result.
-__device__ __forceinline__ uint2 rmsnorm_rope_row(const __nv_bfloat16* __restrict__ xrow,
-                                                  const __nv_bfloat16* __restrict__ w, float eps,
-                                                  const __nv_bfloat16* __restrict__ tab_row, int lane) {
-  float v[4], wv[4];
-  load4(xrow + lane * 4, v);
-  load4(w + lane * 4, wv);
+// The rope-table words of one token for this lane (lanes 0..23 hold pair indices 4*(lane % 12) .. +3).
+__device__ __forceinline__ void load_rope_words(const __nv_bfloat16* __restrict__ tab_row, int lane, uint32_t* tw) {
+  if (tab_row != nullptr && lane < 24) {
+    const int i0 = (lane < 12 ? lane : lane - 12) * 4;  // index of the pair in the table row
+    const __nv_bfloat16* t = tab_row + i0 * 4;
+    const uint4 t0 = __ldg(reinterpret_cast<const uint4*>(t));
+    const uint4 t1 = __ldg(reinterpret_cast<const uint4*>(t + 8));
+    tw[0] = t0.x, tw[1] = t0.y, tw[2] = t0.z, tw[3] = t0.w, tw[4] = t1.x, tw[5] = t1.y, tw[6] = t1.z, tw[7] = t1.w;
+  }
+}
+
+// RMSNorm + rope of the four channels lane*4..lane*4+3 of one (token, head) row given its values, the norm weights
+// of those channels and the token's rope words; returns the packed bf16 result.
+__device__ __forceinline__ uint2 rmsnorm_rope_vals(const float* v, const float* wv, float eps, const uint32_t* tw,
+                                                   bool has_tab, int lane) {
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < 4; ++j) ss = __fadd_rn(ss, __fmul_rn(v[j], v[j]));
@@ -49,18 +57,13 @@ __device__ __forceinline__ uint2 rmsnorm_rope_row(const __nv_bfloat16* __restric
 #pragma unroll
   for (int j = 0; j < 4; ++j) n[j] = bf16_round(__fmul_rn(__fmul_rn(r, v[j]), wv[j]));
   float o[4] = {n[0], n[1], n[2], n[3]};
-  if (tab_row != nullptr) {
+  if (has_tab) {
     // partner lane holds the other half of the rotary pair (channels +-48 = 12 lanes away)
     const int partner = lane < 12 ? lane + 12 : (lane < 24 ? lane - 12 : lane);
     float pn[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) pn[j] = __shfl_sync(0xffffffffu, n[j], partner);
     if (lane < 24) {
-      const int i0 = (lane < 12 ? lane : lane - 12) * 4;  // index of the pair in the table row
-      const __nv_bfloat16* t = tab_row + i0 * 4;
-      const uint4 t0 = __ldg(reinterpret_cast<const uint4*>(t));
-      const uint4 t1 = __ldg(reinterpret_cast<const uint4*>(t + 8));
-      const uint32_t tw[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float t00 = bf16_lo(tw[2 * j]), t01 = bf16_hi(tw[2 * j]);
@@ -75,18 +78,42 @@ __device__ __forceinline__ uint2 rmsnorm_rope_row(const __nv_bfloat16* __restric
   return make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
 }
 
+__device__ __forceinline__ uint2 rmsnorm_rope_row(const __nv_bfloat16* __restrict__ xrow,
+                                                  const __nv_bfloat16* __restrict__ w, float eps,
+                                                  const __nv_bfloat16* __restrict__ tab_row, int lane) {
+  float v[4], wv[4];
+  uint32_t tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  load4(xrow + lane * 4, v);
+  load4(w + lane * 4, wv);
+  load_rope_words(tab_row, lane, tw);
+  return rmsnorm_rope_vals(v, wv, eps, tw, tab_row != nullptr, lane);
+}
+
+// One warp per (token, group of HG consecutive heads): the token's rope words and the norm weights are loaded
+// once and the HG rows' loads are issued together. HG = 4 when H is a multiple of 4, else 1.
+template <int HG>
 __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_ss,
                                                            int64_t x_sh, __nv_bfloat16* __restrict__ y, int64_t y_ss,
                                                            int64_t y_sh, int64_t S, int H,
                                                            const __nv_bfloat16* __restrict__ w, float eps,
                                                            const __nv_bfloat16* __restrict__ tab) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = H / HG;
   const int64_t g = static_cast<int64_t>(blockIdx.x) * 8 + warp;
-  if (g >= S * H) return;
-  const int64_t s = g / H;
-  const int h = static_cast<int>(g - s * H);
-  const uint2 o = rmsnorm_rope_row(x + s * x_ss + h * x_sh, w, eps, tab ? tab + s * 48 * 4 : nullptr, lane);
-  *reinterpret_cast<uint2*>(y + s * y_ss + h * y_sh + lane * 4) = o;
+  if (g >= S * groups) return;
+  const int64_t s = g / groups;
+  const int h0 = static_cast<int>(g - s * groups) * HG;
+  float v[HG][4], wv[4];
+  uint32_t tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < HG; ++i) load4(x + s * x_ss + (h0 + i) * x_sh + lane * 4, v[i]);
+  load4(w + lane * 4, wv);
+  load_rope_words(tab ? tab + s * 48 * 4 : nullptr, lane, tw);
+#pragma unroll
+  for (int i = 0; i < HG; ++i) {
+    const uint2 o = rmsnorm_rope_vals(v[i], wv, eps, tw, tab != nullptr, lane);
+    *reinterpret_cast<uint2*>(y + s * y_ss + (h0 + i) * y_sh + lane * 4) = o;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -284,11 +311,16 @@ extern "C" int rh3_rmsnorm_rope3d(const void* x, int64_t x_ss, int64_t x_sh, voi
                     y_ss % 4 == 0 && y_sh % 4 == 0,
                 "rmsnorm_rope3d: rows must be 8-byte aligned (strides multiples of 4 elements)");
   RH3_CHECK_ARG(!rope_table || aligned(rope_table, 16), "rmsnorm_rope3d: rope table must be 16-byte aligned");
-  const int64_t rows = S * H;
-  RH3_CHECK_ARG((rows + 7) / 8 < (1ll << 31), "rmsnorm_rope3d: too many rows");
-  rmsnorm_rope_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), x_ss, x_sh, static_cast<__nv_bfloat16*>(y), y_ss, y_sh, S, (int)H,
-      static_cast<const __nv_bfloat16*>(weight), eps, static_cast<const __nv_bfloat16*>(rope_table));
+  const int hg = H % 4 == 0 ? 4 : 1;
+  const int64_t warps = S * (H / hg);
+  RH3_CHECK_ARG((warps + 7) / 8 < (1ll << 31), "rmsnorm_rope3d: too many rows");
+  const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  auto* yp = static_cast<__nv_bfloat16*>(y);
+  const auto* wp = static_cast<const __nv_bfloat16*>(weight);
+  const auto* tp = static_cast<const __nv_bfloat16*>(rope_table);
+  if (hg == 4) rmsnorm_rope_kernel<4><<<grid, 256, 0, stream>>>(xp, x_ss, x_sh, yp, y_ss, y_sh, S, (int)H, wp, eps, tp);
+  else rmsnorm_rope_kernel<1><<<grid, 256, 0, stream>>>(xp, x_ss, x_sh, yp, y_ss, y_sh, S, (int)H, wp, eps, tp);
   return check_cuda(cudaGetLastError(), "rmsnorm_rope3d launch");
 }
 
