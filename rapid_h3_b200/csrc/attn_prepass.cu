@@ -143,9 +143,16 @@ __global__ void __launch_bounds__(256) rope_scatter_kernel(const __nv_bfloat16* 
   const __nv_bfloat16* tab_row = tab ? tab + s * 48 * 4 : nullptr;
   __nv_bfloat16* out = dst.ptr[r] + (row0 + s) * 3 * w + hh * D + lane * 4;
   const int64_t hd = static_cast<int64_t>(H) * D;
-  const uint2 qo = rmsnorm_rope_row(row, qw, eps, tab_row, lane);
-  const uint2 ko = rmsnorm_rope_row(row + hd, kw, eps, tab_row, lane);
+  float qv[4], kv[4], qwv[4], kwv[4];
+  uint32_t tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  load4(row + lane * 4, qv);
+  load4(row + hd + lane * 4, kv);
   const uint2 vo = __ldg(reinterpret_cast<const uint2*>(row + 2 * hd + lane * 4));
+  load4(qw + lane * 4, qwv);
+  load4(kw + lane * 4, kwv);
+  load_rope_words(tab_row, lane, tw);  // q and k of a token share its rope words
+  const uint2 qo = rmsnorm_rope_vals(qv, qwv, eps, tw, tab_row != nullptr, lane);
+  const uint2 ko = rmsnorm_rope_vals(kv, kwv, eps, tw, tab_row != nullptr, lane);
   *reinterpret_cast<uint2*>(out) = qo;
   *reinterpret_cast<uint2*>(out + w) = ko;
   *reinterpret_cast<uint2*>(out + 2 * w) = vo;
