@@ -33,6 +33,13 @@ int rh3_sm_count(void);
 /* Synchronises `stream`, stores the device status word in *status_out (0 = every bounded device
  * wait completed; otherwise the code of the wait that gave up) and clears it. */
 int rh3_check_status(cudaStream_t stream, int* status_out);
+/* Self-test of the bounded device waits: launches one small CTA whose threads wait, for at most `max_polls`
+ * polls (1 .. 2^20), on a barrier that nothing ever completes. The wait gives up, the kernel records status
+ * 190 in the device status word (read it with rh3_check_status) and returns by itself; *left_normally (device
+ * memory, one int) is set to 1 when every thread left through the give-up path. Nothing faults or hangs: this is
+ * how the path "a wait ran out" of every kernel of the library is exercised. It has no counterpart in the
+ * reference (whose kernels wait without a limit). */
+int rh3_selftest_wait_expiry(int64_t max_polls, int* left_normally, cudaStream_t stream);
 
 /* ---- per-token quantizers (HBM-bound) ------------------------------------------------------ */
 /* q[M,K] int8, s[M] fp32: s = max(amax/127, 1e-12), q = clamp(rint(x/s), +-127).
@@ -121,7 +128,8 @@ int rh3_attn_kv_stats(const void* k, int64_t k_ss, int64_t k_sh, const void* v, 
  * allocated or freed. Limit: H * ceil(L/256) <= 8192; larger problems are rejected with an error.
  * The first call on a device looks up the array's device address; make that first call outside any stream
  * capture. All calls share the one array: two calls whose kernels overlap on the GPU (different streams)
- * race on it; calls on one stream are safe, and nothing needs to be cleared between calls.
+ * race on it; calls on one stream are safe, and nothing needs to be cleared between calls. Host threads may
+ * make their first calls concurrently (the address look-up is idempotent and stored atomically).
  * This entry point has no counterpart in the reference. */
 int rh3_attn_kv_stats_noalloc(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh,
                               int64_t L, int64_t H, float* kmean, float* vmean, float* vscale, cudaStream_t stream);

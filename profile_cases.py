@@ -1,9 +1,9 @@
 """Small single-kernel cases for profiling one kernel of the library in isolation.
 
-    python -m rapid_h3_b200.profile_cases attn  --L 16384 --H 8  [--iters 3]
-    python -m rapid_h3_b200.profile_cases gemm  --M 8192 --N 12288 --K 4096 [--epi plain|gated|swiglu]
-    python -m rapid_h3_b200.profile_cases quant --M 36436 --K 4096 [--kind plain|fp8|normmod|rot|normmod_rot]
-    python -m rapid_h3_b200.profile_cases prepass --L 16384 --H 8
+    python profile_cases.py attn  --L 16384 --H 8  [--iters 3]
+    python profile_cases.py gemm  --M 8192 --N 12288 --K 4096 [--epi plain|gated|swiglu]
+    python profile_cases.py quant --M 36436 --K 4096 [--kind plain|fp8|normmod|rot|normmod_rot]
+    python profile_cases.py prepass --L 16384 --H 8
 
 Each case builds seeded random inputs on the device, runs the kernel `--iters` times and prints the mean time
 from CUDA events, so the same command line serves a plain timing run and a profiler capture.
@@ -12,7 +12,7 @@ import argparse
 
 import torch
 
-from . import _lib, attn_int8, gemm, quantizers
+from rapid_h3_b200 import _lib, attn_int8, gemm, quantizers
 
 
 def _time(fn, iters):
@@ -51,7 +51,7 @@ def main():
         return torch.randn(*shape, device="cuda", generator=g)
 
     if a.case == "conv":
-        from . import vae
+        from rapid_h3_b200 import vae
         x = randn(1, a.T, a.HH, a.WW, a.Cin).to(torch.bfloat16)
         w = (0.02 * randn(a.Cout, 27, a.Cin)).to(torch.bfloat16)
         ms = _time(lambda: vae.conv3d_causal(x, w, want_stats=a.Cout % 32 == 0), a.iters)
@@ -59,7 +59,7 @@ def main():
         print(f"conv3d {a.T}x{a.HH}x{a.WW} {a.Cin}->{a.Cout}: {ms:.3f} ms, {fl / ms / 1e9:.1f} TFLOP/s")
         return
     if a.case == "vae":
-        from . import vae
+        from rapid_h3_b200 import vae
         dec = vae.VAEDecoder(seed=0)
         latent = randn(1, 16, a.T, a.HH, a.WW).to(torch.bfloat16)
         ms = _time(lambda: dec.decode(latent), a.iters)

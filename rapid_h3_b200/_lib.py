@@ -20,6 +20,7 @@ SIGNATURES = {
     "rh3_version": [],
     "rh3_sm_count": [],
     "rh3_check_status": [_P, _P],
+    "rh3_selftest_wait_expiry": [_I64, _P, _P],
     "rh3_quant_rows_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_quant_rows_fp8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_swiglu_quant_rows_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],

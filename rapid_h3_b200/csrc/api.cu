@@ -103,7 +103,37 @@ int* device_status_word() {
   return cache[dev];
 }
 
+// Self-test of the bounded-wait machinery: 64 threads wait, with a limit of `max_polls` polls, on an mbarrier that
+// nobody ever arrives at. The wait runs out, the first thread to give up raises the CTA's abort flag and records
+// ST_TIMEOUT_SELFTEST in the status word, the others see the flag and leave, and the kernel returns by itself.
+__global__ void wait_expiry_kernel(uint32_t max_polls, int* status, int* left_normally) {
+  __shared__ uint64_t never;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&never, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const bool done = mbar_wait_polls(&never, 0, &abort_flag, status, ST_TIMEOUT_SELFTEST, max_polls);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *left_normally = done ? 0 : 1;
+    mbar_inval(&never);
+  }
+}
+
 }  // namespace rh3
+
+extern "C" int rh3_selftest_wait_expiry(int64_t max_polls, int* left_normally, cudaStream_t stream) {
+  RH3_CHECK_ARG(max_polls >= 1 && max_polls <= (1 << 20), "selftest_wait_expiry: max_polls=%lld must be in [1, 2^20]",
+                (long long)max_polls);
+  RH3_CHECK_ARG(left_normally != nullptr, "selftest_wait_expiry: null result pointer");
+  int* w = rh3::device_status_word();
+  if (!w) return rh3::set_error(RH3_ARG_ERROR, "no device status word (is a CUDA device current?)");
+  rh3::wait_expiry_kernel<<<1, 64, 0, stream>>>(static_cast<uint32_t>(max_polls), w, left_normally);
+  return rh3::check_cuda(cudaGetLastError(), "selftest_wait_expiry launch");
+}
 
 extern "C" const char* rh3_last_error_string(void) { return rh3::g_err; }
 

@@ -16,6 +16,8 @@
 // (`q8(x, 1, 64)`, `f8(x, 0)`). Differences that are deliberate: IEEE division/sqrt instead of the
 // .approx.ftz forms (the CPU oracle must be able to reproduce every bit), block-64 scales and an
 // e4m3 V scaled to 448 by its own abs-max.
+#include <atomic>
+
 #include "common.cuh"
 #include "rapidh3_b200.h"
 
@@ -399,18 +401,22 @@ constexpr int64_t KV_STATS_NOALLOC_MAX_UNITS = 8192;  // limit on H * ceil(L / 2
 static __device__ __align__(256) float g_kv_stats_scratch[KV_STATS_NOALLOC_MAX_UNITS * 4 * 128];
 
 static int kv_stats_scratch_address(float** out) {
-  static float* per_device[64] = {};
+  // Filled on the first call per device. Host threads that race here each look the address up and store the same
+  // value; the entries are atomics so that such a race is well defined.
+  static std::atomic<float*> per_device[64] = {};
   int dev = -1;
   if (int e = rh3::check_cuda(cudaGetDevice(&dev), "attn_kv_stats_noalloc: cudaGetDevice")) return e;
   if (dev < 0 || dev >= 64) return rh3::set_error(RH3_ARG_ERROR, "attn_kv_stats_noalloc: device index %d out of range", dev);
-  if (per_device[dev] == nullptr) {
+  float* addr = per_device[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
     void* p = nullptr;
     if (int e = rh3::check_cuda(cudaGetSymbolAddress(&p, g_kv_stats_scratch),
                                 "attn_kv_stats_noalloc: cudaGetSymbolAddress"))
       return e;
-    per_device[dev] = static_cast<float*>(p);
+    addr = static_cast<float*>(p);
+    per_device[dev].store(addr, std::memory_order_release);
   }
-  *out = per_device[dev];
+  *out = addr;
   return 0;
 }
 

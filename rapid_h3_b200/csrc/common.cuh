@@ -30,6 +30,7 @@ enum : int {
   ST_TIMEOUT_ACC_EMPTY = 104,   // MMA issuer waited too long for a free accumulator
   ST_TIMEOUT_P_READY = 105,     // attention: MMA issuer waited too long for P
   ST_TIMEOUT_PV_DONE = 106,     // attention: softmax waited too long for P.V
+  ST_TIMEOUT_SELFTEST = 190,    // rh3_selftest_wait_expiry: the wait that is meant to run out did
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -73,9 +74,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 // waiter polls it so the whole CTA drains instead of hanging. Returns true when the phase
 // completed, false when the wait was abandoned (the caller must then leave its loop).
 // The limit is generous (seconds): a healthy wait finishes in microseconds.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
+__device__ __forceinline__ bool mbar_wait_polls(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                int* status, int code, uint32_t max_polls) {
+  for (uint32_t it = 0; it < max_polls; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) {
       if (*abort_flag) return false;
@@ -85,6 +86,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort_flag = 1;
   if (status) atomicCAS(status, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  return mbar_wait_polls(bar, parity, abort_flag, status, code, 1u << 24);
 }
 
 // The same bounded wait for roles that share a scheduler with busy compute warps (a TMA producer, an MMA issuer):
@@ -99,6 +104,24 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
   *abort_flag = 1;
   if (status) atomicCAS(status, 0, code);
   return false;
+}
+
+// Named barrier `id` over `nthreads` threads that also ORs a predicate: every participant gets true when any of
+// them passed true. The epilogue warps use it to agree on leaving their tile loop after a wait was abandoned, so
+// that no warp goes on to a barrier the others will never reach.
+__device__ __forceinline__ bool bar_sync_or(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, %2, %3, p;\n\t"
+      "selp.b32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(nthreads)
+      : "memory");
+  return r != 0;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -183,8 +183,10 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
       asm volatile("bar.sync 1, 128;" ::: "memory");
       for (int i = et; i < p.BN; i += 128)
         tail->bias[i] = (p.bias && n0 + i < p.Cout) ? __bfloat162float(p.bias[n0 + i]) : 0.f;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) break;
+      // the four warps leave together: a warp that gave up its wait takes the others with it at this barrier
+      // (which also publishes the staged bias), so none of them waits at the next tile's barrier alone
+      const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
+      if (bar_sync_or(1, 128, !got)) break;
       tc_fence_after();
       const int m = quad * 32 + lane;
       const int hh = m / p.bw, ww = m - hh * p.bw;
@@ -422,9 +424,12 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
   choose_tile(p.H, p.W, &p.bh, &p.bw);
   p.tiles_h = (p.H + p.bh - 1) / p.bh;
   p.tiles_w = (p.W + p.bw - 1) / p.bw;
-  // output channels per tile: the whole width when it fits one accumulator, else an even split
+  // output channels per tile: the whole width when it fits one accumulator, else an even split. The epilogue walks
+  // a tile in 32-column chunks, so a split tile is a multiple of 32 wide: a chunk must never reach into the columns
+  // of the next tile (weight rows past Cout are zero-filled by TMA and their stores are skipped).
   const int splits = (p.Cout + 255) / 256;
   p.BN = ((p.Cout + splits - 1) / splits + 15) / 16 * 16;
+  if (splits > 1) p.BN = (p.BN + 31) / 32 * 32;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.out = static_cast<__nv_bfloat16*>(out);

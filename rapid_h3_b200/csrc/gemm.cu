@@ -189,8 +189,10 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (EPI == EPI_F16 || EPI == EPI_SWIGLU_F16) tail->aux[c] = n < p.N ? __half2float(p.bias_h[n]) : 0.f;
         if (EPI == EPI_F16) tail->aux2[c] = (p.rscale_h && n < p.N) ? __half2float(p.rscale_h[n]) : 0.f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL)) break;
+      // the four warps leave together: a warp that gave up its wait takes the others with it at this barrier
+      // (which also publishes the staged columns), so none of them waits at the next tile's barrier alone
+      const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
+      if (bar_sync_or(1, 128, !got)) break;
       tc_fence_after();
       const int row = m_blk * BM + quad * 32 + lane;
       const bool row_ok = row < p.M;

@@ -14,7 +14,8 @@
 //   KIND_HEADS   x given group-major [G, M, gw] (gw = 128: head-major attention output);
 //                output column k = group k/gw, channel k%gw
 // The division x / s is done as x * (1/s) with an exact IEEE re-division only for the rare values
-// that land within 1e-3 of a rounding tie, which keeps the codes identical to a true division.
+// that land within 2^-14 of a rounding tie (the product is at most 1.5e-5 away from the true quotient),
+// which keeps the codes identical to a true division.
 #include "common.cuh"
 #include "rapidh3_b200.h"
 

@@ -39,18 +39,23 @@ def _gemm(xq, xs, wq, ws, bias, kind, dtype, acc_dump=None, out=None):
 
 
 def int8_gemm(xq, xs, wq, ws, bias=None, config=2, acc_dump=None, out=None):
-    """xq [M,K] int8, xs [M,1] fp32, wq [N,K] int8, ws [1,N] fp32 -> bf16 [M,N].
-    acc_dump (int32 [M,N], optional) receives the raw int32 accumulators."""
+    """W8A8 int8 GEMM with row-wise scales: bf16 [M, N] = ((acc * xs[m]) * ws[n]) + bias[n], acc the exact int32
+    dot product of row m of xq [M, K] with row n of wq [N, K]. xs / ws are fp32 with M / N elements in any shape.
+    Extras of this library: `acc_dump` (int32 [M, N]) receives the raw accumulators for parity checks, `out`
+    (bf16, unit column stride) is written instead of a new tensor. `config` is accepted and ignored."""
     return _gemm(xq, xs, wq, ws, bias, _lib.KIND_I8, torch.int8, acc_dump, out)
 
 
 def fp8_gemm(xq, xs, wq, ws, bias=None, config=2, fast_accum=True, acc_dump=None, out=None):
-    """xq [M,K] fp8, xs [M,1] fp32, wq [N,K] fp8, ws [1,N] fp32 -> bf16 [M,N]."""
+    """The same GEMM on e4m3 codes with fp32 accumulation (`acc_dump` is then fp32 bits). `config` and
+    `fast_accum` are accepted and ignored: the tensor core accumulates in fp32 either way."""
     return _gemm(xq, xs, wq, ws, bias, _lib.KIND_F8, torch.float8_e4m3fn, acc_dump, out)
 
 
 def int8_gemm_gated_residual(xq, xs, wq, ws, gate, resid, config=6):
-    """resid[M,N] += bf16(xq @ wq^T * xs * ws) * gate[N], in place (addcmul_ semantics)."""
+    """In place: resid[m, n] = bf16(fma(bf16((acc * xs[m]) * ws[n]), gate[n], resid[m, n])), which is what
+    `resid.addcmul_(y, gate)` gives for the bf16 GEMM result y. `resid` may be a row slice of a larger tensor (any
+    row stride, unit column stride); M = 0 does nothing. Returns `resid`."""
     m, n, k, xs, ws = _check(xq, xs, wq, ws, torch.int8)
     _lib.require_cuda(gate, resid)
     if gate.dtype != torch.bfloat16 or gate.numel() != n or not gate.is_contiguous():
@@ -64,16 +69,22 @@ def int8_gemm_gated_residual(xq, xs, wq, ws, gate, resid, config=6):
 
 
 def swiglu_perm(n2, device):
-    """Row order for an fc1 weight [gate (F rows) | up (F rows)] so that each group of 8 rows is
-    [gate 4j..4j+3 | up 4j..4j+3], the order int8_gemm_swiglu's epilogue expects."""
+    """Index tensor [n2] that re-orders the rows of an fc1 weight stored as F gate rows followed by F up rows
+    (n2 = 2F, F a multiple of 4) into runs of eight: four gate rows, then the four up rows they multiply. The
+    SwiGLU epilogue finds gate and up of an output column in the same 8-column group of its accumulator tile that
+    way. Entry 8j + i is 4j + i for i < 4 and F + 4j + (i - 4) otherwise (layout contract of the reference's
+    fused fc1 GEMM, cutlass_fp8.py:55-62)."""
     f = n2 // 2
-    j = torch.arange(0, f, 4, device=device)
-    blk = torch.arange(4, device=device)
-    return torch.stack([j[:, None] + blk, f + j[:, None] + blk], dim=1).reshape(-1)
+    if n2 != 2 * f or f % 4:
+        raise RuntimeError("swiglu_perm: the hidden width must be a multiple of 4")
+    rows = torch.arange(n2, device=device).view(2, f // 4, 4)   # [gate | up] x groups of four
+    return rows.transpose(0, 1).reshape(-1)
 
 
 def int8_gemm_swiglu(xq, xs, wq_perm, ws_perm, config=6, out=None):
-    """h [M, F] = bf16(silu(g) * u) for an fc1 whose rows were permuted with swiglu_perm."""
+    """fc1 and SwiGLU in one kernel: with g, u = bf16((acc * xs) * ws) of a gate row and its up row,
+    out [M, N/2] = bf16(g / (1 + exp(-g)) * u). `wq_perm` / `ws_perm` are the weight codes and scales re-ordered with
+    swiglu_perm (N = 2F rows, a multiple of 16)."""
     m, n, k, xs, ws = _check(xq, xs, wq_perm, ws_perm, torch.int8)
     if n % 16:
         raise RuntimeError("int8_gemm_swiglu: N must be a multiple of 16")

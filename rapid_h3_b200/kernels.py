@@ -16,8 +16,12 @@ FP8_MAX = 448.0
 
 @dataclass
 class QWeight:
-    q: torch.Tensor      # [N, K] quantized
-    scale: torch.Tensor  # [1, N] fp32
+    """A quantized weight: codes [N, K] and one fp32 scale per output row, shaped [1, N] (kernels.py:29-32 of the
+    reference). `layout` says in which order the N rows are held: "rows" = the module's own order, "swiglu8" = the
+    gate/up interleave of gemm.swiglu_perm that the fused fc1 + SwiGLU GEMM reads."""
+    q: torch.Tensor
+    scale: torch.Tensor
+    layout: str = "rows"
 
 
 _ROWWISE_I8 = ("int8_rowwise", "int8_fast")

@@ -18,49 +18,91 @@ from . import quantizers as tq
 
 NAME_RE = re.compile(r"^blocks\.(\d+)\.(attn|mlp|cross)\.(qkv_proj|out_proj|fc1|fc2|q_proj|kv_proj)$")
 
-_IDX_CACHE = {}
+_IDX_CACHE = {}   # (segment tuple, S, device) -> int32 [S]; a handful of entries at most
+_IDX_CACHE_MAX = 8
 
 
 def _row_index(segments, s, device):
-    """Per-token modulation-row index (int32 [S]) from [(start, stop, row)], cached per segment list."""
-    key = (id(segments), s, str(device))
-    hit = _IDX_CACHE.get(key)
-    if hit is not None and hit[0] is segments:
-        return hit[1]
-    idx = torch.empty(s, dtype=torch.int32, device=device)
+    """Which row of the modulation tables every token of the packed sequence reads: int32 [S].
+
+    `segments` is the block's `mod_segments`, a list of (start, stop, row). `row` is either one table row for the
+    whole span or an integer tensor with one row per token of the span (per-token conditioning). Spans given as
+    plain integers are remembered by value, so the same segmentation costs one fill per process, however many
+    list objects carry it; spans with tensors are rebuilt on every call because their content may change.
+    Contract: custom_nodes/rapid_h3/__init__.py:189-200 of the reference."""
+    per_token = any(torch.is_tensor(row) for _, _, row in segments)
+    key = None
+    if not per_token:
+        key = (tuple((int(a), int(b), int(row)) for a, b, row in segments), int(s), str(device))
+        hit = _IDX_CACHE.get(key)
+        if hit is not None:
+            return hit
+    idx = torch.zeros(s, dtype=torch.int32, device=device)
     for a, b, row in segments:
-        idx[a:b] = int(row)
-    _IDX_CACHE.clear()
-    _IDX_CACHE[key] = (segments, idx)
+        if b <= a:
+            continue
+        if torch.is_tensor(row):
+            if row.numel() not in (1, b - a):
+                raise RuntimeError(f"mod_segments: span [{a}, {b}) carries {row.numel()} rows")
+            idx[a:b].copy_(row.reshape(-1).to(device=device, dtype=torch.int32))
+        else:
+            idx[a:b].fill_(int(row))
+    if key is not None:
+        if len(_IDX_CACHE) >= _IDX_CACHE_MAX:
+            _IDX_CACHE.pop(next(iter(_IDX_CACHE)))
+        _IDX_CACHE[key] = idx
     return idx
+
+
+def _stored_as_rotated_int8(w):
+    """True when `w` already is what the `int8_rot` recipe stores: ComfyUI's int8_convrot tensor, i.e. int8 codes
+    `_qdata` [N, K] of the weight rotated in groups of 256 with one scale per output row in `_params`."""
+    meta = getattr(w, "_params", None)
+    codes = getattr(w, "_qdata", None)
+    if meta is None or codes is None or codes.dtype != torch.int8:
+        return False
+    return (bool(getattr(meta, "convrot", False)) and getattr(meta, "convrot_groupsize", 0) == tq.ROT_GROUP
+            and not getattr(meta, "transposed", False))
 
 
 class _QuantLinear:
     """Replacement forward bound to one Linear: row quantizer + W8A8 GEMM, bias added afterwards in bf16
-    (reference: __init__.py:132-167). The quantized weight is made once and cached."""
+    (reference: __init__.py:132-167). The quantized weight is made on first use and kept until the weight it was
+    made from changes: the cache key is the owning patcher's `patches_uuid` when the module came with one (the
+    reference's key, __init__.py:119-130), the weight tensor's identity and in-place version, and the device."""
 
-    def __init__(self, module, name, mode, measure_every=0, stats=None):
+    def __init__(self, module, name, mode, measure_every=0, stats=None, patcher=None):
         self.module, self.name, self.mode = module, name, mode
         self.measure_every, self.stats = measure_every, stats if stats is not None else {}
+        self.patcher = patcher
         self.qweight = None
+        self.cache_key = None
         self.calls = 0
 
     def _make_qweight(self, w):
-        """Quantize a bf16 weight, or adopt as is a weight that is already stored the way `int8_rot` needs it
-        (ComfyUI's int8_convrot layout: `_qdata` int8 [N,K] rotated in groups of 256, `_params.scale` per output
-        row), so such checkpoints run without a bf16 copy (reference __init__.py:107-117)."""
-        p = getattr(w, "_params", None)
-        if (p is not None and hasattr(w, "_qdata") and self.mode == "int8_rot" and getattr(p, "convrot", False)
-                and getattr(p, "convrot_groupsize", 0) == tq.ROT_GROUP and not getattr(p, "transposed", False)
-                and w._qdata.dtype == torch.int8):
-            return kernels.QWeight(w._qdata.contiguous(), p.scale.float().reshape(1, -1).contiguous())
-        if p is not None and hasattr(w, "dequantize"):
+        """QWeight of `w` for this linear's mode. A checkpoint that is already stored as rotated int8 is taken over
+        as it is when the mode is `int8_rot` (no bf16 copy is ever made); any other quantized tensor is expanded
+        first and quantized again in this mode (contract: reference __init__.py:107-117)."""
+        if self.mode == "int8_rot" and _stored_as_rotated_int8(w):
+            scale = w._params.scale.to(torch.float32).reshape(1, -1)
+            return kernels.QWeight(w._qdata.contiguous(), scale.contiguous())
+        if hasattr(w, "_params") and hasattr(w, "dequantize"):
             w = w.dequantize()
         return kernels.quantize_weight(w.detach(), self.mode)
 
+    def _weight_key(self, device):
+        w = self.module.weight
+        uuid = getattr(self.patcher, "patches_uuid", None)
+        return (uuid, id(w), getattr(w, "_version", 0), tuple(w.shape), str(device))
+
     def qweight_for(self, x=None):
-        if self.qweight is None:
-            self.qweight = self._make_qweight(self.module.weight)
+        w = self.module.weight
+        if self.qweight is not None and w.numel() == 0:
+            return self.qweight          # the bf16 copy was released on purpose: the int8 copy is all there is
+        key = self._weight_key(w.device if x is None else x.device)
+        if self.qweight is None or key != self.cache_key:
+            self.qweight = self._make_qweight(w)
+            self.cache_key = key
         return self.qweight
 
     def __call__(self, x):
@@ -69,8 +111,8 @@ class _QuantLinear:
         shape = x.shape
         qw = self.qweight_for(x)
         y = kernels.linear(x.reshape(-1, shape[-1]), qw, self.mode)
-        if getattr(qw, "swiglu_perm", False):  # fc1 weight held in SwiGLU-epilogue order
-            y = y[:, torch.argsort(cf.swiglu_perm(y.shape[-1], y.device))]
+        if qw.layout == "swiglu8":  # the fused block keeps fc1 in its epilogue's row order: put the columns back
+            y = y.index_select(-1, torch.argsort(cf.swiglu_perm(y.shape[-1], y.device)))
         if self.module.bias is not None:
             y = y + self.module.bias.to(y.dtype)
         y = y.reshape(*shape[:-1], y.shape[-1])
@@ -118,12 +160,13 @@ class FusedBlock:
         return torch.finfo(torch.bfloat16).eps if e is None else e
 
     def _fc1_swiglu_weight(self):
-        """fc1's int8 weight with rows interleaved for the SwiGLU epilogue (cached in place of the plain copy)."""
+        """(codes, scales) of fc1 with its output rows in the order the SwiGLU epilogue pairs them
+        (gemm.swiglu_perm). The re-ordered copy takes the place of the plain one in fc1's cache, tagged
+        `layout="swiglu8"`, so only one int8 copy of the largest weight of the block is resident."""
         qw = self.fc1_q.qweight_for()
-        if not getattr(qw, "swiglu_perm", False):
-            perm = cf.swiglu_perm(qw.q.shape[0], qw.q.device)
-            qw = kernels.QWeight(qw.q[perm].contiguous(), qw.scale[:, perm].contiguous())
-            qw.swiglu_perm = True
+        if qw.layout != "swiglu8":
+            order = cf.swiglu_perm(qw.q.shape[0], qw.q.device)
+            qw = kernels.QWeight(qw.q.index_select(0, order), qw.scale.index_select(1, order), layout="swiglu8")
             self.fc1_q.qweight = qw
         return qw.q, qw.scale
 

@@ -11,7 +11,13 @@ import torch
 
 from . import _lib, gemm, kernels, quantizers
 
-_ROWS = [0, 0]  # rows given the residual pass, all rows
+# how often the second pass ran: [rows that took it, rows seen]; `residual_share()` reads it
+_ROWS = [0, 0]
+
+
+def residual_share():
+    """Fraction of the rows seen so far that were given the residual pass (0.0 before any call)."""
+    return _ROWS[0] / _ROWS[1] if _ROWS[1] else 0.0
 
 
 def rot_residual_quant_rows_i8(x, q1, s1, rows):
@@ -36,28 +42,40 @@ class _TELinear:
             raise NotImplementedError(f"text-encoder mode {mode!r} is not implemented")
         self.qweight, self.bias, self.mode, self.outlier_ratio = qweight, bias, mode, outlier_ratio
 
+    def _outlier_rows(self, x32, s1):
+        """Indices of the rows whose rotated peak is more than `outlier_ratio` times their rms. H256 is orthonormal,
+        so the rotated row has the rms of the input row, and its abs-max is 127 * s1 by construction of the scale:
+        nothing has to be rotated again to find them (selection rule of the reference, te_quant.py:97-99)."""
+        rms = x32.square().mean(dim=-1).sqrt().clamp_min(1e-12)
+        peak_over_rms = (127.0 * s1.reshape(-1)) / rms
+        return torch.nonzero(peak_over_rms > self.outlier_ratio).reshape(-1)
+
+    def _matmul(self, x2):
+        """x2 [M, K] in the caller's dtype -> W8A8 product in bf16 or, when rows took the second pass, fp32."""
+        qw = self.qweight
+        x16 = x2.to(torch.bfloat16).contiguous()
+        if self.mode == "int8_rot_plain":
+            return kernels.linear(x16, qw, "int8_rot")
+        q1, s1 = quantizers.rot_quant_rows_i8(x16)
+        y = gemm.int8_gemm(q1, s1, qw.q, qw.scale)
+        x32 = x2.float().contiguous()
+        rows = self._outlier_rows(x32, s1)
+        _ROWS[1] += x2.shape[0]
+        if rows.numel() == 0:
+            return y
+        # second int8 pass on what the first quantization lost on those rows: rotate(x) - q1 * s1, quantized with
+        # its own row scale and multiplied with the same weight; the two products add up in fp32
+        q2, s2 = rot_residual_quant_rows_i8(x32, q1, s1, rows)
+        y = y.float()
+        y[rows] += gemm.int8_gemm(q2, s2, qw.q, qw.scale).float()
+        _ROWS[0] += rows.numel()
+        return y
+
     def __call__(self, x):
         if x.device.type != "cuda":
             raise NotImplementedError("_TELinear: CUDA tensors only (no fallback path)")
-        qw = self.qweight
-        shape = x.shape
-        x2 = x.reshape(-1, shape[-1])
-        if self.mode == "int8_rot_plain":
-            y = kernels.linear(x2.to(torch.bfloat16).contiguous(), qw, "int8_rot")
-        else:
-            q1, s1 = quantizers.rot_quant_rows_i8(x2.to(torch.bfloat16).contiguous())
-            y = gemm.int8_gemm(q1, s1, qw.q, qw.scale)
-            # the rotation keeps the row norm: amax / rms of the rotated row from the scale and the input
-            xf = x2.float().contiguous()
-            ratio = 127.0 * s1[:, 0] / xf.pow(2).mean(-1).sqrt().clamp_min(1e-12)
-            rows = (ratio > self.outlier_ratio).nonzero()[:, 0]
-            if rows.numel():
-                q2, s2 = rot_residual_quant_rows_i8(xf, q1, s1, rows)
-                y = y.float()
-                y[rows] += gemm.int8_gemm(q2, s2, qw.q, qw.scale).float()
-                _ROWS[0] += rows.numel()
-            _ROWS[1] += x2.shape[0]
-        y = y.to(x.dtype)
+        lead, k = x.shape[:-1], x.shape[-1]
+        y = self._matmul(x.reshape(-1, k)).to(x.dtype)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)
-        return y.reshape(*shape[:-1], y.shape[-1])
+        return y.reshape(*lead, y.shape[-1])

@@ -74,10 +74,13 @@ def vae_gemm(xq, wq, xs, ws, bias, rscale=None, resid=None, config=6):
 
 
 def _interleave_rows(t, n):
-    """Rows [gate 0..n/2 | up n/2..n] -> [g 4j..4j+3 | u 4j..4j+3] for j = 0..n/8."""
-    half = n // 2
-    return torch.stack([t[:half].reshape(half // 4, 4, *t.shape[1:]),
-                        t[half:].reshape(half // 4, 4, *t.shape[1:])], dim=1).reshape(n, *t.shape[1:])
+    """Re-order the first axis of `t` (n rows: n/2 gate rows, then n/2 up rows) into runs of four gate rows
+    followed by their four up rows, the order vae_gemm_swiglu reads weights, scales and biases in (same layout
+    as gemm.swiglu_perm; the reference builds it in vae_fast.py:259-263)."""
+    if n % 8:
+        raise RuntimeError("_interleave_rows: n must be a multiple of 8")
+    rest = tuple(t.shape[1:])
+    return t.reshape(2, n // 8, 4, *rest).transpose(0, 1).reshape(n, *rest)
 
 
 def vae_gemm_swiglu(xq, wq, xs, ws, bias, config=6):

@@ -1,0 +1,38 @@
+"""The give-up path of the bounded device waits, exercised without faulting or hanging anything: a small kernel
+waits, with a limit of a few thousand polls, on a barrier nothing ever completes; it must come back by itself,
+report its code through the device status word, and leave the context and the status word usable."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_a_wait_that_runs_out_reports_its_code_and_the_library_goes_on():
+    from rapid_h3_b200 import _lib as lib, quantizers
+    assert torch.cuda.is_available()
+    lib.check_status()                                   # clean before
+    left = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.call("rh3_selftest_wait_expiry", 3000, left.data_ptr(), lib.stream())
+    st = ctypes.c_int(0)
+    lib.call("rh3_check_status", lib.stream(), ctypes.addressof(st))
+    assert st.value == 190                               # ST_TIMEOUT_SELFTEST
+    assert "gave up" in lib.last_error()
+    assert left.item() == 1                              # every thread left through the give-up path
+    # the word was cleared by the read, and kernels still run
+    lib.check_status()
+    x = torch.randn(64, 512, device="cuda").to(torch.bfloat16)
+    q, s = quantizers.quant_rows_i8(x)
+    torch.cuda.synchronize()
+    assert (q.float().abs().amax(dim=1) == 127).all()
+    lib.check_status()
+
+
+def test_check_status_raises_on_a_recorded_code():
+    from rapid_h3_b200 import _lib as lib
+    left = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib.call("rh3_selftest_wait_expiry", 200, left.data_ptr(), lib.stream())
+    with pytest.raises(RuntimeError, match="190"):
+        lib.check_status()
+    lib.check_status()

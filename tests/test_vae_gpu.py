@@ -22,7 +22,8 @@ def vae():
 
 
 @pytest.mark.parametrize("shape", [(1, 3, 6, 21, 64, 64), (2, 4, 9, 10, 128, 256), (1, 2, 24, 42, 64, 512),
-                                   (1, 5, 7, 5, 192, 192), (1, 1, 1, 1, 64, 16)])
+                                   (1, 5, 7, 5, 192, 192), (1, 1, 1, 1, 64, 16),
+                                   (1, 2, 6, 7, 64, 288), (1, 2, 5, 9, 64, 480)])  # split tiles that are not 32 wide
 def test_conv3d_causal_matches_oracle(vae, shape):
     v, lib = vae
     n, t, h, w, cin, cout = shape

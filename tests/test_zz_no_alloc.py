@@ -46,6 +46,27 @@ def test_noalloc_kv_stats_equals_regular_entry_twice_in_a_row():
     lib.check_status()
 
 
+@pytest.mark.parametrize("l, h", [(1, 8192), (65536, 32)])
+def test_noalloc_kv_stats_at_exactly_the_builtin_limit(l, h):
+    """8192 units, the last element of the built-in array included: many heads of one token, and many chunks of
+    few heads. One unit more is refused."""
+    from rapid_h3_b200 import _lib as lib
+    g = torch.Generator(device="cuda").manual_seed(l + h)
+    k = torch.randn(l, h, 128, device="cuda", generator=g).to(torch.bfloat16)
+    v = (torch.randn(l, h, 128, device="cuda", generator=g) - 0.5).to(torch.bfloat16)
+    got = _stats(lib, "rh3_attn_kv_stats_noalloc", k, v, with_scratch=False)
+    ref = _stats(lib, "rh3_attn_kv_stats", k, v, with_scratch=True)
+    for a, b in zip(got, ref):
+        assert torch.equal(a, b)
+    lib.check_status()
+    out = torch.zeros(3, 1, 128, device="cuda")
+    l2, h2 = (l, h + 1) if l == 1 else (l + 1, h)
+    rc = lib.lib().rh3_attn_kv_stats_noalloc(k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0),
+                                             v.stride(1), l2, h2, out[0].data_ptr(), out[1].data_ptr(),
+                                             out[2].data_ptr(), lib.stream())
+    assert rc < 0 and "exceeds the built-in scratch limit" in lib.last_error()
+
+
 def test_noalloc_kv_stats_rejects_sizes_beyond_the_builtin_scratch():
     from rapid_h3_b200 import _lib as lib
     k = torch.zeros(8, 1, 128, device="cuda", dtype=torch.bfloat16)
