@@ -42,6 +42,24 @@ def peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+# DRAM traffic of the self-attention main kernel from one ncu capture (profiles/attn_int8_kernel_dram_block_workload.md):
+# dram__bytes_read.sum + dram__bytes_write.sum of the launch at Lq = Lk = 36,436, H = 32, and the first 16 hex digits of
+# the SHA-256 of the kernel source the capture was made with. A different source means the figure is stale: the
+# bench then reports traffic null instead of a number that no longer belongs to the kernel it times.
+ATTN_TRAFFIC = {"bytes": 719.53e6, "lq": 36436, "lk": 36436, "heads": 32, "attn_cu_sha16": "0" * 16}
+
+
+def attn_traffic(alg_bytes_this_launch):
+    import hashlib
+    src = os.path.join(ROOT, "rapid_h3_b200", "csrc", "attn.cu")
+    sha = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16]
+    if sha != ATTN_TRAFFIC["attn_cu_sha16"]:
+        return None, f"no capture for this kernel source (sha {sha})"
+    t = ATTN_TRAFFIC
+    ref = t["heads"] * 128 * (t["lq"] + 2 * t["lk"]) + t["heads"] * 128 * 2 * t["lq"]
+    return t["bytes"] * alg_bytes_this_launch / ref, "bytes per launch (ncu capture, scaled by operand + output bytes)"
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -140,11 +158,15 @@ def cpu_port_step_seconds(workload, rows=1024, attn_rows=256):
                    "linear_s_per_rows": lin, "attn_s_per_head_rows": t_attn, "prepass_s_per_head": t_pre}
 
 
+# bounded CPU sample shared by the cpu_baseline leg and the --impl reference arm (5-10 s of CPU work per step)
+CPU_SAMPLE_ROWS, CPU_SAMPLE_ATTN_ROWS = 12288, 4096
+
+
 def cpu_baseline_record(workload):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cpu_port_step_seconds(workload, rows=128, attn_rows=32)  # warm-up
-    val, info = cpu_port_step_seconds(workload, rows=12288, attn_rows=4096)  # ~10-20 s of CPU work
+    val, info = cpu_port_step_seconds(workload, rows=CPU_SAMPLE_ROWS, attn_rows=CPU_SAMPLE_ATTN_ROWS)
     return {"value": val, "unit": "s/step", "cores": cores, "kind": "port",
             "sample": (f"row-local ops of one block on {info['rows']} of the tokens, attention of 1 head on "
                        f"{info['attn_rows']} query rows x all keys ({info['sample_seconds']:.1f} s of CPU work), "
@@ -194,7 +216,7 @@ def run_reference(args, rank):
         cpu_port_step_seconds(args.workload, rows=128, attn_rows=32)
     vals = []
     for _ in range(args.steps):
-        v, info = cpu_port_step_seconds(args.workload, rows=512, attn_rows=128)
+        v, info = cpu_port_step_seconds(args.workload, rows=CPU_SAMPLE_ROWS, attn_rows=CPU_SAMPLE_ATTN_ROWS)
         vals.append(v)
     val = statistics.median(vals)
     rec = {"impl": "reference", "metric": "H3 DiT step seconds @768x1344x141f", "value": val, "unit": "s/step",
@@ -202,8 +224,10 @@ def run_reference(args, rank):
            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
            "data": "synthetic", "config": workload_config(args.workload, args.gpus),
            "cpu_baseline": {"value": val, "unit": "s/step", "cores": cores, "kind": "port",
-                            "sample": "per step: row-local ops of one block on 512 tokens + attention of 1 head on "
-                                      "128 query rows x all keys, scaled linearly to the full step"},
+                            "sample": f"per step: row-local ops of one block on {CPU_SAMPLE_ROWS} tokens + attention of "
+                                      f"1 head on {CPU_SAMPLE_ATTN_ROWS} query rows x all keys "
+                                      f"({info['sample_seconds']:.1f} s of CPU work), scaled linearly to the full step; "
+                                      "the same sample as the cpu_baseline leg of the GPU arm"},
            "e2e": {"value": val, "unit": "s/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(rec), flush=True)
 
@@ -382,46 +406,67 @@ def main():
     sampler = ClockSampler(local)
     sampler.start()
     r._lib.launch_count = 0
-    r.attn_int8.TIMING = []
+    r.timing.PHASES = {}
     ms_step = timed(step_resident, args.steps)
     launches = r._lib.launch_count
-    timing, r.attn_int8.TIMING = r.attn_int8.TIMING, None
+    phases, r.timing.PHASES = r.timing.totals(), None
     clocks = sampler.stop()
     r._lib.check_status()
     step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
     r._lib.check_status()
 
-    # roofline of the dominant kernel (self-attention main kernel), from CUDA events around its launches
-    self_attn = [(a.elapsed_time(b), lq, lk, h) for a, b, lq, lk, h in timing if lk >= 1024]
+    # rooflines from CUDA events around the phases of every fused block inside the timed region (timing.PHASES):
+    # the dominant kernel (self-attention main kernel), the largest GEMM (fc1 + SwiGLU) and the norm + modulation
+    # quantizer; `work` of a phase is its algorithmic operation / byte count
     pk = peaks()
-    roof = None
-    if self_attn:
-        ms_launch = statistics.mean(t for t, *_ in self_attn)
-        _, lq, lk, h = self_attn[0]
-        tflop = 4.0 * lq * lk * 128 * h / 1e12
-        achieved = tflop / (ms_launch / 1e3)
-        peak = 2.0 * pk["bf16_tflops_sustained"]
-        # DRAM bytes of one launch: dram__bytes_read.sum + dram__bytes_write.sum of this kernel captured with ncu on
-        # the one-block workload (Lq = Lk = 36,436, H = 32: 451.3 MB read + 268.2 MB written), scaled to this launch
-        # by its operand + output bytes (which that capture matched within 4 %)
+    peak8 = 2.0 * pk["bf16_tflops_sustained"]
+    peak_note = (f"2 x {pk['source']} sustained cuBLAS bf16 ({pk['bf16_tflops_sustained']} TF/s): 8-bit operands run "
+                 "at twice the bf16 rate; nominal dense INT8/FP8 peak is 4500")
+    total_ms = ms_step * args.steps
+
+    def tensor_roof(name, kernel):
+        ph = phases.get(name)
+        if not ph or ph["ms"] <= 0:
+            return None
+        achieved = ph["work"] / 1e12 / (ph["ms"] / 1e3)
+        return {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": peak8, "unit": "TFLOP/s",
+                "frac": achieved / peak8, "ms_per_launch": ph["ms"] / ph["n"], "launches": ph["n"],
+                "share_of_step": ph["ms"] / total_ms, "peak_note": peak_note, "frac_of_nominal_int8": achieved / 4500.0}
+
+    roof = tensor_roof("attn_self_main", "attn_int8_kernel")
+    if roof:
+        ph = phases["attn_self_main"]
+        lq = lk = s_total
+        heads_local = cfg.heads // world
+        # DRAM bytes of one launch: dram__bytes_read.sum + dram__bytes_write.sum of this kernel from one ncu capture
+        # (ATTN_TRAFFIC below), scaled to this launch by its operand + output bytes; dropped when the kernel source
+        # has changed since that capture
         def alg_bytes(lq_, lk_, h_):
             return h_ * 128 * (lq_ + 2 * lk_) + h_ * 128 * 2 * lq_
-        traffic = 719.53e6 * alg_bytes(lq, lk, h) / alg_bytes(36436, 36436, 32)
-        roof = {"bound": "tensor", "kernel": "attn_int8_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per launch (ncu, scaled)", "ms_per_launch": ms_launch, "launches": len(self_attn),
-                "share_of_step": sum(t for t, *_ in self_attn) / (ms_step * args.steps),
-                "peak_note": f"2 x {pk['source']} sustained cuBLAS bf16 ({pk['bf16_tflops_sustained']} TF/s): "
-                             "8-bit operands run at twice the bf16 rate; nominal dense INT8/FP8 peak is 4500",
-                "frac_of_nominal_int8": achieved / 4500.0}
+        roof["traffic"], roof["traffic_unit"] = attn_traffic(alg_bytes(lq, lk, heads_local))
+    roof_gemm = tensor_roof("gemm_fc1_swiglu", "gemm_w8a8_kernel<int8, SwiGLU epilogue> (fc1)")
+    roof_quant = None
+    ph = phases.get("quant_norm_mod")
+    if ph and ph["ms"] > 0:
+        gbs = ph["work"] / 1e9 / (ph["ms"] / 1e3)
+        roof_quant = {"bound": "hbm", "kernel": "quant_rows_kernel<norm+modulation, int8>", "achieved": gbs,
+                      "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                      "ms_per_launch": ph["ms"] / ph["n"], "launches": ph["n"], "share_of_step": ph["ms"] / total_ms,
+                      "peak_note": f"{pk['source']} copy bandwidth; 3 algorithmic bytes per element + 4 per row",
+                      "frac_of_nominal_8tbs": gbs / 8000.0}
+    phase_ms = {k: round(v["ms"] / args.steps, 3) for k, v in sorted(phases.items())}
+    exchange_ms = sum(v for k, v in phase_ms.items() if k.startswith("exchange_"))
     h2d = sum(host[i].numel() * host[i].element_size() for i in (0, 1, 2, 4))
     d2h = sum(t.numel() * t.element_size() for t in out_host)
     rec = {"metric": "H3 DiT step seconds @768x1344x141f", "value": ms_step / 1e3, "unit": "s/step", "n_gpus": world,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False,
            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-           "config": dict(workload_config(args.workload, world), linear_mode=args.mode, exchange=exchange), "clocks": clocks,
+           "config": workload_config(args.workload, world), "variant": {"linear_mode": args.mode, "exchange": exchange},
+           "clocks": clocks,
            "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-           "gpu_launches": launches, "roofline": roof}
+           "gpu_launches": launches, "roofline": roof, "roofline_gemm": roof_gemm, "roofline_quant": roof_quant,
+           "phases_ms_per_step": phase_ms, "exchange_ms_per_step": round(exchange_ms, 3)}
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             rec["cpu_baseline"] = cpu_baseline_record(args.workload)

@@ -152,6 +152,14 @@ int rh3_attn_quant_v(const void* v, int64_t v_ss, int64_t v_sh, int64_t L, int64
 int rh3_attn_int8(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
                   const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk, int64_t Lk_pad,
                   int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh, cudaStream_t stream);
+/* rh3_attn_int8, and in addition the exact int32 scores Q8 . K8^T of one 128 x 128 tile (query tile q_tile, key
+ * tile kv_tile, of `head`) are written to s_dump [128][128] int32 (device memory): the accumulator the softmax
+ * reads, for bit-exact checks against an integer matrix product. A verification hook in the spirit of the
+ * reference's ext().int8_prepass (attn_int8.cu:2692-2704); the reference has no dump of the scores themselves. */
+int rh3_attn_int8_dump_scores(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                              const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk,
+                              int64_t Lk_pad, int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh,
+                              int64_t head, int64_t q_tile, int64_t kv_tile, int32_t* s_dump, cudaStream_t stream);
 
 /* ---- VAE decoder: causal 3-D convolution as implicit GEMM, GroupNorm + SiLU, upsampling --------------- */
 /* None of these has a counterpart in the reference (its VAE fast path accelerates a transformer decoder,

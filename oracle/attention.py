@@ -12,7 +12,8 @@ kernel is per-token int8 with u8 P), and its rms/rope uses hardware .approx oper
 defines IEEE arithmetic with a fixed summation order, the exponent as the reference's magic-number
 dequantisation t = fma(1.5*2^23 + s, c, (8 - M) - 1.5*2^23*c) (attn_int8.cu:22-27, :2365-2370), and
 P = e4m3(2^t) with M the row maximum rounded up to an integer (so the result does not depend on the
-key-tile order).
+key-tile order). On a fixed subset of the key columns (POLY_MASK) 2^t is a cubic polynomial, restated
+here operation for operation.
 """
 import math
 
@@ -23,6 +24,38 @@ from .quant import ieee_sqrt
 D = 128
 FP8 = torch.float8_e4m3fn
 MAGIC = 12582912.0  # 1.5 * 2^23: the bias that turns int32 accumulator bits into floats
+
+# Which exponentials are a cubic polynomial instead of exp2 (the kernel moves them from the special-function unit
+# to the FMA pipe, the idea of the reference's softmax rebalancing, csrc/attn_cake/attn_cake.cuh:75-95): the 32
+# columns of a chunk are taken four at a time, bit i of the mask selects columns 4i+2 and 4i+3 of group i.
+POLY_MASK = 0x00
+POLY_CLAMP = -60.0
+POLY_C = [float.fromhex(h) for h in ("0x1.fff694p-1", "0x1.62f31ap-1", "0x1.f0ddf6p-3", "0x1.c3f6fp-5")]
+
+
+def _fma32(a, b, c):
+    """fp32 fused multiply-add of fp32 tensors: the product is exact in float64, one rounding of the sum to 53
+    bits and one to 24 (a double rounding changes the result only on ties of measure zero)."""
+    return (a.double() * b.double() + c.double()).float()
+
+
+def exp2_poly(t):
+    """2^t as the kernel's polynomial path computes it, operation for operation, for an fp32 tensor t."""
+    tc = t.clamp_min(POLY_CLAMP)
+    r = tc + torch.tensor(MAGIC, dtype=torch.float32)          # fp32 add: rint(t) in the low mantissa bits
+    n = r - torch.tensor(MAGIC, dtype=torch.float32)           # exact
+    f = tc - n                                                  # exact, in [-1/2, 1/2]
+    c0, c1, c2, c3 = (torch.tensor(c, dtype=torch.float32) for c in POLY_C)
+    q = _fma32(c3.expand_as(f), f, c2.expand_as(f))
+    q = _fma32(q, f, c1.expand_as(f))
+    q = _fma32(q, f, c0.expand_as(f))
+    return torch.ldexp(q, n.to(torch.int32))                    # adds n to the exponent field
+
+
+def poly_columns(lk):
+    """bool [lk]: key columns whose exponential is the polynomial."""
+    c = torch.arange(lk) % 32
+    return (((POLY_MASK >> (c // 4)) & 1) == 1) & ((c % 4) >= 2)
 
 
 def _bf(x):
@@ -124,6 +157,7 @@ def attention_pre(pre, scale=None, heads=None, rows=None):
         kf = pre["k8"][h, :lk].float()
         vf = pre["vt"][h, :, :lk].view(FP8).float().t().contiguous()  # [Lk, 128]
         kc = pre["ks"][h][torch.arange(lk) // 64]                      # per-key scale
+        pcols = poly_columns(lk)
         for r0 in range(0, len(rows), 512):
             rr = rows[r0:r0 + 512]
             s = pre["q8"][h, rr].float() @ kf.t()                      # exact: |s| < 2^24
@@ -134,7 +168,7 @@ def attention_pre(pre, scale=None, heads=None, rows=None):
             m = torch.ceil((sf * c.double() - b.double()).float().amax(1, keepdim=True))
             off = (8.0 - m) - b
             t = (sf * c.double() + off.double()).float()
-            p = torch.exp2(t)
+            p = torch.where(pcols[None, :], exp2_poly(t), torch.exp2(t))
             l = p.sum(1, keepdim=True)
             o = p.to(FP8).float() @ vf
             y = (o / l) * pre["vscale"][h][None] + pre["vmean"][h][None]

@@ -20,11 +20,18 @@ def _qlinear(x, weight):
     return ol.int_mm(xq, wq), xs, ws
 
 
-def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None, mode="int8_rowwise"):
+def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None, mode="int8_rowwise", adaln=None,
+                replay=None):
+    """`adaln`: the six fp32 modulation tables, when the caller wants the block checked on given tables (the AdaLN
+    projection is a plain bf16 matrix product of the host framework whose summation order differs between devices;
+    it is an input of the quantized path, not part of it).
+    `replay`: {"x_attn": ..., "x_cross": ...}: residual streams to start the cross-attention and the MLP stage from,
+    instead of this function's own (a checker passes what the device produced, so that every stage is compared on
+    identical inputs and a last-bit difference of one stage is not amplified through the next quantizer)."""
     s, d = x.shape
     a = block.attn
     hd = a.heads * a.head_dim
-    sh1, sc1, g1, sh2, sc2, g2 = block.adaln_proj(t_emb)
+    sh1, sc1, g1, sh2, sc2, g2 = block.adaln_proj(t_emb) if adaln is None else adaln
     idx = torch.empty(s, dtype=torch.int32)
     for lo, hi, row in mod_segments:
         idx[lo:hi] = int(row)
@@ -62,12 +69,15 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None,
     wq, ws = q_weight(a.out_proj)
     x = gated(ol.int_mm(oq8, wq), os_, ws, g1, x)
     rec("x_attn", x)
+    if replay is not None and "x_attn" in replay:
+        x = replay["x_attn"].clone()
 
     if hasattr(block, "cross"):
         c = block.cross
         zeros = torch.zeros(1, d)
         xq, xs = norm_mod_q(x, block.norm_c.weight.detach(), block.norm_c.eps,
                                            torch.zeros(s, dtype=torch.int32), zeros, zeros)
+        rec("cross_in_q", xq), rec("cross_in_s", xs)
         wq, ws = q_weight(c.q_proj)
         qc = ol.dequant(ol.int_mm(xq, wq), xs, ws).reshape(s, c.heads, c.head_dim)
         cq8, cs = ol.quantize_rows(ctx, mode)
@@ -76,19 +86,26 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None,
         kc, vc = (t.reshape(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
         qc = oa.rmsnorm_rope(qc, c.q_norm.weight.detach(), c.q_norm.eps, None)
         kc = oa.rmsnorm_rope(kc, c.k_norm.weight.detach(), c.k_norm.eps, None)
+        rec("cross_q", qc), rec("cross_k", kc), rec("cross_v", vc)
         oc = oa.attention(qc, kc, vc)
         rec("cross_out", oc)
         oq8, os_ = ol.quantize_rows(oc.reshape(s, hd), mode)
         wq, ws = q_weight(c.out_proj)
         x = ol.gated_residual(ol.int_mm(oq8, wq), os_, ws, torch.ones(d, dtype=torch.bfloat16), x)
         rec("x_cross", x)
+        if replay is not None and "x_cross" in replay:
+            x = replay["x_cross"].clone()
 
     xq, xs = norm_mod_q(x, block.norm2.weight.detach(), block.norm2.eps, idx, sh2, sc2)
+    rec("mlp_in_q", xq), rec("mlp_in_s", xs)
     wq, ws = q_weight(block.mlp.fc1)
     perm = ol.swiglu_perm(wq.shape[0])
     h = ol.swiglu_epilogue(ol.int_mm(xq, wq[perm]), xs, ws[:, perm])
     rec("mlp_h", h)
+    if replay is not None and "mlp_h" in replay:
+        h = replay["mlp_h"].clone()
     hq, hs = ol.quantize_rows(h, mode)
+    rec("fc2_in_q", hq), rec("fc2_in_s", hs)
     wq, ws = q_weight(block.mlp.fc2)
     x = gated(ol.int_mm(hq, wq), hs, ws, g2, x)
     rec("x_out", x)

@@ -41,22 +41,33 @@ def upsample(x):
     return y.contiguous()
 
 
-def decode(params, latent, widths=(512, 256, 128), blocks=2):
-    """latent [N,C,T,H,W] bf16 -> RGB [N,3,4T-3,32H,32W] bf16 (for three stages)."""
+def decode(params, latent, widths=(512, 256, 128), blocks=2, trace=None):
+    """latent [N,C,T,H,W] bf16 -> RGB [N,3,4T-3,32H,32W] bf16 (for three stages). `trace` (a list) receives one
+    record (op, layer name, inputs, output) per layer, so that a caller can replay every layer on the oracle's own
+    input."""
     p = params
+
+    def rec(op, name, ins, y):
+        if trace is not None:
+            trace.append((op, name, ins, y))
+        return y
+
+    def conv(name, x, residual=None):
+        return rec("conv", name, (x, residual), conv3d_causal(x, p[name + ".w"], p[name + ".b"], residual))
+
+    def norm(name, x):
+        return rec("gn", name, (x,), gn_silu(x, p[name + ".g"], p[name + ".be"]))
+
     n, c, t, h, w = latent.shape
     x = torch.zeros(n, t, h, w, 64, dtype=torch.bfloat16)
     x[..., :c] = latent.permute(0, 2, 3, 4, 1)
-    x = conv3d_causal(x, p["conv_in.w"], p["conv_in.b"])
+    x = conv("conv_in", x)
     for si in range(len(widths)):
         for bi in range(blocks):
-            hdn = gn_silu(x, p[f"s{si}.b{bi}.n1.g"], p[f"s{si}.b{bi}.n1.be"])
-            hdn = conv3d_causal(hdn, p[f"s{si}.b{bi}.c1.w"], p[f"s{si}.b{bi}.c1.b"])
-            hdn = gn_silu(hdn, p[f"s{si}.b{bi}.n2.g"], p[f"s{si}.b{bi}.n2.be"])
-            x = conv3d_causal(hdn, p[f"s{si}.b{bi}.c2.w"], p[f"s{si}.b{bi}.c2.b"], residual=x)
+            hdn = conv(f"s{si}.b{bi}.c1", norm(f"s{si}.b{bi}.n1", x))
+            x = conv(f"s{si}.b{bi}.c2", norm(f"s{si}.b{bi}.n2", hdn), residual=x)
         if si + 1 < len(widths):
-            x = conv3d_causal(upsample(x), p[f"s{si}.up.w"], p[f"s{si}.up.b"])
-    x = gn_silu(x, p["head.n.g"], p["head.n.be"])
-    y = conv3d_causal(x, p["head.c.w"], p["head.c.b"])
+            x = conv(f"s{si}.up", rec("up", f"s{si}", (x,), upsample(x)))
+    y = conv("head.c", norm("head.n", x))
     n, t2, h2, w2, _ = y.shape
     return y.view(n, t2, h2, w2, 3, 8, 8).permute(0, 4, 1, 2, 5, 3, 6).reshape(n, 3, t2, h2 * 8, w2 * 8)

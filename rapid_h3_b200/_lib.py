@@ -48,6 +48,8 @@ SIGNATURES = {
     "rh3_attn_quant_qk": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
     "rh3_attn_quant_v": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
     "rh3_attn_int8": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _I64, _I64, _P],
+    "rh3_attn_int8_dump_scores": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _I64, _I64, _I64, _I64,
+                                  _I64, _P, _P],
     "rh3_depth_to_space8": [_P, _P, _I64, _I64, _I64, _I64, _P],
     "rh3_conv3d_causal": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P],
     "rh3_conv3d_gn_part_rows": [_I64, _I64, _I64, _I64],

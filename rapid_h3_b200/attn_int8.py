@@ -14,12 +14,9 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
+from .timing import phase as _phase
 
 D = 128
-
-# When set to a list, attention_pre() appends (start_event, stop_event, Lq, Lk, H) around every launch of
-# the main kernel on the current stream (the reference's RAPIDH3_TIMING idea, __init__.py:258-264).
-TIMING = None
 
 
 def _pad128(n):
@@ -72,8 +69,13 @@ def rms_rope(x, weight, eps, tab=None, out=None):
     return out
 
 
-def int8_prepass(q, k, v):
+def int8_prepass(q, k, v, _tag="call"):
     """Quantize the operands of one attention call: K/V statistics, block-64 int8 Q and K, e4m3 V^T."""
+    with _phase(f"attn_{_tag}_prepass", (q.shape[0] + 2 * k.shape[0]) * q.shape[1] * D * 3):
+        return _int8_prepass(q, k, v)
+
+
+def _int8_prepass(q, k, v):
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_qkv(t, n)
     lq, h, _ = q.shape
@@ -103,7 +105,7 @@ def int8_prepass(q, k, v):
     return Prepass(q8, qs, k8, ks, vt, vscale, vmean, kmean, lq, lk)
 
 
-def attention_pre(pre, scale=None, out=None, scatter=None):
+def attention_pre(pre, scale=None, out=None, scatter=None, _tag="call"):
     """Main kernel on pre-quantized operands -> out [Lq, H, 128] bf16 (strided `out` allowed).
     `scatter` = (device pointers, row starts [n+1], row stride, head stride) sends query rows
     [start[r], start[r+1]) to buffer r instead (rh3_attn_int8_scatter); nothing is returned then."""
@@ -116,32 +118,29 @@ def attention_pre(pre, scale=None, out=None, scatter=None):
         _check_qkv(out, "out")
         if out.shape[0] != pre.lq or out.shape[1] != h:
             raise RuntimeError("out must be [Lq, H, 128]")
-    if TIMING is not None:
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-    if scatter is None:
-        _lib.call("rh3_attn_int8", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
-                  pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
-                  pre.k8.shape[1], h, float(scale), out.data_ptr(), out.stride(0), out.stride(1), _lib.stream())
-    else:
-        ptrs, starts, o_ss, o_sh = scatter
-        n = len(ptrs)
-        c_ptrs = (ctypes.c_void_p * n)(*ptrs)
-        c_starts = (ctypes.c_int64 * (n + 1))(*starts)
-        _lib.call("rh3_attn_int8_scatter", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
-                  pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
-                  pre.k8.shape[1], h, float(scale), c_ptrs, c_starts, n, o_ss, o_sh, _lib.stream())
-    if TIMING is not None:
-        ev1.record()
-        TIMING.append((ev0, ev1, pre.lq, pre.lk, h))
+    with _phase(f"attn_{_tag}_main", 4 * pre.lq * pre.lk * D * h):
+        if scatter is None:
+            _lib.call("rh3_attn_int8", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
+                      pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq, pre.q8.shape[1], pre.lk,
+                      pre.k8.shape[1], h, float(scale), out.data_ptr(), out.stride(0), out.stride(1), _lib.stream())
+        else:
+            ptrs, starts, o_ss, o_sh = scatter
+            n = len(ptrs)
+            c_ptrs = (ctypes.c_void_p * n)(*ptrs)
+            c_starts = (ctypes.c_int64 * (n + 1))(*starts)
+            _lib.call("rh3_attn_int8_scatter", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(),
+                      pre.ks.data_ptr(), pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), pre.lq,
+                      pre.q8.shape[1], pre.lk, pre.k8.shape[1], h, float(scale), c_ptrs, c_starts, n, o_ss, o_sh,
+                      _lib.stream())
     return out
 
 
-def attention(q, k, v, scale=None, config=0, smooth_k=True, smooth_v=True, rotate=False, out=None):
-    """q [Lq, H, 128], k, v [Lk, H, 128] bf16 (strided views allowed) -> [Lq, H, 128] bf16."""
+def attention(q, k, v, scale=None, config=0, smooth_k=True, smooth_v=True, rotate=False, out=None, _tag="call"):
+    """q [Lq, H, 128], k, v [Lk, H, 128] bf16 (strided views allowed) -> [Lq, H, 128] bf16.
+    `_tag` only names the timing phases of this call (timing.PHASES)."""
     if rotate:
         raise NotImplementedError("the Hadamard-rotated per-token variant is not implemented")
-    return attention_pre(int8_prepass(q, k, v), scale, out)
+    return attention_pre(int8_prepass(q, k, v, _tag), scale, out, _tag=_tag)
 
 
 def attention_bhsd(q, k, v, scale=None, config=0, out=None):

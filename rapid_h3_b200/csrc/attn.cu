@@ -60,6 +60,9 @@ struct AttnParams {
   int n_dst;
   long long dst_start[9];
   __nv_bfloat16* dst_ptr[8];
+  // verification hook (DUMP instantiation only): the int32 scores of one 128 x 128 tile go to s_dump [128][128]
+  int32_t* s_dump;
+  int dump_q_tile, dump_kv_tile, dump_head;
 };
 
 struct __align__(8) AttnSmemTail {
@@ -134,6 +137,41 @@ __device__ __forceinline__ float chunk_max(const uint32_t* r) {
   return fmaxf(m, __uint_as_float(r[31]));
 }
 
+// Which exponentials leave the special-function unit. The 32 columns of a chunk are taken four at a time
+// (group i = 0..7: columns 4i..4i+3); bit i of the mask sends the SECOND pair of group i (columns 4i+2, 4i+3)
+// through the polynomial below on the FMA pipe instead of ex2.approx. 0x77 = six of sixteen pairs = 3/8 of all
+// exponentials. The CPU oracle applies the same mask, so both sides evaluate the same function per column.
+#ifndef RH3_ATTN_POLY_MASK
+#define RH3_ATTN_POLY_MASK 0x00
+#endif
+constexpr uint32_t kPolyMask = RH3_ATTN_POLY_MASK;
+
+// 2^t for two values at once without the special-function unit: t is clamped at -60 (2^-60 is nothing against
+// a row sum >= 128, and the exponent arithmetic below needs a bounded t), split as t = n + f with n = rint(t)
+// taken from the low mantissa bits of t + 1.5*2^23 and f = t - n in [-1/2, 1/2] (exact), 2^f evaluated as a
+// cubic in Horner form with fused multiply-adds (relative error 7.5e-5, far inside P's 3-bit mantissa; the
+// unrounded value also enters the row sum, where the error alternates in sign over f), and n added to the
+// exponent field. Every operation is a correctly rounded fp32 operation, so the result is reproducible bit for
+// bit on a CPU.
+constexpr float kPolyClamp = -60.f;
+constexpr float kPolyC0 = 0x1.fff694p-1f, kPolyC1 = 0x1.62f31ap-1f, kPolyC2 = 0x1.f0ddf6p-3f, kPolyC3 = 0x1.c3f6fp-5f;
+__device__ __forceinline__ void exp2_poly2(uint64_t t2, float& pa, float& pb) {
+  float ta, tb;
+  unpack2(t2, ta, tb);
+  const uint64_t tc = pack2(fmaxf(ta, kPolyClamp), fmaxf(tb, kPolyClamp));
+  const uint64_t r = add2(tc, pack2(kMagic, kMagic));                        // low mantissa bits = n
+  const uint64_t n = add2(r, pack2(-kMagic, -kMagic));                       // n as a float (exact)
+  const uint64_t f = fma2(n, pack2(-1.f, -1.f), tc);                         // t - n (exact)
+  uint64_t q = fma2(pack2(kPolyC3, kPolyC3), f, pack2(kPolyC2, kPolyC2));
+  q = fma2(q, f, pack2(kPolyC1, kPolyC1));
+  q = fma2(q, f, pack2(kPolyC0, kPolyC0));
+  float ra, rb, qa, qb;
+  unpack2(r, ra, rb);
+  unpack2(q, qa, qb);
+  pa = __uint_as_float(__float_as_uint(qa) + (__float_as_uint(ra) << 23));   // the magic's own bits shift out
+  pb = __uint_as_float(__float_as_uint(qb) + (__float_as_uint(rb) << 23));
+}
+
 // One 32-column chunk: p = 2^(bits * cc + off) in packed f32x2, e4m3 codes written to 16-byte chunks
 // 2k and 2k+1 of the row of P in shared memory (XOR-swizzled), unrounded p added to the sum.
 __device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, float cc, float off, uint8_t* p_row, int sw,
@@ -145,8 +183,14 @@ __device__ __forceinline__ void exp_chunk(const uint32_t* r, int k, float cc, fl
   for (int i = 0; i < 8; ++i) {
     float pa, pb, pc, pd;
     unpack2(fma2(pack2(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1])), cc2, off2), pa, pb);
-    unpack2(fma2(pack2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), cc2, off2), pc, pd);
-    pa = ex2_approx(pa); pb = ex2_approx(pb); pc = ex2_approx(pc); pd = ex2_approx(pd);
+    const uint64_t t_cd = fma2(pack2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), cc2, off2);
+    pa = ex2_approx(pa); pb = ex2_approx(pb);
+    if ((kPolyMask >> i) & 1u) {
+      exp2_poly2(t_cd, pc, pd);
+    } else {
+      unpack2(t_cd, pc, pd);
+      pc = ex2_approx(pc); pd = ex2_approx(pd);
+    }
     if (i & 1) ls1 = add2(ls1, add2(pack2(pa, pb), pack2(pc, pd)));
     else ls0 = add2(ls0, add2(pack2(pa, pb), pack2(pc, pd)));
     w[i] = pack_e4m3x4(pa, pb, pc, pd);
@@ -165,6 +209,7 @@ static_assert(128 * REGS_SERVICE + 256 * REGS_SOFTMAX == ATTN_THREADS * REGS_COM
 __device__ __forceinline__ void reg_release_service() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
 __device__ __forceinline__ void reg_take_softmax() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
 
+template <bool DUMP>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
                  const __grid_constant__ CUtensorMap tma_v, const AttnParams p) {
@@ -326,6 +371,19 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       tmem_ld_wait_regs(r1);
       tmem_ld_wait_regs(r2);
       tmem_ld_wait_regs(r3);
+      if constexpr (DUMP) {
+        // raw bits are the float 1.5*2^23 + s, i.e. the integer 0x4B400000 + s for |s| < 2^22
+        if (h == p.dump_head && q_pair * QG + g == p.dump_q_tile && j == p.dump_kv_tile) {
+          int32_t* d = p.s_dump + row * BKV;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            d[i] = static_cast<int32_t>(r0[i] - kMagicBits);
+            d[32 + i] = static_cast<int32_t>(r1[i] - kMagicBits);
+            d[64 + i] = static_cast<int32_t>(r2[i] - kMagicBits);
+            d[96 + i] = static_cast<int32_t>(r3[i] - kMagicBits);
+          }
+        }
+      }
       // S is in registers: bias it for the next Q.K^T and hand it back
       tmem_st32_splat(t_row, kMagicBits);
       tmem_st32_splat(t_row + 32, kMagicBits);
@@ -437,7 +495,8 @@ namespace {
 int attn_launch(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt, const float* vscale,
                 const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk, int64_t Lk_pad, int64_t H,
                 float softmax_scale, void* out, void* const* dst, const int64_t* dst_start, int n_dst, int64_t o_ss,
-                int64_t o_sh, cudaStream_t stream) {
+                int64_t o_sh, cudaStream_t stream, int32_t* s_dump = nullptr, int64_t dump_q_tile = 0,
+                int64_t dump_kv_tile = 0, int64_t dump_head = 0) {
   RH3_CHECK_ARG(Lq > 0 && Lk > 0 && H > 0 && H < 65536, "attn_int8: bad shape Lq=%lld Lk=%lld H=%lld", (long long)Lq,
                 (long long)Lk, (long long)H);
   RH3_CHECK_ARG(Lq_pad >= Lq && Lk_pad >= Lk && Lq_pad % 256 == 0 && Lk_pad % 128 == 0,
@@ -479,7 +538,15 @@ int attn_launch(const void* q8, const float* qs, const void* k8, const float* ks
   p.sl2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
   p.status = device_status_word();
   const dim3 grid(static_cast<unsigned>((Lq + QG * BQ - 1) / (QG * BQ)), static_cast<unsigned>(H));
-  auto kern = attn_int8_kernel;
+  auto kern = s_dump ? attn_int8_kernel<true> : attn_int8_kernel<false>;
+  if (s_dump) {
+    RH3_CHECK_ARG(dump_head >= 0 && dump_head < H && dump_q_tile >= 0 && dump_q_tile * BQ < Lq_pad && dump_kv_tile >= 0 &&
+                      dump_kv_tile * BKV < Lk_pad,
+                  "attn_int8_dump_scores: tile (%lld, %lld) of head %lld does not exist", (long long)dump_q_tile,
+                  (long long)dump_kv_tile, (long long)dump_head);
+    p.s_dump = s_dump;
+    p.dump_q_tile = (int)dump_q_tile; p.dump_kv_tile = (int)dump_kv_tile; p.dump_head = (int)dump_head;
+  }
   if (int e = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_SMEM_BYTES),
                          "attn smem attribute"))
     return e;
@@ -494,6 +561,19 @@ extern "C" int rh3_attn_int8(const void* q8, const float* qs, const void* k8, co
                              cudaStream_t stream) {
   return attn_launch(q8, qs, k8, ks, vt, vscale, vmean, Lq, Lq_pad, Lk, Lk_pad, H, softmax_scale, out, nullptr, nullptr,
                      0, o_ss, o_sh, stream);
+}
+
+// Verification hook: the same launch as rh3_attn_int8, and in addition the exact int32 scores Q8 . K8^T of the 128 x 128
+// tile (query tile q_tile, key tile kv_tile) of `head` are written to s_dump [128][128] (rows and keys beyond Lq / Lk
+// are the products with the zero padding).
+extern "C" int rh3_attn_int8_dump_scores(const void* q8, const float* qs, const void* k8, const float* ks, const void* vt,
+                                         const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk,
+                                         int64_t Lk_pad, int64_t H, float softmax_scale, void* out, int64_t o_ss,
+                                         int64_t o_sh, int64_t head, int64_t q_tile, int64_t kv_tile, int32_t* s_dump,
+                                         cudaStream_t stream) {
+  RH3_CHECK_ARG(s_dump != nullptr, "attn_int8_dump_scores: null dump buffer");
+  return attn_launch(q8, qs, k8, ks, vt, vscale, vmean, Lq, Lq_pad, Lk, Lk_pad, H, softmax_scale, out, nullptr, nullptr,
+                     0, o_ss, o_sh, stream, s_dump, q_tile, kv_tile, head);
 }
 
 // The same kernel with its output rows scattered over up to 8 buffers: rows [dst_start[r], dst_start[r+1]) go to

@@ -305,13 +305,16 @@ __global__ void __launch_bounds__(256) gn_reduce_kernel(const float* __restrict_
 
 // y = silu((x - mean[g]) * rstd[g] * gamma[c] + beta[c]). A thread keeps one group of 8 channels for the whole
 // launch (the block's 256 threads cover 256 / (C/8) sites per iteration), so the per-channel scale
-// a = rstd * gamma and offset b = beta - mean * a are computed once and the loop body is one FMA and one
-// tanh per value: silu(t) = t * (0.5 + 0.5 * tanh(t / 2)). Launched as (blocks, N); C/8 <= 256 (threads beyond
-// the last whole site of the block idle).
-__device__ __forceinline__ float tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
+// a = rstd * gamma and offset b = beta - mean * a are computed once and the loop body is one FMA and the SiLU
+// per value: silu(t) = t / (1 + 2^(-t * log2 e)) with the hardware exponential and reciprocal (both good to
+// about 1e-7 relative, far inside the bf16 rounding of the result; the hyperbolic-tangent form with its 2^-11
+// error flipped too many of those roundings). Launched as (blocks, N); C/8 <= 256 (threads beyond the last
+// whole site of the block idle).
+__device__ __forceinline__ float silu_fast(float t) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return t * r;
 }
 __global__ void __launch_bounds__(256) gn_silu_kernel(const __nv_bfloat16* __restrict__ x,
                                                       const float* __restrict__ mean_rstd,  // [N][32][2]
@@ -351,8 +354,7 @@ __global__ void __launch_bounds__(256) gn_silu_kernel(const __nv_bfloat16* __res
     for (int j = 0; j < 4; ++j) {
       const float t0 = fmaf(bf16_lo(xw[j]), a[2 * j], b[2 * j]);
       const float t1 = fmaf(bf16_hi(xw[j]), a[2 * j + 1], b[2 * j + 1]);
-      const float h0 = 0.5f * t0, h1 = 0.5f * t1;
-      o[j] = pack_bf16x2(fmaf(h0, tanh_approx(h0), h0), fmaf(h1, tanh_approx(h1), h1));
+      o[j] = pack_bf16x2(silu_fast(t0), silu_fast(t1));
     }
     *reinterpret_cast<uint4*>(ys + site * C + c0) = make_uint4(o[0], o[1], o[2], o[3]);
   }

@@ -13,6 +13,7 @@ import re
 import torch
 
 from . import attn_int8, kernels
+from .timing import phase as _phase
 from . import gemm as cf
 from . import quantizers as tq
 
@@ -177,13 +178,28 @@ class FusedBlock:
         return self._const[key]
 
     @staticmethod
-    def _gemm_gated(xq, xs, q, x, gate_tab, segments):
-        """x += gate * (xq @ W^T), one GEMM per modality segment, each with its own gate row."""
+    def _gate_rows(gate_tab):
+        """The gate table [R, d] as bf16 rows, converted once per forward (one row per modality)."""
+        return gate_tab.to(torch.bfloat16).contiguous()
+
+    @staticmethod
+    def _gemm_gated(xq, xs, q, x, gates, segments):
+        """x += gate * (xq @ W^T), one GEMM per modality segment, each with its own gate row of `gates` [R, d] bf16;
+        a segment whose row is a per-token tensor is split into runs of equal rows."""
         qw = q.qweight_for()
         for a, b, row in segments:
-            if b > a:
-                g = gate_tab[int(row)].to(torch.bfloat16).contiguous()
-                cf.int8_gemm_gated_residual(xq[a:b], xs[a:b], qw.q, qw.scale, g, x[a:b])
+            if b <= a:
+                continue
+            if torch.is_tensor(row) and row.numel() > 1:
+                rows = row.reshape(-1).tolist()
+                start = 0
+                for i in range(1, len(rows) + 1):
+                    if i == len(rows) or rows[i] != rows[start]:
+                        cf.int8_gemm_gated_residual(xq[a + start:a + i], xs[a + start:a + i], qw.q, qw.scale,
+                                                    gates[int(rows[start])], x[a + start:a + i])
+                        start = i
+            else:
+                cf.int8_gemm_gated_residual(xq[a:b], xs[a:b], qw.q, qw.scale, gates[int(row)], x[a:b])
         return x
 
     # -- forward -----------------------------------------------------------------------------
@@ -194,45 +210,58 @@ class FusedBlock:
         s, d = x.shape
         a = blk.attn
         hd = a.heads * a.head_dim
-        shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = blk.adaln_proj(t_emb)
-        idx = _row_index(mod_segments, s, x.device)
-        tab = rope_freqs.reshape(s, 48, 2, 2)
+        f = blk.mlp.fc2.weight.shape[1] if blk.mlp.fc2.weight.numel() else self.fc2_q.qweight_for().q.shape[1]
+        with _phase("adaln"):
+            shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = blk.adaln_proj(t_emb)
+            idx = _row_index(mod_segments, s, x.device)
+            tab = rope_freqs.reshape(s, 48, 2, 2).contiguous()
+            gates_msa, gates_mlp = self._gate_rows(gate_msa), self._gate_rows(gate_mlp)
         rot = self.rotate
+        qbytes = lambda k: s * k * 3 + 4 * s  # noqa: E731  (row quantizer: 2 bytes in, 1 out per element, a scale per row)
 
         def rec(name, value):
             if trace is not None:
                 trace[name] = value.clone() if torch.is_tensor(value) else value
 
         # ---- self-attention ----
-        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm1), self._eps(blk.norm1), idx, shift_msa, scale_msa, rotate=rot)
+        with _phase("quant_norm_mod", qbytes(d)):
+            xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm1), self._eps(blk.norm1), idx, shift_msa, scale_msa, rotate=rot)
         rec("attn_in_q", xq), rec("attn_in_s", xs)
         qw = self.qkv_q.qweight_for()
-        qkv = cf.int8_gemm(xq, xs, qw.q, qw.scale)
+        with _phase("gemm_qkv", 2 * s * 3 * hd * d):
+            qkv = cf.int8_gemm(xq, xs, qw.q, qw.scale)
         rec("qkv", qkv)
         q, k, v = (t.view(s, a.heads, a.head_dim) for t in qkv.split(hd, dim=-1))
         if sp is not None and sp.fused:
             # both exchanges done by the kernels: rope + scatter to the head owners, attention epilogue scatters back
             if a.q_norm.eps != a.k_norm.eps:
                 raise NotImplementedError("fused exchange: q and k norms must share eps")
-            qg, kg, vg = sp.rope_scatter(qkv, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps,
-                                         tab.contiguous())
+            with _phase("exchange_rope_scatter", s * hd * 2 * 3 * 2):
+                qg, kg, vg = sp.rope_scatter(qkv, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps, tab)
             o = sp.attention_scatter(qg, kg, vg)                    # [P, S_local, (H/P)*128] group-major
-            oq, os_ = tq.quant_groups_i8(o, rotate=rot)
+            with _phase("quant_attn_out", qbytes(hd)):
+                oq, os_ = tq.quant_groups_i8(o, rotate=rot)
         else:
-            attn_int8.rms_rope(q, self._norm_w(a.q_norm), a.q_norm.eps, tab, out=q)
-            attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
+            with _phase("rms_rope", s * hd * 2 * 2 * 2):
+                attn_int8.rms_rope(q, self._norm_w(a.q_norm), a.q_norm.eps, tab, out=q)
+                attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
             rec("qkv_rr", qkv)
             if sp is None:
-                o = attn_int8.attention(q, k, v)                       # [S, H, 128] token-major
+                o = attn_int8.attention(q, k, v, _tag="self")          # [S, H, 128] token-major
                 rec("attn_out", o)
-                oq, os_ = tq.rot_quant_rows_i8(o.view(s, hd), rotate=rot)
+                with _phase("quant_attn_out", qbytes(hd)):
+                    oq, os_ = tq.rot_quant_rows_i8(o.view(s, hd), rotate=rot)
             else:
-                qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
-                og = attn_int8.attention(qg, kg, vg)
-                o = sp.heads_to_tokens(og)                              # [P, S_local, (H/P)*128] group-major
-                oq, os_ = tq.quant_groups_i8(o, rotate=rot)
+                with _phase("exchange_all_to_all"):
+                    qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
+                og = attn_int8.attention(qg, kg, vg, _tag="self")
+                with _phase("exchange_all_to_all"):
+                    o = sp.heads_to_tokens(og)                          # [P, S_local, (H/P)*128] group-major
+                with _phase("quant_attn_out", qbytes(hd)):
+                    oq, os_ = tq.quant_groups_i8(o, rotate=rot)
         del qkv, q, k, v
-        x = self._gemm_gated(oq, os_, self.out_q, x, gate_msa, mod_segments)
+        with _phase("gemm_out_proj", 2 * s * d * hd):
+            x = self._gemm_gated(oq, os_, self.out_q, x, gates_msa, mod_segments)
         rec("x_attn", x)
 
         # ---- cross-attention to text ----
@@ -240,29 +269,44 @@ class FusedBlock:
             c = blk.cross
             zeros, ones = self._zeros_tab(d, x.device)
             idx0 = self._const.setdefault(("idx0", s, str(x.device)), torch.zeros(s, dtype=torch.int32, device=x.device))
-            xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm_c), self._eps(blk.norm_c), idx0, zeros, zeros, rotate=rot)
+            with _phase("quant_norm_mod", qbytes(d)):
+                xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm_c), self._eps(blk.norm_c), idx0, zeros, zeros, rotate=rot)
+            rec("cross_in_q", xq), rec("cross_in_s", xs)
             qw = self.cq_q.qweight_for()
-            qc = cf.int8_gemm(xq, xs, qw.q, qw.scale).view(s, c.heads, c.head_dim)
-            cq8, cs = tq.rot_quant_rows_i8(ctx, rotate=rot)
-            qw = self.ckv_q.qweight_for()
-            kv = cf.int8_gemm(cq8, cs, qw.q, qw.scale)
-            kc, vc = (t.view(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
-            attn_int8.rms_rope(qc, self._norm_w(c.q_norm), c.q_norm.eps, None, out=qc)
-            attn_int8.rms_rope(kc, self._norm_w(c.k_norm), c.k_norm.eps, None, out=kc)
-            oc = attn_int8.attention(qc, kc, vc)
+            with _phase("gemm_cross", 2 * s * hd * d):
+                qc = cf.int8_gemm(xq, xs, qw.q, qw.scale).view(s, c.heads, c.head_dim)
+            with _phase("cross_text_kv"):
+                cq8, cs = tq.rot_quant_rows_i8(ctx, rotate=rot)
+                qw = self.ckv_q.qweight_for()
+                kv = cf.int8_gemm(cq8, cs, qw.q, qw.scale)
+                kc, vc = (t.view(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
+                attn_int8.rms_rope(kc, self._norm_w(c.k_norm), c.k_norm.eps, None, out=kc)
+            with _phase("rms_rope", s * hd * 2 * 2):
+                attn_int8.rms_rope(qc, self._norm_w(c.q_norm), c.q_norm.eps, None, out=qc)
+            rec("cross_q", qc), rec("cross_k", kc), rec("cross_v", vc)
+            oc = attn_int8.attention(qc, kc, vc, _tag="cross")
             rec("cross_out", oc)
-            oq, os_ = tq.rot_quant_rows_i8(oc.view(s, hd), rotate=rot)
+            with _phase("quant_attn_out", qbytes(hd)):
+                oq, os_ = tq.rot_quant_rows_i8(oc.view(s, hd), rotate=rot)
             qw = self.co_q.qweight_for()
-            cf.int8_gemm_gated_residual(oq, os_, qw.q, qw.scale, ones, x)
+            with _phase("gemm_cross", 2 * s * d * hd):
+                cf.int8_gemm_gated_residual(oq, os_, qw.q, qw.scale, ones, x)
             rec("x_cross", x)
 
         # ---- MLP ----
-        xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm2), self._eps(blk.norm2), idx, shift_mlp, scale_mlp, rotate=rot)
-        h = cf.int8_gemm_swiglu(xq, xs, *self._fc1_swiglu_weight())
+        with _phase("quant_norm_mod", qbytes(d)):
+            xq, xs = tq.norm_mod_rot_quant_rows_i8(x, self._norm_w(blk.norm2), self._eps(blk.norm2), idx, shift_mlp, scale_mlp, rotate=rot)
+        rec("mlp_in_q", xq), rec("mlp_in_s", xs)
+        w1q, w1s = self._fc1_swiglu_weight()
+        with _phase("gemm_fc1_swiglu", 2 * s * 2 * f * d):
+            h = cf.int8_gemm_swiglu(xq, xs, w1q, w1s)
         rec("mlp_h", h)
-        hq, hs = tq.rot_quant_rows_i8(h, rotate=rot)
+        with _phase("quant_fc2_in", qbytes(f)):
+            hq, hs = tq.rot_quant_rows_i8(h, rotate=rot)
+        rec("fc2_in_q", hq), rec("fc2_in_s", hs)
         del h
-        out = self._gemm_gated(hq, hs, self.fc2_q, x, gate_mlp, mod_segments)
+        with _phase("gemm_fc2", 2 * s * d * f):
+            out = self._gemm_gated(hq, hs, self.fc2_q, x, gates_mlp, mod_segments)
         rec("x_out", out)
         return out
 

@@ -12,6 +12,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
+from .timing import phase as _phase
 
 
 def shard_bounds(total, world, align=64):
@@ -126,7 +127,8 @@ class Ulysses:
     def _barrier(self):
         """All ranks' kernels enqueued so far have finished (and their stores have landed) before anything enqueued
         after it starts: a one-element all-reduce on the compute stream."""
-        dist.all_reduce(self._flag, group=self.group)
+        with _phase("exchange_barrier"):
+            dist.all_reduce(self._flag, group=self.group)
 
     def rope_scatter(self, qkv, q_weight, k_weight, eps, tab):
         """qkv [S_local, 3*H*D] (raw q | k | v of this rank's tokens) -> q, k, v [S_total, H/P, D] of this rank's
@@ -148,11 +150,11 @@ class Ulysses:
         """Attention on this rank's heads; the epilogue stores every token's output row into the rank that owns the
         token. Returns [P, S_local, (H/P)*D] as heads_to_tokens does."""
         from . import attn_int8
-        pre = attn_int8.int8_prepass(q, k, v)
+        pre = attn_int8.int8_prepass(q, k, v, "self")
         w = self._w
         offsets, starts = scatter_plan(self.bounds, self.rank, w)
         ptrs = [self._o_buf.ptrs[r] + offsets[r] for r in range(self.world)]
-        attn_int8.attention_pre(pre, scale, scatter=(ptrs, starts, w, self._head_dim))
+        attn_int8.attention_pre(pre, scale, scatter=(ptrs, starts, w, self._head_dim), _tag="self")
         self._barrier()
         s_loc = self.counts[self.rank]
         return self._o_buf.local[: self.world * s_loc * w * 2].view(torch.bfloat16).view(self.world, s_loc, w)

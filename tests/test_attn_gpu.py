@@ -94,7 +94,36 @@ def test_attention_matches_oracle(ops, shape):
     assert rel_l2(out.cpu(), ref) <= TOL
     # and the quantization error against fp32 attention stays in the range of this numerics class
     full = oa.attention_fp32(q, k, v)
-    assert rel_l2(out.cpu(), full) < 0.08
+    assert rel_l2(out.cpu(), full) < 0.05   # the oracle itself sits near 0.04 on these inputs (e4m3 P dominates)
+
+
+@pytest.mark.parametrize("tile", [(0, 0, 0), (2, 9, 1), (2, 7, 10)])
+def test_int32_scores_of_a_tile_are_exact(ops, tile):
+    """The int32 accumulator the softmax reads (Q8 . K8^T of one 128 x 128 tile, kept pre-biased by 1.5 * 2^23 in
+    TMEM) against the integer matrix product of the same codes: bit for bit, including a tile that holds the
+    ragged end of the queries and the keys (zero padding) and scores near the largest magnitude int8 rows reach."""
+    attn, lib = ops
+    head, q_tile, kv_tile = tile
+    lq, lk, h = 1230, 1390, 3
+    q, _, _ = inputs.attention_case(lq, h, seed=21)
+    _, k, v = inputs.attention_case(lk, h, seed=22)
+    q[5] = 40.0                      # rows whose codes are all +-127: |s| up to 127 * 127 * 128 = 2.06e6 < 2^22
+    k[7] = -40.0
+    pre = attn.int8_prepass(q.cuda(), k.cuda(), v.cuda())
+    out = torch.empty(lq, h, 128, device="cuda", dtype=torch.bfloat16)
+    dump = torch.full((128, 128), -1, dtype=torch.int32, device="cuda")
+    lib.call("rh3_attn_int8_dump_scores", pre.q8.data_ptr(), pre.qs.data_ptr(), pre.k8.data_ptr(), pre.ks.data_ptr(),
+             pre.vt.data_ptr(), pre.vscale.data_ptr(), pre.vmean.data_ptr(), lq, pre.q8.shape[1], lk, pre.k8.shape[1], h,
+             float(128 ** -0.5), out.data_ptr(), out.stride(0), out.stride(1), head, q_tile, kv_tile, dump.data_ptr(),
+             lib.stream())
+    lib.check_status()
+    q8 = pre.q8[head, q_tile * 128:(q_tile + 1) * 128].cpu().long()
+    k8 = pre.k8[head, kv_tile * 128:(kv_tile + 1) * 128].cpu().long()
+    want = (q8 @ k8.t()).to(torch.int32)
+    assert torch.equal(dump.cpu(), want)
+    if tile == (0, 0, 0):
+        assert want.abs().max() > 1_000_000          # the large scores are in this tile
+    assert torch.equal(out, attn.attention_pre(pre))  # the dump changes nothing else
 
 
 def test_attention_rr_and_strided_output(ops):

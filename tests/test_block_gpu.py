@@ -95,6 +95,85 @@ def test_step_matches_manual_chain_and_bf16_noise_floor(pkg, mode):
     assert err <= 4.0 * floor
 
 
+@pytest.mark.parametrize("mode", ["int8_rowwise", "int8_rot"])
+def test_fused_block_at_the_benchmark_width_matches_oracle(pkg, mode):
+    """One block of the benchmark configuration (d_model 4096, 32 heads x 128, MLP hidden 16384, cross-attention
+    to 512 text tokens of width 4096) on 4096 video + 148 audio tokens: two modality segments, a ragged last
+    64-token block, K = 16384 rows in the fc2 quantizer. Stage by stage against the CPU oracle."""
+    import copy
+    r = pkg
+    cfg = r.model.H3Config(n_blocks=1)
+    assert (cfg.d_model, cfg.heads, cfg.head_dim, cfg.mlp_hidden, cfg.text_dim) == (4096, 32, 128, 16384, 4096)
+    blk = r.model.init_weights(r.model.DiTBlock(cfg), seed=11)
+    latent, audio, t_emb, rope, ctx, segs, s = _case(r, cfg, grid=(16, 16, 16), n_audio=148, text_len=512, seed=4)
+    assert s == 4244 and s % 64 != 0
+    x = torch.randn(s, cfg.d_model, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    model = torch.nn.Module()
+    model.blocks = torch.nn.ModuleList([copy.deepcopy(blk).cuda()])
+    # the modulation tables are an input of the quantized path: both sides get the ones the device computes (a
+    # 4096-long bf16 dot product sums in a different order on the CPU)
+    adaln = tuple(t.cpu() for t in model.blocks[0].adaln_proj(t_emb[0].cuda()))
+    patched, = r.nodes.RapidH3LinearQuant().patch(model, mode)
+    trace = {}
+    out = patched.block_forward[0].forward(x.cuda(), t_emb[0].cuda(), segs, rope.cuda(), ctx[0].cuda(), trace=trace)
+    r._lib.check_status()
+    got = {k: v.cpu() for k, v in trace.items()}
+    # every stage of the oracle starts from the residual stream the device produced, so each stage is compared on
+    # identical inputs: what is integer (codes, scales, and the bf16 GEMM outputs that follow from them) must be
+    # bit-identical, what passes through the attention kernel's exponentials is held to 1e-3
+    want = {}
+    ref = ob.fused_block(blk, x, t_emb[0], segs, rope, ctx[0], trace=want, mode=mode, adaln=adaln,
+                         replay={k: got[k] for k in ("x_attn", "x_cross", "mlp_h")})
+    for name in ("attn_in_q", "attn_in_s", "qkv", "qkv_rr", "cross_in_q", "cross_in_s", "cross_q", "cross_k", "cross_v",
+                 "mlp_in_q", "mlp_in_s", "fc2_in_q", "fc2_in_s"):
+        assert torch.equal(got[name], want[name]), name
+    for name in ("attn_out", "x_attn", "cross_out", "x_cross", "mlp_h", "x_out"):
+        assert rel_l2(got[name], want[name]) <= 1e-3, name
+    assert rel_l2(out.cpu(), ref) <= 1e-3
+
+
+@pytest.mark.parametrize("mode", ["int8_rowwise", "int8_rot"])
+def test_step_divergence_at_the_benchmark_width(pkg, mode):
+    """The step-level acceptance measure at the benchmark width: four random-init blocks (d_model 4096, 32 heads, MLP
+    16384, cross-attention) on a 6 x 24 x 42 token grid + 148 audio tokens. The quantized step against the
+    unquantized bf16 model, in units of the divergence the bf16 model itself shows when its inputs move by one bf16
+    ulp (the reference's RapidH3Shadow measure, __init__.py:459-487).
+
+    The stated bar is 2x that floor. This random-init model does NOT meet it: row-wise W8A8 sits near 5x with or
+    without the H256 rotation (Gaussian weights and activations have no outlier channels for the rotation to
+    spread; every int8 row quantizer then costs about 1 % per linear, 28 linears deep). The test records the
+    ratios, separates the share of the linears from the share of the attention kernel, and holds the measured level
+    as a regression bound; it does not claim the 2x bar."""
+    r = pkg
+    cfg = r.model.H3Config(n_blocks=4)
+    model = r.model.init_weights_on_device(
+        r.model.H3Transformer(cfg).cuda(), torch.Generator(device="cuda").manual_seed(12))
+    grid, n_audio = (6, 24, 42), 148
+    latent, audio, t_emb, rope, ctx = r.step.make_inputs(cfg, grid, n_audio, 1, 512, seed=13)
+    dev = [t.cuda() for t in (latent, audio, t_emb, rope, ctx)]
+    args = (dev[0][0], dev[1][0], dev[2][0], dev[3], dev[4][0])
+    with torch.no_grad():
+        ref_v, ref_a = model(*args)
+        g = torch.Generator(device="cuda").manual_seed(1234)
+        jit = [t * (1 + 2.0 ** -8 * torch.randn(t.shape, generator=g, device="cuda").to(t.dtype)) for t in dev[:2]]
+        noisy_v, _ = model(jit[0][0], jit[1][0], *args[2:])
+        # quantized linears with the stock bf16 attention: the linears' share of the divergence
+        lin_only, = r.nodes.RapidH3LinearQuant().patch(model, mode, fuse_block=False)
+        lin_v, _ = lin_only(*args)
+    rt = r.step.H3Runtime(model, mode)
+    vid, aud = rt.step(*dev)
+    r._lib.check_status()
+    floor = rel_l2(noisy_v, ref_v)
+    err, err_lin = rel_l2(vid[0], ref_v), rel_l2(lin_v, ref_v)
+    err_attn = max(err * err - err_lin * err_lin, 0.0) ** 0.5
+    print(f"step divergence at d=4096 ({mode}): floor {floor:.3e}; quantized step {err:.3e} = {err / floor:.2f}x; "
+          f"linears alone {err_lin:.3e} = {err_lin / floor:.2f}x; attention kernel (in quadrature) {err_attn:.3e} = "
+          f"{err_attn / floor:.2f}x")
+    assert torch.isfinite(vid.float()).all()
+    assert err <= 6.5 * floor            # regression bound at the measured level (5.3x / 4.7x), not the 2x bar
+    assert err_lin <= err * 1.05         # the fused path adds the attention kernel's error, it does not hide any
+
+
 def test_fused_block_refuses_unsupported_calls(pkg):
     r = pkg
     cfg = r.model.H3Config.tiny()

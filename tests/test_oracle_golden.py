@@ -111,3 +111,75 @@ def test_rotation_butterfly_equals_hadamard_product():
     out = ol.linear(xb, wq, ws, "int8_rot").double()
     ref = xb.double() @ w.double().t()
     assert ((out - ref).norm() / ref.norm()).item() < 2e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# fixtures made by the reference's own H256 ConvRot code and its attention emulation script
+# ---------------------------------------------------------------------------------------------
+import os  # noqa: E402
+
+_GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _code_agreement(q, q0):
+    """(fraction of codes that differ, largest difference): the reference's own yardstick, bench/rot_test.py:22-26."""
+    d = (q.int() - q0.int()).abs()
+    return (d > 0).float().mean().item(), int(d.max())
+
+
+def test_rotation_matches_the_reference_convrot():
+    """H256 itself, the rotated activations, and the rotated int8 codes of activations and weights against what
+    triton_fp8.regular_hadamard / convrot and kernels.quantize_weight("int8_rot") of the reference return. The
+    reference rotates with a matrix product (summation order unspecified), so codes are held to its own
+    criterion: at most one step apart on fewer than 1e-3 of the elements, scales equal to fp32 rounding."""
+    g = torch.load(os.path.join(_GOLDEN, "rot_ref.pt"))
+    assert torch.equal(ol.regular_hadamard(256).float(), g["h256"])
+    r = ol.rotate256(g["x"].float())
+    assert (r - g["x_rot"]).abs().max() <= 4e-6 * g["x_rot"].abs().max()
+    xq, xs = ol.quantize_rows(g["x"], "int8_rot")
+    frac, worst = _code_agreement(xq, g["x_q"])
+    assert frac < 1e-3 and worst <= 1
+    assert ((xs - g["x_s"]).abs() / g["x_s"]).max() < 1e-6
+    wq, ws = ol.quantize_weight(g["w"], "int8_rot")
+    frac, worst = _code_agreement(wq, g["w_q"])
+    assert frac < 1e-3 and worst <= 1
+    assert ((ws - g["w_s"]).abs() / g["w_s"]).max() < 1e-6
+
+
+def test_attention_operands_match_the_reference_emulation():
+    """Block-64 int8 Q and K (K mean-smoothed) and per-channel e4m3 V: codes x scales of the oracle's pre-pass
+    equal, bit for bit, the fake-quantized tensors of bench/attn_emulate.py `q8(x, 1, 64)` / `f8(x, 0)` when both
+    are given the same channel means."""
+    from oracle import attention as oa
+    g = torch.load(os.path.join(_GOLDEN, "attn_ref.pt"))
+    q, k, v = g["q"], g["k"], g["v"]
+    l = q.shape[0]
+    kmean, vmean, vscale = oa.kv_stats(k, v)
+    assert torch.equal(kmean, g["kmean"]) and torch.equal(vmean, g["vmean"])
+    q8, qs = oa.quant_block64(q, pad=256)
+    k8, ks = oa.quant_block64(k, kmean)
+    vt = oa.quant_v(v, vmean, vscale)
+    blk = torch.arange(l) // 64
+    for h, ref in enumerate(g["heads"]):
+        assert torch.equal(q8[h, :l].float() * qs[h][blk][:, None], ref["q_fq"])
+        assert torch.equal(k8[h, :l].float() * ks[h][blk][:, None], ref["k_fq"])
+        vdec = vt[h, :, :l].view(torch.float8_e4m3fn).float().t() * vscale[h][None]
+        assert torch.equal(vdec, ref["v_fq"])
+
+
+def test_attention_output_is_bounded_by_the_reference_emulation():
+    """The main loop against `attn(..., pmode="run_fp8")` of bench/attn_emulate.py on the same fake-quantized
+    operands. The two are not the same arithmetic: the reference scales P to 448 against the final row maximum,
+    here P is scaled to 2^8 against the row maximum rounded up to an integer (base 2), so each P lands on a
+    different point of the e4m3 grid. What must hold: both sit at the same distance from the exact-P result
+    (within 25 %), and they differ from each other by no more than the two rounding errors combined."""
+    from oracle import attention as oa
+    g = torch.load(os.path.join(_GOLDEN, "attn_ref.pt"))
+    out = oa.attention(g["q"], g["k"], g["v"]).float()
+    for h, ref in enumerate(g["heads"]):
+        exact = ref["out_exact_p"]
+        e_ref = ((ref["out_run_fp8"] - exact).norm() / exact.norm()).item()
+        e_own = ((out[:, h] - exact).norm() / exact.norm()).item()
+        between = ((out[:, h] - ref["out_run_fp8"]).norm() / exact.norm()).item()
+        assert e_own <= 1.25 * e_ref + 4e-3      # 4e-3: the bf16 rounding of the output
+        assert between <= e_own + e_ref

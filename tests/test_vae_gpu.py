@@ -93,7 +93,7 @@ def test_gn_silu_and_upsample(vae):
     beta = (0.1 * torch.randn(128, generator=g)).to(torch.bfloat16)
     xd = x.cuda()
     y = v.gn_silu(xd, v.gn_sums_from_tensor(xd), x.numel() // (2 * 32), gamma.cuda(), beta.cuda())
-    assert rel_l2(y.cpu(), ov.gn_silu(x, gamma, beta)) <= 2e-3
+    assert rel_l2(y.cpu(), ov.gn_silu(x, gamma, beta)) <= 1e-3
     assert torch.equal(v.upsample(xd).cpu(), ov.upsample(x))
 
 
@@ -109,6 +109,42 @@ def test_decoder_matches_oracle(vae):
     # every layer rounds to bf16 (2^-9 relative); rounding flips compound over the 9 layers, so the whole
     # decoder is compared at a few bf16 ulps while each op alone is held to 1e-3 above
     assert rel_l2(rgb.cpu(), ref) <= 2e-2
+
+
+def test_decoder_at_the_benchmark_widths_layer_by_layer(vae):
+    """The decoder of the benchmark configuration (widths 512 -> 256 -> 128, two residual blocks per stage) on a
+    16 x 5 x 6 x 8 latent. Every layer (convolution with bias and residual, GroupNorm + SiLU, causal upsampling)
+    is replayed on the oracle's own input of that layer and held to rel-L2 <= 1e-3; the whole 21-layer chain,
+    where one-ulp bf16 flips compound from layer to layer, is reported and held to 2e-2."""
+    v, lib = vae
+    dec = v.VAEDecoder(seed=2)
+    assert dec.widths == (512, 256, 128) and dec.blocks == 2
+    latent = torch.randn(1, 16, 5, 6, 8, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16)
+    trace = []
+    ref = ov.decode(dec.cpu, latent, trace=trace)
+    worst = {}
+    for op, name, ins, want in trace:
+        if op == "conv":
+            x, res = ins
+            got, _ = v.conv3d_causal(x.contiguous().cuda(), dec.p[name + ".w"], dec.p[name + ".b"],
+                                     None if res is None else res.contiguous().cuda())
+        elif op == "gn":
+            xd = ins[0].contiguous().cuda()
+            got = v.gn_silu(xd, v.gn_sums_from_tensor(xd), xd.numel() // (xd.shape[0] * 32), dec.p[name + ".g"],
+                            dec.p[name + ".be"])
+        else:
+            got = v.upsample(ins[0].contiguous().cuda())
+            assert torch.equal(got.cpu(), want)
+        e = rel_l2(got.cpu(), want)
+        worst[op] = max(worst.get(op, 0.0), e)
+        assert e <= 1e-3, (op, name, e)
+    lib.check_status()
+    rgb = dec.decode(latent.cuda())
+    lib.check_status()
+    assert rgb.shape == (1, 3, 17, 192, 256)
+    whole = rel_l2(rgb.cpu(), ref)
+    print(f"decoder at widths (512, 256, 128): worst layer rel-L2 {worst}, whole chain {whole:.2e}")
+    assert whole <= 2e-2
 
 
 def test_depth_to_space_is_the_head_permutation(vae):
