@@ -328,6 +328,9 @@ def main():
                     help="N > 1: token <-> head exchanges as NCCL all-to-all, or done by the rope and attention kernels "
                          "themselves (stores into peer buffers); auto = fused, falling back to nccl if the peer "
                          "buffers cannot be set up")
+    ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
+                    help="run the CFG samples of a step side by side on two streams (auto: when N > 1, where it hides "
+                         "the exchanges of the sequence-parallel step)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -355,18 +358,28 @@ def main():
     cfg = H3Config(n_blocks=blocks)
     rt = r.step.H3Runtime.random(cfg, seed=0, device=f"cuda:{local}", mode=args.mode)
     s_total = grid[0] * grid[1] * grid[2] + n_audio
-    sp = r.sp.Ulysses(s_total) if world > 1 else None
+    # the CFG samples of a step are independent: with --overlap each runs on its own stream, and (N > 1) with its own
+    # process group and exchange buffers, so one sample's exchanges hide under the other's kernels
+    side_by_side = batch > 1 and (args.overlap == "on" or (args.overlap == "auto" and world > 1))
+    streams = [torch.cuda.Stream() for _ in range(batch)] if side_by_side else None
+    sp = None
     exchange = "none"
-    if sp is not None:
+    if world > 1:
+        groups = [dist.new_group(list(range(world))) for _ in range(batch)] if side_by_side else [None]
+        sps = [r.sp.Ulysses(s_total, group=g) for g in groups]
         exchange = "nccl all_to_all_single"
         if args.exchange in ("fused", "auto"):
             try:
-                how = sp.enable_fused(cfg.heads, cfg.head_dim, torch.device("cuda", local))
+                for u in sps:
+                    how = u.enable_fused(cfg.heads, cfg.head_dim, torch.device("cuda", local))
                 exchange = f"kernel stores into peer buffers ({how})"
             except Exception as e:  # noqa: BLE001
                 if args.exchange == "fused":
                     raise
+                for u in sps:
+                    u.fused = False
                 print(f"[bench] peer buffers unavailable ({type(e).__name__}: {e}); using NCCL all-to-all", file=sys.stderr)
+        sp = sps if side_by_side else sps[0]
     host = [t.pin_memory() for t in r.step.make_inputs(cfg, grid, n_audio, batch, text_len, seed=0)]
     dev = [t.cuda(non_blocking=True) for t in host]
     rope_dev = dev[3]
@@ -379,11 +392,11 @@ def main():
         torch.cuda.synchronize()
 
     def step_resident():
-        return rt.step(dev[0], dev[1], dev[2], rope_dev, dev[4], sp=sp)
+        return rt.step(dev[0], dev[1], dev[2], rope_dev, dev[4], sp=sp, streams=streams)
 
     def step_e2e():
         lat, aud, temb, ctx = (host[i].cuda(non_blocking=True) for i in (0, 1, 2, 4))
-        v, a = rt.step(lat, aud, temb, rope_dev, ctx, sp=sp)
+        v, a = rt.step(lat, aud, temb, rope_dev, ctx, sp=sp, streams=streams)
         out_host[0].copy_(v, non_blocking=True)
         out_host[1].copy_(a, non_blocking=True)
 
@@ -462,7 +475,8 @@ def main():
     rec = {"metric": "H3 DiT step seconds @768x1344x141f", "value": ms_step / 1e3, "unit": "s/step", "n_gpus": world,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False,
            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-           "config": workload_config(args.workload, world), "variant": {"linear_mode": args.mode, "exchange": exchange},
+           "config": workload_config(args.workload, world), "variant": {"linear_mode": args.mode, "exchange": exchange,
+                       "cfg_samples": "side by side on two streams" if side_by_side else "one after the other"},
            "clocks": clocks,
            "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
            "gpu_launches": launches, "roofline": roof, "roofline_gemm": roof_gemm, "roofline_quant": roof_quant,

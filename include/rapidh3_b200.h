@@ -116,7 +116,8 @@ int rh3_rmsnorm_rope3d(const void* x, int64_t x_ss, int64_t x_sh, void* y, int64
 /* Bytes of scratch rh3_attn_kv_stats needs for L tokens and H heads (returns the size, not a status). */
 int64_t rh3_attn_kv_stats_scratch_bytes(int64_t L, int64_t H);
 /* kmean, vmean, vscale: fp32 [H,128]. Per-(head, channel) mean of K and V over the L tokens (sums in
- * 256-token chunks, chunks in order) and vscale = max(max|v - vmean|, 1e-8) / 448.
+ * 256-token chunks: 16 groups of 16 tokens, tokens, groups and chunks each in order) and
+ * vscale = max(max|v - vmean|, 1e-8) / 448. Rows 16-byte aligned.
  * Replaces stats_partial + stats_final (attn_int8.cu:82-109). */
 int rh3_attn_kv_stats(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t L,
                       int64_t H, void* scratch, int64_t scratch_bytes, float* kmean, float* vmean, float* vscale,
@@ -144,6 +145,23 @@ int rh3_attn_quant_qk(const void* x, int64_t x_ss, int64_t x_sh, int64_t L, int6
  * scale of bench/attn_emulate.py:16-18,101 (`f8(v - vm, 0)`). */
 int rh3_attn_quant_v(const void* v, int64_t v_ss, int64_t v_sh, int64_t L, int64_t Lpad, int64_t H,
                      const float* vmean, const float* vscale, void* vt, cudaStream_t stream);
+/* The whole pre-pass of one attention call in three launches (what the reference's `prepass`, attn_int8.cu:2568-2644,
+ * does in five, incl. its `_rr` forms that fuse the q/k RMSNorm + RoPE, :297-340 / :360-399):
+ *   q [Lq,H,128], k, v [Lk,H,128] bf16 views (element strides given; rows 16-byte aligned).
+ *   q_weight / k_weight (bf16 [128], both or neither): when given, q and k are raw and get the per-head RMSNorm (eps)
+ *   and, with rope_table (bf16 [L,48,2,2], needs Lq == Lk), the 3-D RoPE of rh3_rmsnorm_rope3d first. The normalised k
+ *   is written to k_roped (strides kr_ss, kr_sh; it may be k itself) because the K quantizer needs the mean of the
+ *   whole sequence before it can run; the normalised q is quantized from registers and only stored when q_roped is
+ *   not NULL. scratch: rh3_attn_kv_stats_scratch_bytes(Lk, H) bytes.
+ *   Outputs as rh3_attn_quant_qk / rh3_attn_quant_v / rh3_attn_kv_stats define them: q8 [H,Lq_pad,128], qs [H,Lq_pad/64],
+ *   k8 [H,Lk_pad,128], ks [H,Lk_pad/64], vt [H,128,Lk_pad], vscale, vmean, kmean [H,128]. Lq_pad % 256 == 0,
+ *   Lk_pad % 128 == 0. */
+int rh3_attn_prepass(const void* q, int64_t q_ss, int64_t q_sh, int64_t Lq, int64_t Lq_pad, const void* k, int64_t k_ss,
+                     int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t Lk, int64_t Lk_pad, int64_t H,
+                     const void* q_weight, const void* k_weight, float eps, const void* rope_table, void* q_roped,
+                     int64_t qr_ss, int64_t qr_sh, void* k_roped, int64_t kr_ss, int64_t kr_sh, void* scratch,
+                     int64_t scratch_bytes, void* q8, float* qs, void* k8, float* ks, void* vt, float* vscale,
+                     float* vmean, float* kmean, cudaStream_t stream);
 /* out[Lq, H, 128] bf16 (element strides o_ss, o_sh) = softmax(Q.K^T * softmax_scale) . V from the
  * pre-pass operands: int8 Q.K^T into int32, base-2 online softmax in fp32, P as e4m3 against the
  * running maximum, e4m3 P.V into fp32, out = (O/l) * vscale + vmean. Lq may differ from Lk.

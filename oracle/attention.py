@@ -63,15 +63,16 @@ def _bf(x):
 
 
 def rmsnorm_rope(x, weight, eps, tab=None):
-    """x bf16 [S,H,128] -> bf16 [S,H,128]."""
+    """x bf16 [S,H,128] -> bf16 [S,H,128]. Sum of squares in the kernel's order: a lane holds 8 consecutive
+    channels and adds their squares in order, then an xor butterfly (8, 4, 2, 1) over the 16 lanes of the row."""
     s, h, _ = x.shape
     xf = x.float()
-    sq = (xf * xf).view(s, h, 32, 4)
-    acc = torch.zeros(s, h, 32)
-    for j in range(4):
+    sq = (xf * xf).view(s, h, 16, 8)
+    acc = torch.zeros(s, h, 16)
+    for j in range(8):
         acc = acc + sq[..., j]
-    lanes = torch.arange(32)
-    for o in (16, 8, 4, 2, 1):
+    lanes = torch.arange(16)
+    for o in (8, 4, 2, 1):
         acc = acc + acc[..., lanes ^ o]
     ss = acc[..., 0]
     r = 1.0 / ieee_sqrt(ss / 128.0 + torch.tensor(eps, dtype=torch.float32))
@@ -85,16 +86,20 @@ def rmsnorm_rope(x, weight, eps, tab=None):
     return torch.cat([o1, o2, n[..., 96:]], -1).to(torch.bfloat16)
 
 
-def chunked_column_sum(x, chunk=256):
-    """Sum over dim 0 of fp32 x [L, ...]: sequential inside 256-row chunks, then chunks in order."""
+def chunked_column_sum(x, chunk=256, group=16):
+    """Sum over dim 0 of fp32 x [L, ...] in the kernel's order: a 256-row chunk is 16 groups of 16 rows; rows of a
+    group in order, then the groups in order, then the chunks in order."""
     l = x.shape[0]
     nchunk = (l + chunk - 1) // chunk
     pad = torch.zeros((nchunk * chunk,) + x.shape[1:], dtype=torch.float32)
     pad[:l] = x
-    pad = pad.view((nchunk, chunk) + x.shape[1:])
+    pad = pad.view((nchunk, chunk // group, group) + x.shape[1:])
+    grp = torch.zeros((nchunk, chunk // group) + x.shape[1:], dtype=torch.float32)
+    for i in range(group):
+        grp = grp + pad[:, :, i]
     part = torch.zeros((nchunk,) + x.shape[1:], dtype=torch.float32)
-    for i in range(chunk):
-        part = part + pad[:, i]
+    for g in range(chunk // group):
+        part = part + grp[:, g]
     tot = torch.zeros(x.shape[1:], dtype=torch.float32)
     for c in range(nchunk):
         tot = tot + part[c]

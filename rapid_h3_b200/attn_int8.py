@@ -69,39 +69,58 @@ def rms_rope(x, weight, eps, tab=None, out=None):
     return out
 
 
-def int8_prepass(q, k, v, _tag="call"):
-    """Quantize the operands of one attention call: K/V statistics, block-64 int8 Q and K, e4m3 V^T."""
+def int8_prepass(q, k, v, tab=None, qw=None, kw=None, eps=1e-5, q_roped=None, k_roped=None, _tag="call"):
+    """Quantize the operands of one attention call (three launches): K/V statistics, block-64 int8 Q and K, e4m3 V^T.
+    With norm weights `qw` / `kw` (bf16 [128]) q and k are raw and get the per-head RMSNorm first, and with `tab`
+    (bf16 [S, 48, 2, 2]) the 3-D RoPE as well; the normalised k is written to `k_roped` (a [Lk, H, 128] view, `k`
+    itself for in place; a new tensor if None) and the normalised q only if `q_roped` is given."""
     with _phase(f"attn_{_tag}_prepass", (q.shape[0] + 2 * k.shape[0]) * q.shape[1] * D * 3):
-        return _int8_prepass(q, k, v)
+        return _int8_prepass(q, k, v, tab, qw, kw, eps, q_roped, k_roped)
 
 
-def _int8_prepass(q, k, v):
+def _int8_prepass(q, k, v, tab, qw, kw, eps, q_roped, k_roped):
     for t, n in ((q, "q"), (k, "k"), (v, "v")):
         _check_qkv(t, n)
     lq, h, _ = q.shape
     lk = k.shape[0]
     if k.shape != v.shape or k.shape[1] != h:
         raise RuntimeError("k and v must have the same shape and q's head count")
+    if (qw is None) != (kw is None):
+        raise RuntimeError("q and k norm weights come together")
     dev = q.device
+    if qw is not None:
+        for w in (qw, kw):
+            if w.dtype != torch.bfloat16 or w.numel() != D:
+                raise RuntimeError("norm weight must be bf16 [128]")
+        qw, kw = qw.contiguous(), kw.contiguous()
+        if k_roped is None:
+            k_roped = torch.empty((lk, h, D), device=dev, dtype=torch.bfloat16)
+        _check_qkv(k_roped, "k_roped")
+        if q_roped is not None:
+            _check_qkv(q_roped, "q_roped")
+    if tab is not None:
+        if qw is None or lq != lk or tab.dtype != torch.bfloat16 or tab.numel() != lq * 48 * 4:
+            raise RuntimeError("a rope table (bf16 [S, 48, 2, 2]) needs the norm weights and Lq == Lk")
+        tab = tab.contiguous()
     lqp, lkp = _pad256(lq), _pad128(lk)
     f32 = dict(device=dev, dtype=torch.float32)
     kmean, vmean, vscale = (torch.empty((h, D), **f32) for _ in range(3))
     nbytes = _lib.lib().rh3_attn_kv_stats_scratch_bytes(lk, h)
     scratch = torch.empty(nbytes, device=dev, dtype=torch.uint8)
-    st = _lib.stream()
-    _lib.call("rh3_attn_kv_stats", k.data_ptr(), k.stride(0), k.stride(1), v.data_ptr(), v.stride(0), v.stride(1),
-              lk, h, scratch.data_ptr(), nbytes, kmean.data_ptr(), vmean.data_ptr(), vscale.data_ptr(), st)
     q8 = torch.empty((h, lqp, D), device=dev, dtype=torch.int8)
     k8 = torch.empty((h, lkp, D), device=dev, dtype=torch.int8)
     qs = torch.empty((h, lqp // 64), **f32)
     ks = torch.empty((h, lkp // 64), **f32)
     vt = torch.empty((h, D, lkp), device=dev, dtype=torch.float8_e4m3fn)
-    _lib.call("rh3_attn_quant_qk", q.data_ptr(), q.stride(0), q.stride(1), lq, lqp, h, None, q8.data_ptr(),
-              qs.data_ptr(), st)
-    _lib.call("rh3_attn_quant_qk", k.data_ptr(), k.stride(0), k.stride(1), lk, lkp, h, kmean.data_ptr(),
-              k8.data_ptr(), ks.data_ptr(), st)
-    _lib.call("rh3_attn_quant_v", v.data_ptr(), v.stride(0), v.stride(1), lk, lkp, h, vmean.data_ptr(),
-              vscale.data_ptr(), vt.data_ptr(), st)
+
+    def view(t):
+        return (None, 0, 0) if t is None else (t.data_ptr(), t.stride(0), t.stride(1))
+
+    _lib.call("rh3_attn_prepass", q.data_ptr(), q.stride(0), q.stride(1), lq, lqp, k.data_ptr(), k.stride(0), k.stride(1),
+              v.data_ptr(), v.stride(0), v.stride(1), lk, lkp, h, _lib.ptr(qw), _lib.ptr(kw), float(eps), _lib.ptr(tab),
+              *view(q_roped), *view(k_roped if qw is not None else None), scratch.data_ptr(), nbytes, q8.data_ptr(),
+              qs.data_ptr(), k8.data_ptr(), ks.data_ptr(), vt.data_ptr(), vscale.data_ptr(), vmean.data_ptr(),
+              kmean.data_ptr(), _lib.stream())
     return Prepass(q8, qs, k8, ks, vt, vscale, vmean, kmean, lq, lk)
 
 
@@ -140,7 +159,7 @@ def attention(q, k, v, scale=None, config=0, smooth_k=True, smooth_v=True, rotat
     `_tag` only names the timing phases of this call (timing.PHASES)."""
     if rotate:
         raise NotImplementedError("the Hadamard-rotated per-token variant is not implemented")
-    return attention_pre(int8_prepass(q, k, v, _tag), scale, out, _tag=_tag)
+    return attention_pre(int8_prepass(q, k, v, _tag=_tag), scale, out, _tag=_tag)
 
 
 def attention_bhsd(q, k, v, scale=None, config=0, out=None):
@@ -152,8 +171,9 @@ def attention_bhsd(q, k, v, scale=None, config=0, out=None):
     return o.transpose(0, 1).unsqueeze(0) if out is None else out
 
 
-def attention_rr(q, k, v, tab, qw, kw, eps, scale=None, config=0, out=None):
-    """attention() on raw q/k with the per-head RMSNorm + 3-D RoPE applied first; q and k are left untouched."""
-    qn = rms_rope(q, qw, eps, tab)
-    kn = rms_rope(k, kw, eps, tab)
-    return attention(qn, kn, v, scale, out=out)
+def attention_rr(q, k, v, tab, qw, kw, eps, scale=None, config=0, out=None, q_roped=None, k_roped=None, _tag="call"):
+    """attention() on raw q / k with the per-head RMSNorm (+ 3-D RoPE when `tab` is given) fused into the pre-pass.
+    q and k are left untouched unless the caller passes them as `q_roped` / `k_roped` (views that receive the
+    normalised rows; the fused block passes k itself, whose raw values nothing reads afterwards)."""
+    pre = int8_prepass(q, k, v, tab, qw, kw, eps, q_roped, k_roped, _tag=_tag)
+    return attention_pre(pre, scale, out, _tag=_tag)

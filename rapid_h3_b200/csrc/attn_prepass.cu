@@ -1,21 +1,34 @@
-// Attention pre-pass kernels (all HBM-bound, one pass over their inputs each):
+// Attention pre-pass: everything that turns bf16 q / k / v rows into the operands of the INT8 attention kernel.
+// All of it is HBM-bound row work, laid out the same way everywhere: a HALF-WARP owns one (token, head) row of 128
+// channels, lane i of the half-warp holds channels 8i .. 8i+7, so every global access is one 16-byte load or store
+// per lane (256 B per row per instruction) and a warp has two rows in flight.
 //
-//   rh3_rmsnorm_rope3d      per-(token, head) RMSNorm over 128 channels + split-half partial 3-D RoPE
-//                           (rot_dim 96 = 3 axes x 16 frequencies x 2; pairs (i, i+48); channels
-//                           96..127 are normalised only); bf16 in, bf16 out, token-local.
-//   rh3_attn_kv_stats       per-(head, channel) K mean (smoothing), V mean and V scale, with a
-//                           deterministic two-level sum: 256-token chunks, then chunks in order.
-//   rh3_attn_quant_qk       int8 codes with ONE abs-max scale per 64-token block per head
-//                           (K after subtracting the per-head channel mean), laid out [H][Lpad][128].
-//   rh3_attn_quant_v        V - mean -> fp8 e4m3 with one scale per (head, channel), transposed to
-//                           [H][128][Lpad] so that keys are the contiguous (K-major) axis of P.V.
+//   rh3_attn_prepass        the whole pre-pass of one attention call in three launches:
+//                             1. rope_stats_kernel  Q rows: (RMSNorm + 3-D RoPE) -> block-64 int8 codes and scales,
+//                                                   straight from registers;
+//                                                   K rows: (RMSNorm + RoPE, stored once as bf16) and V rows:
+//                                                   per-(head, channel) partial sums / extrema of 256-token chunks
+//                             2. kv_stats_final     K mean (smoothing), V mean and V scale from the partials
+//                             3. quant_kv_kernel    K - mean -> block-64 int8; (V - mean) / scale -> e4m3, transposed
+//                           q is read once, k and v twice, and nothing but the roped k is written besides the operands.
+//   rh3_rmsnorm_rope3d      the RMSNorm + RoPE alone (bf16 in, bf16 out)
+//   rh3_attn_kv_stats, rh3_attn_quant_qk, rh3_attn_quant_v   the stages one by one, on the same kernels
+//   rh3_rope_scatter_heads  RMSNorm + RoPE fused with the token -> head exchange of sequence parallelism
 //
-// Reference for the arithmetic: custom_nodes/rapid_h3/csrc/attn_int8.cu:82-109 (stats_partial /
-// stats_final), :130-170 (quant_qk), :217-260 (rms_rope_row), :404-443 (per-block K scale),
-// :452-496 (quant_v incl. its e4m3 branch) and the error-emulation script bench/attn_emulate.py:10-23
-// (`q8(x, 1, 64)`, `f8(x, 0)`). Differences that are deliberate: IEEE division/sqrt instead of the
-// .approx.ftz forms (the CPU oracle must be able to reproduce every bit), block-64 scales and an
-// e4m3 V scaled to 448 by its own abs-max.
+// Arithmetic contract (what the CPU oracle restates bit for bit; reference: custom_nodes/rapid_h3/csrc/
+// attn_int8.cu:82-109 stats, :130-170 / :404-443 Q/K quantizers, :217-260 rms_rope_row, :452-496 quant_v, and the
+// emulation script bench/attn_emulate.py:10-23 `q8(x, 1, 64)` / `f8(x, 0)`):
+//   RMSNorm   sum of squares: the 8 channels of a lane in order, then an xor butterfly over the 16 lanes;
+//             r = 1 / sqrt(ss / 128 + eps) with IEEE division and square root (the reference uses the .approx forms,
+//             which no CPU reproduces); y = bf16((r * x) * w)
+//   RoPE      pairs (i, i + 48), i < 48, table row [48][2][2] bf16 = (t00, t01, t10, t11):
+//             out_i = bf16(a * t00 + b * t01), out_{i+48} = bf16(a * t10 + b * t11), a = y_i, b = y_{i+48};
+//             channels 96..127 are normalised only
+//   K / V statistics over the STORED bf16 values: inside a 256-token chunk the 16 tokens of a half-warp in order,
+//             then the 16 half-warps in order; then the chunks in order; mean = sum / L;
+//             vscale = max(max(vmax - vmean, vmean - vmin), 1e-8) / 448
+//   Q / K     one scale per 64-token block per head, s = max(amax, 1e-8) / 127, code = rint((x - mean) / s)
+//   V         e4m3((v - vmean) / vscale) clamped to +-448, stored [H][128][Lpad] so that keys are contiguous
 #include <atomic>
 
 #include "common.cuh"
@@ -25,105 +38,112 @@ namespace rh3 {
 namespace {
 
 constexpr int D = 128;
-constexpr int STAT_CHUNK = 256;
+constexpr int CHUNK = 256;         // tokens per statistics chunk = per CTA of rope_stats_kernel
+constexpr int HW_PER_CTA = 16;     // half-warps in a 256-thread CTA
+constexpr int TOK_PER_HW = CHUNK / HW_PER_CTA;   // K / V side: 16 tokens per half-warp, in batches of 4
+constexpr int Q_TILE = 128;                      // Q side: a CTA covers two 64-token blocks, 8 tokens per half-warp
+constexpr int Q_TOK_PER_HW = Q_TILE / HW_PER_CTA;
 
-__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* x) {
-  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+// ---------------------------------------------------------------------------------------------
+// half-warp row helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4 raw, float* x) {
   x[0] = bf16_lo(raw.x); x[1] = bf16_hi(raw.x); x[2] = bf16_lo(raw.y); x[3] = bf16_hi(raw.y);
+  x[4] = bf16_lo(raw.z); x[5] = bf16_hi(raw.z); x[6] = bf16_lo(raw.w); x[7] = bf16_hi(raw.w);
+}
+__device__ __forceinline__ uint4 pack8(const float* x) {
+  return make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+}
+__device__ __forceinline__ uint4 load_row16(const __nv_bfloat16* row, int l16) {
+  return __ldg(reinterpret_cast<const uint4*>(row + l16 * 8));
+}
+// sum over the 16 lanes of a half-warp, same value in every lane, fixed order (xor 8, 4, 2, 1)
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float half_warp_max(float v) {
+#pragma unroll
+  for (int o = 8; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
 }
 
-// ---------------------------------------------------------------------------------------------
-// RMSNorm + 3-D RoPE. One warp per (token, head) row; lane l owns channels 4l..4l+3.
-// ---------------------------------------------------------------------------------------------
-// The rope-table words of one token for this lane (lanes 0..23 hold pair indices 4*(lane % 12) .. +3).
-__device__ __forceinline__ void load_rope_words(const __nv_bfloat16* __restrict__ tab_row, int lane, uint32_t* tw) {
-  if (tab_row != nullptr && lane < 24) {
-    const int i0 = (lane < 12 ? lane : lane - 12) * 4;  // index of the pair in the table row
-    const __nv_bfloat16* t = tab_row + i0 * 4;
-    const uint4 t0 = __ldg(reinterpret_cast<const uint4*>(t));
-    const uint4 t1 = __ldg(reinterpret_cast<const uint4*>(t + 8));
-    tw[0] = t0.x, tw[1] = t0.y, tw[2] = t0.z, tw[3] = t0.w, tw[4] = t1.x, tw[5] = t1.y, tw[6] = t1.z, tw[7] = t1.w;
+// What a lane needs of the norm weight and of one token's rope table row.
+struct NormRope {
+  float w[8];        // norm weight of this lane's channels
+  uint32_t t[16];    // rope words of this lane's 8 pairs: t[2j] = (t00, t01), t[2j+1] = (t10, t11) of pair j
+};
+__device__ __forceinline__ void load_norm_weight(const __nv_bfloat16* __restrict__ w, int l16, NormRope& nr) {
+  unpack8(load_row16(w, l16), nr.w);
+}
+// Lanes 0..5 hold the first halves of the rotary pairs (channels 0..47), lanes 6..11 the second halves (48..95);
+// both read the 64 bytes of the table row that describe their 8 pairs. Lanes 12..15 only normalise.
+__device__ __forceinline__ void load_rope_row(const __nv_bfloat16* __restrict__ tab_row, int l16, NormRope& nr) {
+  if (l16 < 12) {
+    const uint4* p = reinterpret_cast<const uint4*>(tab_row + (l16 < 6 ? l16 : l16 - 6) * 32);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 q = __ldg(p + i);
+      nr.t[4 * i] = q.x, nr.t[4 * i + 1] = q.y, nr.t[4 * i + 2] = q.z, nr.t[4 * i + 3] = q.w;
+    }
   }
 }
-
-// RMSNorm + rope of the four channels lane*4..lane*4+3 of one (token, head) row given its values, the norm weights
-// of those channels and the token's rope words; returns the packed bf16 result.
-__device__ __forceinline__ uint2 rmsnorm_rope_vals(const float* v, const float* wv, float eps, const uint32_t* tw,
-                                                   bool has_tab, int lane) {
+// RMSNorm (+ RoPE when `rope`) of one row held as 8 floats per lane; the result is the bf16-rounded row, as floats.
+__device__ __forceinline__ void norm_rope_row(float* v, const NormRope& nr, float eps, bool rope, int lane) {
+  const int l16 = lane & 15;
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < 4; ++j) ss = __fadd_rn(ss, __fmul_rn(v[j], v[j]));
-  ss = warp_sum_xor(ss);
+  for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(v[j], v[j]));
+  ss = half_warp_sum(ss);
   const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.f), eps)));
-  float n[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) n[j] = bf16_round(__fmul_rn(__fmul_rn(r, v[j]), wv[j]));
-  float o[4] = {n[0], n[1], n[2], n[3]};
-  if (has_tab) {
-    // partner lane holds the other half of the rotary pair (channels +-48 = 12 lanes away)
-    const int partner = lane < 12 ? lane + 12 : (lane < 24 ? lane - 12 : lane);
-    float pn[4];
+  for (int j = 0; j < 8; ++j) v[j] = bf16_round(__fmul_rn(__fmul_rn(r, v[j]), nr.w[j]));
+  if (rope) {
+    // the other half of every pair lives 6 lanes away (48 channels) in the same half-warp
+    const int partner = (lane & 16) | (l16 < 6 ? l16 + 6 : (l16 < 12 ? l16 - 6 : l16));
+    float other[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) pn[j] = __shfl_sync(0xffffffffu, n[j], partner);
-    if (lane < 24) {
+    for (int j = 0; j < 8; ++j) other[j] = __shfl_sync(0xffffffffu, v[j], partner);
+    if (l16 < 12) {
+      const bool first = l16 < 6;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float t00 = bf16_lo(tw[2 * j]), t01 = bf16_hi(tw[2 * j]);
-        const float t10 = bf16_lo(tw[2 * j + 1]), t11 = bf16_hi(tw[2 * j + 1]);
-        const float a = lane < 12 ? n[j] : pn[j];
-        const float b = lane < 12 ? pn[j] : n[j];
-        o[j] = lane < 12 ? bf16_round(__fadd_rn(__fmul_rn(a, t00), __fmul_rn(b, t01)))
-                         : bf16_round(__fadd_rn(__fmul_rn(a, t10), __fmul_rn(b, t11)));
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t tw = first ? nr.t[2 * j] : nr.t[2 * j + 1];
+        const float a = first ? v[j] : other[j], b = first ? other[j] : v[j];
+        v[j] = bf16_round(__fadd_rn(__fmul_rn(a, bf16_lo(tw)), __fmul_rn(b, bf16_hi(tw))));
       }
     }
   }
-  return make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
-}
-
-__device__ __forceinline__ uint2 rmsnorm_rope_row(const __nv_bfloat16* __restrict__ xrow,
-                                                  const __nv_bfloat16* __restrict__ w, float eps,
-                                                  const __nv_bfloat16* __restrict__ tab_row, int lane) {
-  float v[4], wv[4];
-  uint32_t tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  load4(xrow + lane * 4, v);
-  load4(w + lane * 4, wv);
-  load_rope_words(tab_row, lane, tw);
-  return rmsnorm_rope_vals(v, wv, eps, tw, tab_row != nullptr, lane);
-}
-
-// One warp per (token, group of HG consecutive heads): the token's rope words and the norm weights are loaded
-// once and the HG rows' loads are issued together. HG = 4 when H is a multiple of 4, else 1.
-template <int HG>
-__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_ss,
-                                                           int64_t x_sh, __nv_bfloat16* __restrict__ y, int64_t y_ss,
-                                                           int64_t y_sh, int64_t S, int H,
-                                                           const __nv_bfloat16* __restrict__ w, float eps,
-                                                           const __nv_bfloat16* __restrict__ tab) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int groups = H / HG;
-  const int64_t g = static_cast<int64_t>(blockIdx.x) * 8 + warp;
-  if (g >= S * groups) return;
-  const int64_t s = g / groups;
-  const int h0 = static_cast<int>(g - s * groups) * HG;
-  float v[HG][4], wv[4];
-  uint32_t tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-  for (int i = 0; i < HG; ++i) load4(x + s * x_ss + (h0 + i) * x_sh + lane * 4, v[i]);
-  load4(w + lane * 4, wv);
-  load_rope_words(tab ? tab + s * 48 * 4 : nullptr, lane, tw);
-#pragma unroll
-  for (int i = 0; i < HG; ++i) {
-    const uint2 o = rmsnorm_rope_vals(v[i], wv, eps, tw, tab != nullptr, lane);
-    *reinterpret_cast<uint2*>(y + s * y_ss + (h0 + i) * y_sh + lane * 4) = o;
-  }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Sequence-parallel form: RMSNorm + RoPE of q and k fused with the token -> head exchange. The qkv rows of
-// this rank's tokens are normalised, rotated and stored straight into the buffer of the rank that owns the
-// head (its own memory or a peer's over NVLink): dst[r] is [total tokens, 3, (H/P)*128] on rank r, row0 is
-// the global index of this rank's first token. Plain stores only; ordering against the readers is the
-// caller's stream-ordered barrier. One warp per (token, head): q row, k row, v row (copied unchanged).
+// RMSNorm + RoPE alone: a half-warp per (token, head) row
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_ss, int64_t x_sh,
+                                                           __nv_bfloat16* __restrict__ y, int64_t y_ss, int64_t y_sh,
+                                                           int64_t S, int H, const __nv_bfloat16* __restrict__ w,
+                                                           float eps, const __nv_bfloat16* __restrict__ tab) {
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * HW_PER_CTA + (threadIdx.x >> 4);
+  const bool live = row < S * H;
+  const int64_t s = live ? row / H : 0;
+  const int h = live ? static_cast<int>(row - s * H) : 0;
+  NormRope nr;
+  load_norm_weight(w, l16, nr);
+  if (tab) load_rope_row(tab + s * 48 * 4, l16, nr);
+  float v[8];
+  unpack8(load_row16(x + s * x_ss + h * x_sh, l16), v);
+  norm_rope_row(v, nr, eps, tab != nullptr, lane);   // both half-warps take part in the shuffles
+  if (live) *reinterpret_cast<uint4*>(y + s * y_ss + h * y_sh + l16 * 8) = pack8(v);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sequence-parallel form: RMSNorm + RoPE of q and k fused with the token -> head exchange. The qkv rows of this
+// rank's tokens are normalised, rotated and stored straight into the buffer of the rank that owns the head (its
+// own memory or a peer's over NVLink): dst[r] is [total tokens, 3, (H/P)*128] on rank r, row0 is the global index
+// of this rank's first token. Plain stores only; ordering against the readers is the caller's stream-ordered
+// barrier. A half-warp per (token, head): q row, k row, v row (copied unchanged).
 // ---------------------------------------------------------------------------------------------
 struct ScatterDst {
   __nv_bfloat16* ptr[8];
@@ -134,176 +154,337 @@ __global__ void __launch_bounds__(256) rope_scatter_kernel(const __nv_bfloat16* 
                                                            const __nv_bfloat16* __restrict__ qw,
                                                            const __nv_bfloat16* __restrict__ kw, float eps,
                                                            const __nv_bfloat16* __restrict__ tab, const ScatterDst dst) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t g = static_cast<int64_t>(blockIdx.x) * 8 + warp;
-  if (g >= S * H) return;
-  const int64_t s = g / H;
-  const int h = static_cast<int>(g - s * H);
-  const int r = h / heads_per_rank, hh = h - r * heads_per_rank;
-  const int64_t w = static_cast<int64_t>(heads_per_rank) * D;
-  const __nv_bfloat16* row = qkv + s * ld + h * D;
-  const __nv_bfloat16* tab_row = tab ? tab + s * 48 * 4 : nullptr;
-  __nv_bfloat16* out = dst.ptr[r] + (row0 + s) * 3 * w + hh * D + lane * 4;
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const int64_t id = static_cast<int64_t>(blockIdx.x) * HW_PER_CTA + (threadIdx.x >> 4);
+  const bool live = id < S * H;
+  const int64_t s = live ? id / H : 0;
+  const int h = live ? static_cast<int>(id - s * H) : 0;
   const int64_t hd = static_cast<int64_t>(H) * D;
-  float qv[4], kv[4], qwv[4], kwv[4];
-  uint32_t tw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  load4(row + lane * 4, qv);
-  load4(row + hd + lane * 4, kv);
-  const uint2 vo = __ldg(reinterpret_cast<const uint2*>(row + 2 * hd + lane * 4));
-  load4(qw + lane * 4, qwv);
-  load4(kw + lane * 4, kwv);
-  load_rope_words(tab_row, lane, tw);  // q and k of a token share its rope words
-  const uint2 qo = rmsnorm_rope_vals(qv, qwv, eps, tw, tab_row != nullptr, lane);
-  const uint2 ko = rmsnorm_rope_vals(kv, kwv, eps, tw, tab_row != nullptr, lane);
-  *reinterpret_cast<uint2*>(out) = qo;
-  *reinterpret_cast<uint2*>(out + w) = ko;
-  *reinterpret_cast<uint2*>(out + 2 * w) = vo;
+  const __nv_bfloat16* row = qkv + s * ld + h * D;
+  NormRope nq, nk;
+  load_norm_weight(qw, l16, nq);
+  load_norm_weight(kw, l16, nk);
+  if (tab) {
+    load_rope_row(tab + s * 48 * 4, l16, nq);   // q and k of a token share its rope words
+#pragma unroll
+    for (int i = 0; i < 16; ++i) nk.t[i] = nq.t[i];
+  }
+  float q[8], k[8];
+  unpack8(load_row16(row, l16), q);
+  unpack8(load_row16(row + hd, l16), k);
+  const uint4 v = load_row16(row + 2 * hd, l16);
+  norm_rope_row(q, nq, eps, tab != nullptr, lane);
+  norm_rope_row(k, nk, eps, tab != nullptr, lane);
+  if (live) {
+    const int r = h / heads_per_rank, hh = h - r * heads_per_rank;
+    const int64_t w = static_cast<int64_t>(heads_per_rank) * D;
+    __nv_bfloat16* out = dst.ptr[r] + (row0 + s) * 3 * w + hh * D + l16 * 8;
+    *reinterpret_cast<uint4*>(out) = pack8(q);
+    *reinterpret_cast<uint4*>(out + w) = pack8(k);
+    *reinterpret_cast<uint4*>(out + 2 * w) = v;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
-// K/V statistics. Pass 1: one warp per (head, 256-token chunk), tokens in order. The partials are
-// scratch: part[(h * nchunk + c) * 4 * 128 + {ksum, vsum, vmax, vmin} * 128 + channel].
+// Launch 1 of the pre-pass. CTAs [0, q_ctas) quantize Q: one CTA = 128 tokens (two 64-token blocks) of one head, a
+// half-warp owns 8 of them, loads all 8 rows before it touches the first and keeps them as packed bf16 until the
+// block maximum is known. The other CTAs prepare K and V: one CTA = one 256-token statistics chunk of one head, a
+// half-warp owns 16 tokens and works through them four at a time (eight 16-byte loads in flight per lane). Heads
+// vary fastest, so the CTAs that share a token's rope table row run together and find it in L2.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) kv_stats_partial_kernel(const __nv_bfloat16* __restrict__ K, int64_t k_ss,
-                                                               int64_t k_sh, const __nv_bfloat16* __restrict__ V,
-                                                               int64_t v_ss, int64_t v_sh, int64_t L, int H,
-                                                               int nchunk, float* __restrict__ part) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.x * 8 + warp, c = blockIdx.y;
-  if (h >= H) return;
-  const int64_t s0 = static_cast<int64_t>(c) * STAT_CHUNK;
-  const int64_t s1 = s0 + STAT_CHUNK < L ? s0 + STAT_CHUNK : L;
-  float ks[4] = {0.f, 0.f, 0.f, 0.f}, vs[4] = {0.f, 0.f, 0.f, 0.f};
-  float vmx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, vmn[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
-  for (int64_t s = s0; s < s1; ++s) {
-    float kv[4], vv[4];
-    load4(K + s * k_ss + h * k_sh + lane * 4, kv);
-    load4(V + s * v_ss + h * v_sh + lane * 4, vv);
+struct RopeStatsParams {
+  // Q side
+  const __nv_bfloat16* q; int64_t q_ss, q_sh; int64_t Lq, Lq_pad;
+  const __nv_bfloat16* q_w;           // norm weight or null (q is already normalised / rotated)
+  __nv_bfloat16* q_out; int64_t qo_ss, qo_sh;  // optional: the normalised / rotated q as bf16 (null = not stored)
+  int8_t* q8; float* qs;
+  // K / V side
+  const __nv_bfloat16* k; int64_t k_ss, k_sh;
+  const __nv_bfloat16* k_w;           // norm weight or null
+  __nv_bfloat16* k_out; int64_t ko_ss, ko_sh;  // where the normalised / rotated k goes (may be k itself); unused if !k_w
+  const __nv_bfloat16* v; int64_t v_ss, v_sh;
+  int64_t Lk;
+  float* part;                        // [H][nchunk_k][4][128]: k sum, v sum, v max, v min
+  int nchunk_k;
+  // common
+  const __nv_bfloat16* tab;           // rope table [L][48][2][2] or null
+  float eps;
+  int H;
+  int q_ctas;
+};
+
+__global__ void __launch_bounds__(256, 2) rope_stats_kernel(const RopeStatsParams p) {
+  __shared__ float sh[HW_PER_CTA * 4 * D];  // Q side: 16 block maxima; K/V side: per half-warp partials [hw][4][128]
+  const int lane = threadIdx.x & 31, l16 = lane & 15, hw = threadIdx.x >> 4;
+  const bool q_side = static_cast<int>(blockIdx.x) < p.q_ctas;
+  const int idx = q_side ? blockIdx.x : blockIdx.x - p.q_ctas;
+  const int chunk = idx / p.H, h = idx - chunk * p.H;
+  NormRope nr;
+
+  if (q_side) {
+    // ---- Q: (norm + rope) -> rows kept as packed bf16 -> block-64 abs-max -> int8 codes ----
+    const int64_t tok0 = static_cast<int64_t>(chunk) * Q_TILE + hw * Q_TOK_PER_HW;
+    if (p.q_w) load_norm_weight(p.q_w, l16, nr);
+    uint4 kept[Q_TOK_PER_HW];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      ks[i] = __fadd_rn(ks[i], kv[i]);
-      vs[i] = __fadd_rn(vs[i], vv[i]);
-      vmx[i] = fmaxf(vmx[i], vv[i]);
-      vmn[i] = fminf(vmn[i], vv[i]);
+    for (int i = 0; i < Q_TOK_PER_HW; ++i) {
+      const int64_t s = tok0 + i < p.Lq ? tok0 + i : 0;
+      kept[i] = load_row16(p.q + s * p.q_ss + h * p.q_sh, l16);
+    }
+    float am = 0.f;
+#pragma unroll
+    for (int i = 0; i < Q_TOK_PER_HW; ++i) {
+      const int64_t s = tok0 + i;
+      const bool live = s < p.Lq;   // uniform over the half-warp
+      float v[8];
+      unpack8(kept[i], v);
+      if (p.q_w) {
+        if (p.tab) load_rope_row(p.tab + (live ? s : 0) * 48 * 4, l16, nr);
+        norm_rope_row(v, nr, p.eps, p.tab != nullptr, lane);
+        if (p.q_out && live) *reinterpret_cast<uint4*>(p.q_out + s * p.qo_ss + h * p.qo_sh + l16 * 8) = pack8(v);
+        kept[i] = pack8(v);
+      }
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(v[j]));
+      } else {
+        kept[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    am = half_warp_max(am);
+    if (l16 == 0) sh[hw] = am;
+    __syncthreads();
+    const int b8 = hw & ~7;  // the eight half-warps of this 64-token block
+    am = sh[b8];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) am = fmaxf(am, sh[b8 + i]);
+    const float scale = __fdiv_rn(fmaxf(am, 1e-8f), 127.f), inv = __fdiv_rn(1.f, scale);
+    if ((hw & 7) == 0 && l16 == 0) p.qs[static_cast<int64_t>(h) * (p.Lq_pad / 64) + chunk * 2 + (hw >> 3)] = scale;
+    int8_t* out = p.q8 + (static_cast<int64_t>(h) * p.Lq_pad + tok0) * D + l16 * 8;
+#pragma unroll
+    for (int i = 0; i < Q_TOK_PER_HW; ++i) {
+      float v[8];
+      unpack8(kept[i], v);   // rows beyond Lq hold zeros and get zero codes
+      *reinterpret_cast<uint2*>(out + i * D) = quant8_i8(v, scale, inv);
+    }
+    return;
+  }
+
+  // ---- K (norm + rope, stored once) and V: chunk partials of the stored values ----
+  const int64_t tok0 = static_cast<int64_t>(chunk) * CHUNK + hw * TOK_PER_HW;
+  if (p.k_w) load_norm_weight(p.k_w, l16, nr);
+  float ks[8], vs[8], vmx[8], vmn[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ks[j] = 0.f, vs[j] = 0.f, vmx[j] = -INFINITY, vmn[j] = INFINITY;
+#pragma unroll 1
+  for (int i0 = 0; i0 < TOK_PER_HW; i0 += 4) {
+    uint4 kraw[4], vraw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t s = tok0 + i0 + u < p.Lk ? tok0 + i0 + u : 0;
+      kraw[u] = load_row16(p.k + s * p.k_ss + h * p.k_sh, l16);
+      vraw[u] = load_row16(p.v + s * p.v_ss + h * p.v_sh, l16);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t s = tok0 + i0 + u;
+      const bool live = s < p.Lk;
+      float kv[8], vv[8];
+      unpack8(kraw[u], kv);
+      unpack8(vraw[u], vv);
+      if (p.k_w) {
+        if (p.tab) load_rope_row(p.tab + (live ? s : 0) * 48 * 4, l16, nr);
+        norm_rope_row(kv, nr, p.eps, p.tab != nullptr, lane);
+        if (live) *reinterpret_cast<uint4*>(p.k_out + s * p.ko_ss + h * p.ko_sh + l16 * 8) = pack8(kv);
+      }
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ks[j] = __fadd_rn(ks[j], kv[j]);
+          vs[j] = __fadd_rn(vs[j], vv[j]);
+          vmx[j] = fmaxf(vmx[j], vv[j]);
+          vmn[j] = fminf(vmn[j], vv[j]);
+        }
+      }
     }
   }
-  float* p = part + (static_cast<int64_t>(h) * nchunk + c) * 4 * D + lane * 4;
-  *reinterpret_cast<float4*>(p) = make_float4(ks[0], ks[1], ks[2], ks[3]);
-  *reinterpret_cast<float4*>(p + D) = make_float4(vs[0], vs[1], vs[2], vs[3]);
-  *reinterpret_cast<float4*>(p + 2 * D) = make_float4(vmx[0], vmx[1], vmx[2], vmx[3]);
-  *reinterpret_cast<float4*>(p + 3 * D) = make_float4(vmn[0], vmn[1], vmn[2], vmn[3]);
+  float* mine = sh + hw * 4 * D + l16 * 8;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    mine[j] = ks[j];
+    mine[D + j] = vs[j];
+    mine[2 * D + j] = vmx[j];
+    mine[3 * D + j] = vmn[j];
+  }
+  __syncthreads();
+  // the 16 half-warps of the chunk in order; thread t: channel t % 128, the two sums (t < 128) or the two extrema
+  const int c = threadIdx.x & 127, pair = threadIdx.x >> 7;
+  float a = pair ? -INFINITY : 0.f, b = pair ? INFINITY : 0.f;
+  for (int g = 0; g < HW_PER_CTA; ++g) {
+    const float x0 = sh[g * 4 * D + (2 * pair) * D + c], x1 = sh[g * 4 * D + (2 * pair + 1) * D + c];
+    a = pair ? fmaxf(a, x0) : __fadd_rn(a, x0);
+    b = pair ? fminf(b, x1) : __fadd_rn(b, x1);
+  }
+  float* out = p.part + (static_cast<int64_t>(h) * p.nchunk_k + chunk) * 4 * D;
+  out[(2 * pair) * D + c] = a;
+  out[(2 * pair + 1) * D + c] = b;
 }
 
-// Pass 2: one thread per (head, channel), chunks in order.
+// ---------------------------------------------------------------------------------------------
+// Launch 2: chunk partials -> K mean, V mean, V scale. A thread per (head, channel) walks the chunks in order.
+// ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) kv_stats_final_kernel(const float* __restrict__ part, int nchunk, int64_t L,
                                                              float* __restrict__ kmean, float* __restrict__ vmean,
                                                              float* __restrict__ vscale) {
-  const int h = blockIdx.x, d = threadIdx.x;
-  const float* p = part + static_cast<int64_t>(h) * nchunk * 4 * D + d;
-  float ks = 0.f, vs = 0.f, vmx = -INFINITY, vmn = INFINITY;
-  for (int c = 0; c < nchunk; ++c) {
-    ks = __fadd_rn(ks, p[0]);
-    vs = __fadd_rn(vs, p[D]);
-    vmx = fmaxf(vmx, p[2 * D]);
-    vmn = fminf(vmn, p[3 * D]);
-    p += 4 * D;
+  const int h = blockIdx.x, c = threadIdx.x;
+  const float* p = part + static_cast<int64_t>(h) * nchunk * 4 * D + c;
+  float ksum = 0.f, vsum = 0.f, vhi = -INFINITY, vlo = INFINITY;
+  for (int i = 0; i < nchunk; ++i, p += 4 * D) {
+    ksum = __fadd_rn(ksum, p[0]);
+    vsum = __fadd_rn(vsum, p[D]);
+    vhi = fmaxf(vhi, p[2 * D]);
+    vlo = fminf(vlo, p[3 * D]);
   }
-  const float fl = static_cast<float>(L);
-  const float km = __fdiv_rn(ks, fl), vm = __fdiv_rn(vs, fl);
-  kmean[h * D + d] = km;
-  vmean[h * D + d] = vm;
-  const float am = fmaxf(__fsub_rn(vmx, vm), __fsub_rn(vm, vmn));
-  vscale[h * D + d] = __fdiv_rn(fmaxf(am, 1e-8f), 448.f);
+  const float n = static_cast<float>(L);
+  const float mk = __fdiv_rn(ksum, n), mv = __fdiv_rn(vsum, n);
+  kmean[h * D + c] = mk;
+  vmean[h * D + c] = mv;
+  // largest |v - mean| from the two extrema (the subtraction is monotonic, so this is the abs-max of v - mean)
+  vscale[h * D + c] = __fdiv_rn(fmaxf(fmaxf(__fsub_rn(vhi, mv), __fsub_rn(mv, vlo)), 1e-8f), 448.f);
 }
 
 // ---------------------------------------------------------------------------------------------
-// Q/K block-64 int8. One CTA per (64-token block, head); 8 warps x 8 tokens, lane = 4 channels.
+// Launch 3. One CTA = one 128-token tile of one head (the key tile of the attention kernel); half-warp hw owns
+// tokens 8*hw .. 8*hw+7. K: minus the channel mean, block-64 abs-max, int8 codes. V: e4m3 codes of
+// (v - mean) / scale written row-major into a 16 KB shared tile and read back by channel, 32 keys (two 16-byte
+// stores, one full 32-byte sector) at a time.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) quant_block64_kernel(const __nv_bfloat16* __restrict__ X, int64_t x_ss,
-                                                            int64_t x_sh, int64_t L, int64_t Lpad,
-                                                            const float* __restrict__ mean,  // [H][128] or null
-                                                            int8_t* __restrict__ out, float* __restrict__ scales) {
-  __shared__ float red[8];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+template <bool DO_K, bool DO_V>
+__global__ void __launch_bounds__(256, 3) quant_kv_kernel(const __nv_bfloat16* __restrict__ K, int64_t k_ss, int64_t k_sh,
+                                                       const __nv_bfloat16* __restrict__ V, int64_t v_ss, int64_t v_sh,
+                                                       int64_t L, int64_t Lpad, const float* __restrict__ kmean,
+                                                       const float* __restrict__ vmean, const float* __restrict__ vscale,
+                                                       int8_t* __restrict__ k8, float* __restrict__ kscale,
+                                                       uint8_t* __restrict__ Vt) {
+  __shared__ __align__(16) uint8_t tile[DO_V ? 128 * D : 16];
+  __shared__ float red[HW_PER_CTA];
+  const int l16 = threadIdx.x & 15, hw = threadIdx.x >> 4;
   const int h = blockIdx.y;
-  const int64_t blk = blockIdx.x;
-  float m[4] = {0.f, 0.f, 0.f, 0.f};
-  if (mean) {
-    const float4 mm = *reinterpret_cast<const float4*>(mean + h * D + lane * 4);
-    m[0] = mm.x; m[1] = mm.y; m[2] = mm.z; m[3] = mm.w;
-  }
-  float v[8][4];
-  float am = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int64_t s = blk * 64 + warp * 8 + i;
-    if (s < L) {
-      load4(X + s * x_ss + h * x_sh + lane * 4, v[i]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        v[i][j] = __fsub_rn(v[i][j], m[j]);
-        am = fmaxf(am, fabsf(v[i][j]));
-      }
-    } else {
-      v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
-    }
-  }
-  am = warp_max(am);
-  if (lane == 0) red[warp] = am;
-  __syncthreads();
-  am = red[0];
-#pragma unroll
-  for (int w = 1; w < 8; ++w) am = fmaxf(am, red[w]);
-  const float sc = __fdiv_rn(fmaxf(am, 1e-8f), 127.f);
-  const float inv = __fdiv_rn(1.f, sc);
-  if (threadIdx.x == 0) scales[static_cast<int64_t>(h) * (Lpad / 64) + blk] = sc;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int64_t s = blk * 64 + warp * 8 + i;
-    const uint32_t packed = pack_low_bytes(quant_code_i8(v[i][0], sc, inv), quant_code_i8(v[i][1], sc, inv),
-                                           quant_code_i8(v[i][2], sc, inv), quant_code_i8(v[i][3], sc, inv));
-    *reinterpret_cast<uint32_t*>(out + (static_cast<int64_t>(h) * Lpad + s) * D + lane * 4) = packed;
-  }
-}
+  const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * 128, tok0 = tile0 + hw * 8;
 
-// ---------------------------------------------------------------------------------------------
-// V -> e4m3, transposed. One CTA per (128-token tile, head).
-// ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) quant_v_kernel(const __nv_bfloat16* __restrict__ V, int64_t v_ss, int64_t v_sh,
-                                                      int64_t L, int64_t Lpad, const float* __restrict__ vmean,
-                                                      const float* __restrict__ vscale, uint8_t* __restrict__ Vt) {
-  constexpr int T = 128, P = D + 4;  // tile[token][channel], padded rows
-  __shared__ uint8_t tile[T * P];
-  const int h = blockIdx.y, tid = threadIdx.x;
-  const int64_t s0 = static_cast<int64_t>(blockIdx.x) * T;
-  for (int i = tid; i < T * (D / 4); i += 256) {
-    const int r = i / (D / 4), c4 = (i % (D / 4)) * 4;
-    const int64_t s = s0 + r;
-    uint32_t packed = 0;
-    if (s < L) {
-      float x[4];
-      load4(V + s * v_ss + h * v_sh + c4, x);
-      const float4 m = *reinterpret_cast<const float4*>(vmean + h * D + c4);
-      const float4 sc = *reinterpret_cast<const float4*>(vscale + h * D + c4);
-      const float mm[4] = {m.x, m.y, m.z, m.w}, ss[4] = {sc.x, sc.y, sc.z, sc.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        packed |= quant_code_e4m3(__fsub_rn(x[j], mm[j]), ss[j], __fdiv_rn(1.f, ss[j])) << (8 * j);
+  if (DO_K) {
+    float mean[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (kmean) {
+      const float4 m0 = *reinterpret_cast<const float4*>(kmean + h * D + l16 * 8);
+      const float4 m1 = *reinterpret_cast<const float4*>(kmean + h * D + l16 * 8 + 4);
+      mean[0] = m0.x, mean[1] = m0.y, mean[2] = m0.z, mean[3] = m0.w;
+      mean[4] = m1.x, mean[5] = m1.y, mean[6] = m1.z, mean[7] = m1.w;
     }
-    *reinterpret_cast<uint32_t*>(&tile[r * P + c4]) = packed;
-  }
-  __syncthreads();
-  // write: channel d, 16 consecutive tokens per 16-byte store
-  for (int i = tid; i < D * (T / 16); i += 256) {
-    const int d = i / (T / 16), cc = (i % (T / 16)) * 16;
-    alignas(16) uint8_t o[16];
+    uint4 kept[8];
+    float am = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) o[j] = tile[(cc + j) * P + d];
-    *reinterpret_cast<uint4*>(Vt + (static_cast<int64_t>(h) * D + d) * Lpad + s0 + cc) = *reinterpret_cast<uint4*>(o);
+    for (int i = 0; i < 8; ++i) {
+      const bool live = tok0 + i < L;
+      kept[i] = live ? load_row16(K + (tok0 + i) * k_ss + h * k_sh, l16) : make_uint4(0, 0, 0, 0);
+      if (live) {
+        float v[8];
+        unpack8(kept[i], v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(__fsub_rn(v[j], mean[j])));
+      }
+    }
+    am = half_warp_max(am);
+    if (l16 == 0) red[hw] = am;
+    __syncthreads();
+    const int b8 = hw & ~7;  // the eight half-warps of this 64-token block
+    am = red[b8];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) am = fmaxf(am, red[b8 + i]);
+    const float scale = __fdiv_rn(fmaxf(am, 1e-8f), 127.f), inv = __fdiv_rn(1.f, scale);
+    if ((hw & 7) == 0 && l16 == 0) kscale[static_cast<int64_t>(h) * (Lpad / 64) + blockIdx.x * 2 + (hw >> 3)] = scale;
+    int8_t* out = k8 + (static_cast<int64_t>(h) * Lpad + tok0) * D + l16 * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v[8];
+      unpack8(kept[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __fsub_rn(v[j], mean[j]);
+      // rows beyond L get zero codes (their mean must not be subtracted)
+      *reinterpret_cast<uint2*>(out + i * D) = tok0 + i < L ? quant8_i8(v, scale, inv) : make_uint2(0, 0);
+    }
+  }
+
+  if (DO_V) {
+    float mean[8], sc[8], inv[8];
+    {
+      const float4 m0 = *reinterpret_cast<const float4*>(vmean + h * D + l16 * 8);
+      const float4 m1 = *reinterpret_cast<const float4*>(vmean + h * D + l16 * 8 + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(vscale + h * D + l16 * 8);
+      const float4 s1 = *reinterpret_cast<const float4*>(vscale + h * D + l16 * 8 + 4);
+      mean[0] = m0.x, mean[1] = m0.y, mean[2] = m0.z, mean[3] = m0.w;
+      mean[4] = m1.x, mean[5] = m1.y, mean[6] = m1.z, mean[7] = m1.w;
+      sc[0] = s0.x, sc[1] = s0.y, sc[2] = s0.z, sc[3] = s0.w;
+      sc[4] = s1.x, sc[5] = s1.y, sc[6] = s1.z, sc[7] = s1.w;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) inv[j] = __fdiv_rn(1.f, sc[j]);
+    }
+    uint4 raw[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) raw[i] = load_row16(V + (tok0 + i < L ? tok0 + i : 0) * v_ss + h * v_sh, l16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v[8];
+      unpack8(raw[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __fsub_rn(v[j], mean[j]);
+      *reinterpret_cast<uint2*>(tile + (hw * 8 + i) * D + l16 * 8) =
+          tok0 + i < L ? quant8_e4m3_per_channel(v, sc, inv) : make_uint2(0, 0);
+    }
+    __syncthreads();
+    // item = (channel d, group of 32 keys): consecutive threads take consecutive channels, so one load instruction
+    // reads 32 consecutive bytes of one token row (no bank conflict) and every thread stores a full 32-byte sector
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep) {
+      const int item = threadIdx.x + rep * 256, d = item & 127, grp = item >> 7;
+      uint32_t w[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const uint8_t* src = tile + (grp * 32 + q * 4) * D + d;
+        w[q] = static_cast<uint32_t>(src[0]) | (static_cast<uint32_t>(src[D]) << 8) |
+               (static_cast<uint32_t>(src[2 * D]) << 16) | (static_cast<uint32_t>(src[3 * D]) << 24);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(Vt + (static_cast<int64_t>(h) * D + d) * Lpad + tile0 + grp * 32);
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
   }
 }
 
 bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+bool strides16(int64_t a, int64_t b) { return a % 8 == 0 && b % 8 == 0; }  // rows start on 16-byte boundaries
+
+int launch_rope_stats(const RopeStatsParams& p, int kv_ctas, cudaStream_t stream) {
+  const int64_t ctas = static_cast<int64_t>(p.q_ctas) + kv_ctas;
+  if (ctas == 0) return 0;
+  RH3_CHECK_ARG(ctas < (1ll << 31), "attention pre-pass: too many tokens x heads");
+  rope_stats_kernel<<<static_cast<unsigned>(ctas), 256, 0, stream>>>(p);
+  return check_cuda(cudaGetLastError(), "attention pre-pass (rope / statistics) launch");
+}
+
+int kv_stats_run(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t L,
+                 int64_t H, float* part, float* kmean, float* vmean, float* vscale, cudaStream_t stream,
+                 const char* who) {
+  const int64_t nchunk = (L + CHUNK - 1) / CHUNK;
+  RH3_CHECK_ARG(nchunk * H < (1ll << 31), "%s: L x H too large", who);
+  RopeStatsParams p{};
+  p.k = static_cast<const __nv_bfloat16*>(k); p.k_ss = k_ss; p.k_sh = k_sh;
+  p.v = static_cast<const __nv_bfloat16*>(v); p.v_ss = v_ss; p.v_sh = v_sh;
+  p.Lk = L; p.part = part; p.nchunk_k = static_cast<int>(nchunk); p.H = static_cast<int>(H);
+  if (int e = launch_rope_stats(p, static_cast<int>(nchunk * H), stream)) return e;
+  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(part, static_cast<int>(nchunk), L, kmean, vmean,
+                                                                      vscale);
+  return check_cuda(cudaGetLastError(), "attention pre-pass (statistics) launch");
+}
 
 }  // namespace
 }  // namespace rh3
@@ -316,20 +497,14 @@ extern "C" int rh3_rmsnorm_rope3d(const void* x, int64_t x_ss, int64_t x_sh, voi
   RH3_CHECK_ARG(S >= 0 && H > 0 && H < 65536, "rmsnorm_rope3d: bad shape S=%lld H=%lld", (long long)S, (long long)H);
   if (S == 0) return 0;
   RH3_CHECK_ARG(x && y && weight, "rmsnorm_rope3d: null pointer");
-  RH3_CHECK_ARG(aligned(x, 8) && aligned(y, 8) && aligned(weight, 8) && x_ss % 4 == 0 && x_sh % 4 == 0 &&
-                    y_ss % 4 == 0 && y_sh % 4 == 0,
-                "rmsnorm_rope3d: rows must be 8-byte aligned (strides multiples of 4 elements)");
+  RH3_CHECK_ARG(aligned(x, 16) && aligned(y, 16) && aligned(weight, 16) && strides16(x_ss, x_sh) && strides16(y_ss, y_sh),
+                "rmsnorm_rope3d: rows must be 16-byte aligned (strides multiples of 8 elements)");
   RH3_CHECK_ARG(!rope_table || aligned(rope_table, 16), "rmsnorm_rope3d: rope table must be 16-byte aligned");
-  const int hg = H % 4 == 0 ? 4 : 1;
-  const int64_t warps = S * (H / hg);
-  RH3_CHECK_ARG((warps + 7) / 8 < (1ll << 31), "rmsnorm_rope3d: too many rows");
-  const unsigned grid = static_cast<unsigned>((warps + 7) / 8);
-  const auto* xp = static_cast<const __nv_bfloat16*>(x);
-  auto* yp = static_cast<__nv_bfloat16*>(y);
-  const auto* wp = static_cast<const __nv_bfloat16*>(weight);
-  const auto* tp = static_cast<const __nv_bfloat16*>(rope_table);
-  if (hg == 4) rmsnorm_rope_kernel<4><<<grid, 256, 0, stream>>>(xp, x_ss, x_sh, yp, y_ss, y_sh, S, (int)H, wp, eps, tp);
-  else rmsnorm_rope_kernel<1><<<grid, 256, 0, stream>>>(xp, x_ss, x_sh, yp, y_ss, y_sh, S, (int)H, wp, eps, tp);
+  const int64_t rows = S * H;
+  RH3_CHECK_ARG((rows + HW_PER_CTA - 1) / HW_PER_CTA < (1ll << 31), "rmsnorm_rope3d: too many rows");
+  rmsnorm_rope_kernel<<<static_cast<unsigned>((rows + HW_PER_CTA - 1) / HW_PER_CTA), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), x_ss, x_sh, static_cast<__nv_bfloat16*>(y), y_ss, y_sh, S, (int)H,
+      static_cast<const __nv_bfloat16*>(weight), eps, static_cast<const __nv_bfloat16*>(rope_table));
   return check_cuda(cudaGetLastError(), "rmsnorm_rope3d launch");
 }
 
@@ -340,17 +515,17 @@ extern "C" int rh3_rope_scatter_heads(const void* qkv, int64_t ld, int64_t S, in
                 "rope_scatter_heads: bad shape S=%lld H=%lld P=%lld", (long long)S, (long long)H, (long long)P);
   if (S == 0) return 0;
   RH3_CHECK_ARG(qkv && q_weight && k_weight && dst, "rope_scatter_heads: null pointer");
-  RH3_CHECK_ARG(aligned(qkv, 8) && aligned(q_weight, 8) && aligned(k_weight, 8) && ld % 4 == 0 && ld >= 3 * H * D,
-                "rope_scatter_heads: rows must be 8-byte aligned and hold q | k | v");
+  RH3_CHECK_ARG(aligned(qkv, 16) && aligned(q_weight, 16) && aligned(k_weight, 16) && ld % 8 == 0 && ld >= 3 * H * D,
+                "rope_scatter_heads: rows must be 16-byte aligned and hold q | k | v");
   RH3_CHECK_ARG(!rope_table || aligned(rope_table, 16), "rope_scatter_heads: rope table must be 16-byte aligned");
   ScatterDst d{};
   for (int r = 0; r < P; ++r) {
-    RH3_CHECK_ARG(dst[r] && aligned(dst[r], 8), "rope_scatter_heads: destination %d is null or misaligned", r);
+    RH3_CHECK_ARG(dst[r] && aligned(dst[r], 16), "rope_scatter_heads: destination %d is null or misaligned", r);
     d.ptr[r] = static_cast<__nv_bfloat16*>(dst[r]);
   }
   const int64_t rows = S * H;
-  RH3_CHECK_ARG((rows + 7) / 8 < (1ll << 31), "rope_scatter_heads: too many rows");
-  rope_scatter_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
+  RH3_CHECK_ARG((rows + HW_PER_CTA - 1) / HW_PER_CTA < (1ll << 31), "rope_scatter_heads: too many rows");
+  rope_scatter_kernel<<<static_cast<unsigned>((rows + HW_PER_CTA - 1) / HW_PER_CTA), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(qkv), ld, S, (int)H, (int)(H / P), row0,
       static_cast<const __nv_bfloat16*>(q_weight), static_cast<const __nv_bfloat16*>(k_weight), eps,
       static_cast<const __nv_bfloat16*>(rope_table), d);
@@ -358,7 +533,7 @@ extern "C" int rh3_rope_scatter_heads(const void* qkv, int64_t ld, int64_t S, in
 }
 
 extern "C" int64_t rh3_attn_kv_stats_scratch_bytes(int64_t L, int64_t H) {
-  const int64_t nchunk = (L + STAT_CHUNK - 1) / STAT_CHUNK;
+  const int64_t nchunk = (L + CHUNK - 1) / CHUNK;
   return H * nchunk * 4 * D * static_cast<int64_t>(sizeof(float));
 }
 
@@ -369,18 +544,10 @@ extern "C" int rh3_attn_kv_stats(const void* k, int64_t k_ss, int64_t k_sh, cons
   RH3_CHECK_ARG(k && v && scratch && kmean && vmean && vscale, "attn_kv_stats: null pointer");
   RH3_CHECK_ARG(scratch_bytes >= rh3_attn_kv_stats_scratch_bytes(L, H), "attn_kv_stats: scratch too small (%lld < %lld)",
                 (long long)scratch_bytes, (long long)rh3_attn_kv_stats_scratch_bytes(L, H));
-  RH3_CHECK_ARG(aligned(k, 8) && aligned(v, 8) && aligned(scratch, 16) && k_ss % 4 == 0 && k_sh % 4 == 0 &&
-                    v_ss % 4 == 0 && v_sh % 4 == 0,
-                "attn_kv_stats: misaligned input");
-  const int nchunk = static_cast<int>((L + STAT_CHUNK - 1) / STAT_CHUNK);
-  RH3_CHECK_ARG(nchunk < 65536, "attn_kv_stats: L too large");
-  kv_stats_partial_kernel<<<dim3(static_cast<unsigned>((H + 7) / 8), nchunk), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(k), k_ss, k_sh, static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, L, (int)H,
-      nchunk, static_cast<float*>(scratch));
-  if (int e = check_cuda(cudaGetLastError(), "attn_kv_stats partial launch")) return e;
-  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(static_cast<const float*>(scratch), nchunk, L,
-                                                                      kmean, vmean, vscale);
-  return check_cuda(cudaGetLastError(), "attn_kv_stats final launch");
+  RH3_CHECK_ARG(aligned(k, 16) && aligned(v, 16) && aligned(scratch, 16) && strides16(k_ss, k_sh) && strides16(v_ss, v_sh),
+                "attn_kv_stats: rows must be 16-byte aligned (strides multiples of 8 elements)");
+  return kv_stats_run(k, k_ss, k_sh, v, v_ss, v_sh, L, H, static_cast<float*>(scratch), kmean, vmean, vscale, stream,
+                      "attn_kv_stats");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -425,25 +592,19 @@ extern "C" int rh3_attn_kv_stats_noalloc(const void* k, int64_t k_ss, int64_t k_
                                          float* vscale, cudaStream_t stream) {
   RH3_CHECK_ARG(L > 0 && H > 0 && H < 65536, "attn_kv_stats_noalloc: bad shape L=%lld H=%lld", (long long)L,
                 (long long)H);
-  const int64_t nchunk64 = (L + STAT_CHUNK - 1) / STAT_CHUNK;
-  RH3_CHECK_ARG(H * nchunk64 <= KV_STATS_NOALLOC_MAX_UNITS,
+  const int64_t nchunk = (L + CHUNK - 1) / CHUNK;
+  RH3_CHECK_ARG(H * nchunk <= KV_STATS_NOALLOC_MAX_UNITS,
                 "attn_kv_stats_noalloc: H * ceil(L/256) = %lld exceeds the built-in scratch limit of %lld; "
                 "use rh3_attn_kv_stats with caller-provided scratch",
-                (long long)(H * nchunk64), (long long)KV_STATS_NOALLOC_MAX_UNITS);
+                (long long)(H * nchunk), (long long)KV_STATS_NOALLOC_MAX_UNITS);
   RH3_CHECK_ARG(k && v && kmean && vmean && vscale, "attn_kv_stats_noalloc: null pointer");
-  RH3_CHECK_ARG(aligned(k, 8) && aligned(v, 8) && k_ss % 4 == 0 && k_sh % 4 == 0 && v_ss % 4 == 0 && v_sh % 4 == 0,
-                "attn_kv_stats_noalloc: misaligned input");
+  RH3_CHECK_ARG(aligned(k, 16) && aligned(v, 16) && strides16(k_ss, k_sh) && strides16(v_ss, v_sh),
+                "attn_kv_stats_noalloc: rows must be 16-byte aligned (strides multiples of 8 elements)");
   float* scratch = nullptr;
   if (int e = kv_stats_scratch_address(&scratch)) return e;
-  const int nchunk = static_cast<int>(nchunk64);
   // every partial that the second kernel reads is written by the first one in this call, so nothing
   // left over from an earlier call needs clearing
-  kv_stats_partial_kernel<<<dim3(static_cast<unsigned>((H + 7) / 8), nchunk), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(k), k_ss, k_sh, static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, L, (int)H,
-      nchunk, scratch);
-  if (int e = check_cuda(cudaGetLastError(), "attn_kv_stats_noalloc partial launch")) return e;
-  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(scratch, nchunk, L, kmean, vmean, vscale);
-  return check_cuda(cudaGetLastError(), "attn_kv_stats_noalloc final launch");
+  return kv_stats_run(k, k_ss, k_sh, v, v_ss, v_sh, L, H, scratch, kmean, vmean, vscale, stream, "attn_kv_stats_noalloc");
 }
 
 extern "C" int rh3_attn_quant_qk(const void* x, int64_t x_ss, int64_t x_sh, int64_t L, int64_t Lpad, int64_t H,
@@ -452,10 +613,12 @@ extern "C" int rh3_attn_quant_qk(const void* x, int64_t x_ss, int64_t x_sh, int6
                 "attn_quant_qk: bad shape L=%lld Lpad=%lld H=%lld (Lpad must be a multiple of 128)", (long long)L,
                 (long long)Lpad, (long long)H);
   RH3_CHECK_ARG(x && codes && scales, "attn_quant_qk: null pointer");
-  RH3_CHECK_ARG(aligned(x, 8) && aligned(codes, 16) && x_ss % 4 == 0 && x_sh % 4 == 0 && (!mean || aligned(mean, 16)),
-                "attn_quant_qk: misaligned input");
-  quant_block64_kernel<<<dim3(static_cast<unsigned>(Lpad / 64), static_cast<unsigned>(H)), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), x_ss, x_sh, L, Lpad, mean, static_cast<int8_t*>(codes), scales);
+  RH3_CHECK_ARG(aligned(x, 16) && aligned(codes, 16) && strides16(x_ss, x_sh) && (!mean || aligned(mean, 16)),
+                "attn_quant_qk: rows must be 16-byte aligned (strides multiples of 8 elements)");
+  RH3_CHECK_ARG(Lpad / 128 < (1ll << 31), "attn_quant_qk: L too large");
+  quant_kv_kernel<true, false><<<dim3(static_cast<unsigned>(Lpad / 128), static_cast<unsigned>(H)), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), x_ss, x_sh, nullptr, 0, 0, L, Lpad, mean, nullptr, nullptr,
+      static_cast<int8_t*>(codes), scales, nullptr);
   return check_cuda(cudaGetLastError(), "attn_quant_qk launch");
 }
 
@@ -465,10 +628,64 @@ extern "C" int rh3_attn_quant_v(const void* v, int64_t v_ss, int64_t v_sh, int64
                 "attn_quant_v: bad shape L=%lld Lpad=%lld H=%lld (Lpad must be a multiple of 128)", (long long)L,
                 (long long)Lpad, (long long)H);
   RH3_CHECK_ARG(v && vmean && vscale && vt, "attn_quant_v: null pointer");
-  RH3_CHECK_ARG(aligned(v, 8) && aligned(vt, 16) && aligned(vmean, 16) && aligned(vscale, 16) && v_ss % 4 == 0 &&
-                    v_sh % 4 == 0,
-                "attn_quant_v: misaligned input");
-  quant_v_kernel<<<dim3(static_cast<unsigned>(Lpad / 128), static_cast<unsigned>(H)), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, L, Lpad, vmean, vscale, static_cast<uint8_t*>(vt));
+  RH3_CHECK_ARG(aligned(v, 16) && aligned(vt, 16) && aligned(vmean, 16) && aligned(vscale, 16) && strides16(v_ss, v_sh),
+                "attn_quant_v: rows must be 16-byte aligned (strides multiples of 8 elements)");
+  quant_kv_kernel<false, true><<<dim3(static_cast<unsigned>(Lpad / 128), static_cast<unsigned>(H)), 256, 0, stream>>>(
+      nullptr, 0, 0, static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, L, Lpad, nullptr, vmean, vscale, nullptr, nullptr,
+      static_cast<uint8_t*>(vt));
   return check_cuda(cudaGetLastError(), "attn_quant_v launch");
+}
+
+// The whole pre-pass of one attention call (see the head of this file): three launches.
+extern "C" int rh3_attn_prepass(const void* q, int64_t q_ss, int64_t q_sh, int64_t Lq, int64_t Lq_pad, const void* k,
+                                int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t Lk,
+                                int64_t Lk_pad, int64_t H, const void* q_weight, const void* k_weight, float eps,
+                                const void* rope_table, void* q_roped, int64_t qr_ss, int64_t qr_sh, void* k_roped,
+                                int64_t kr_ss, int64_t kr_sh, void* scratch, int64_t scratch_bytes, void* q8, float* qs,
+                                void* k8, float* ks, void* vt, float* vscale, float* vmean, float* kmean,
+                                cudaStream_t stream) {
+  RH3_CHECK_ARG(Lq > 0 && Lk > 0 && H > 0 && H < 65536, "attn_prepass: bad shape Lq=%lld Lk=%lld H=%lld", (long long)Lq,
+                (long long)Lk, (long long)H);
+  RH3_CHECK_ARG(Lq_pad >= Lq && Lq_pad % 256 == 0 && Lk_pad >= Lk && Lk_pad % 128 == 0,
+                "attn_prepass: Lq_pad must be a multiple of 256 and Lk_pad a multiple of 128, covering Lq / Lk");
+  RH3_CHECK_ARG(q && k && v && scratch && q8 && qs && k8 && ks && vt && vscale && vmean && kmean,
+                "attn_prepass: null pointer");
+  RH3_CHECK_ARG((q_weight == nullptr) == (k_weight == nullptr), "attn_prepass: q and k norm weights come together");
+  RH3_CHECK_ARG(!rope_table || (q_weight && Lq == Lk), "attn_prepass: a rope table needs the norm weights and Lq == Lk");
+  RH3_CHECK_ARG(!k_weight || k_roped, "attn_prepass: the normalised k needs a place to go (k_roped; it may be k itself)");
+  RH3_CHECK_ARG(aligned(q, 16) && aligned(k, 16) && aligned(v, 16) && strides16(q_ss, q_sh) && strides16(k_ss, k_sh) &&
+                    strides16(v_ss, v_sh) && (!q_roped || (aligned(q_roped, 16) && strides16(qr_ss, qr_sh))) &&
+                    (!k_roped || (aligned(k_roped, 16) && strides16(kr_ss, kr_sh))),
+                "attn_prepass: rows must be 16-byte aligned (strides multiples of 8 elements)");
+  RH3_CHECK_ARG(aligned(scratch, 16) && aligned(q8, 16) && aligned(k8, 16) && aligned(vt, 16) && aligned(vscale, 16) &&
+                    aligned(vmean, 16) && aligned(kmean, 16) &&
+                    (!q_weight || (aligned(q_weight, 16) && aligned(k_weight, 16))) &&
+                    (!rope_table || aligned(rope_table, 16)),
+                "attn_prepass: operand buffers, weights and the rope table must be 16-byte aligned");
+  RH3_CHECK_ARG(scratch_bytes >= rh3_attn_kv_stats_scratch_bytes(Lk, H), "attn_prepass: scratch too small (%lld < %lld)",
+                (long long)scratch_bytes, (long long)rh3_attn_kv_stats_scratch_bytes(Lk, H));
+  const int64_t nchunk_k = (Lk + CHUNK - 1) / CHUNK, nchunk_q = Lq_pad / Q_TILE;
+  RH3_CHECK_ARG((nchunk_k + nchunk_q) * H < (1ll << 31) && Lk_pad / 128 < (1ll << 31), "attn_prepass: L x H too large");
+  RopeStatsParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q); p.q_ss = q_ss; p.q_sh = q_sh; p.Lq = Lq; p.Lq_pad = Lq_pad;
+  p.q_w = static_cast<const __nv_bfloat16*>(q_weight);
+  p.q_out = static_cast<__nv_bfloat16*>(q_roped); p.qo_ss = qr_ss; p.qo_sh = qr_sh;
+  p.q8 = static_cast<int8_t*>(q8); p.qs = qs;
+  p.k = static_cast<const __nv_bfloat16*>(k); p.k_ss = k_ss; p.k_sh = k_sh;
+  p.k_w = static_cast<const __nv_bfloat16*>(k_weight);
+  p.k_out = static_cast<__nv_bfloat16*>(k_roped); p.ko_ss = kr_ss; p.ko_sh = kr_sh;
+  p.v = static_cast<const __nv_bfloat16*>(v); p.v_ss = v_ss; p.v_sh = v_sh;
+  p.Lk = Lk; p.part = static_cast<float*>(scratch); p.nchunk_k = static_cast<int>(nchunk_k);
+  p.tab = static_cast<const __nv_bfloat16*>(rope_table); p.eps = eps; p.H = static_cast<int>(H);
+  p.q_ctas = static_cast<int>(nchunk_q * H);
+  if (int e = launch_rope_stats(p, static_cast<int>(nchunk_k * H), stream)) return e;
+  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(p.part, p.nchunk_k, Lk, kmean, vmean, vscale);
+  if (int e = check_cuda(cudaGetLastError(), "attn_prepass statistics launch")) return e;
+  // K is read where the first launch left it: the normalised copy when there is one
+  const __nv_bfloat16* kq = k_weight ? static_cast<const __nv_bfloat16*>(k_roped) : static_cast<const __nv_bfloat16*>(k);
+  const int64_t kq_ss = k_weight ? kr_ss : k_ss, kq_sh = k_weight ? kr_sh : k_sh;
+  quant_kv_kernel<true, true><<<dim3(static_cast<unsigned>(Lk_pad / 128), static_cast<unsigned>(H)), 256, 0, stream>>>(
+      kq, kq_ss, kq_sh, static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, Lk, Lk_pad, kmean, vmean, vscale,
+      static_cast<int8_t*>(k8), ks, static_cast<uint8_t*>(vt));
+  return check_cuda(cudaGetLastError(), "attn_prepass quantizer launch");
 }

@@ -511,6 +511,29 @@ __device__ __forceinline__ uint2 quant8_e4m3(const float* y, float s, float inv)
   }
   return make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
 }
+// The same for eight values that each have their own scale (a row of V against per-channel scales).
+__device__ __forceinline__ uint2 quant8_e4m3_per_channel(const float* y, const float* s, const float* inv) {
+  float yq[8];
+  bool near = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    yq[j] = __fmul_rn(y[j], inv[j]);
+    const uint32_t drop = __float_as_uint(yq[j]) & 0xFFFFFu;
+    near |= (fabsf(yq[j]) < 0.015625f) | ((drop - 0x7FFF0u) < 0x20u);
+  }
+  if (near) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) yq[j] = __fdiv_rn(y[j], s[j]);
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint16_t h;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(h) : "f"(yq[2 * j]), "f"(yq[2 * j + 1]));
+    w[j] = h;
+  }
+  return make_uint2(w[0] | (w[1] << 16), w[2] | (w[3] << 16));
+}
 // pack the low bytes of four words into one word (a -> byte 0 ... d -> byte 3)
 __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);

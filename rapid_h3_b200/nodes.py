@@ -171,6 +171,10 @@ class FusedBlock:
             self.fc1_q.qweight = qw
         return qw.q, qw.scale
 
+    @staticmethod
+    def _eps_mismatch():
+        raise NotImplementedError("the fused attention pre-pass needs q_norm and k_norm to share eps")
+
     def _zeros_tab(self, d, device):
         key = ("zeros", d, str(device))
         if key not in self._const:
@@ -242,16 +246,21 @@ class FusedBlock:
             with _phase("quant_attn_out", qbytes(hd)):
                 oq, os_ = tq.quant_groups_i8(o, rotate=rot)
         else:
-            with _phase("rms_rope", s * hd * 2 * 2 * 2):
-                attn_int8.rms_rope(q, self._norm_w(a.q_norm), a.q_norm.eps, tab, out=q)
-                attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
-            rec("qkv_rr", qkv)
             if sp is None:
-                o = attn_int8.attention(q, k, v, _tag="self")          # [S, H, 128] token-major
-                rec("attn_out", o)
+                # RMSNorm + RoPE of q and k run inside the attention pre-pass: q is quantized from registers, the
+                # normalised k replaces the raw one in the qkv buffer (nothing reads the raw values afterwards);
+                # when a trace is asked for, the normalised q is stored too
+                o = attn_int8.attention_rr(q, k, v, tab, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps
+                                           if a.q_norm.eps == a.k_norm.eps else self._eps_mismatch(),
+                                           q_roped=q if trace is not None else None, k_roped=k, _tag="self")
+                rec("qkv_rr", qkv)
+                rec("attn_out", o)                                     # [S, H, 128] token-major
                 with _phase("quant_attn_out", qbytes(hd)):
                     oq, os_ = tq.rot_quant_rows_i8(o.view(s, hd), rotate=rot)
             else:
+                with _phase("rms_rope", s * hd * 2 * 2 * 2):
+                    attn_int8.rms_rope(q, self._norm_w(a.q_norm), a.q_norm.eps, tab, out=q)
+                    attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
                 with _phase("exchange_all_to_all"):
                     qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
                 og = attn_int8.attention(qg, kg, vg, _tag="self")
@@ -280,11 +289,11 @@ class FusedBlock:
                 qw = self.ckv_q.qweight_for()
                 kv = cf.int8_gemm(cq8, cs, qw.q, qw.scale)
                 kc, vc = (t.view(ctx.shape[0], c.heads, c.head_dim) for t in kv.split(hd, dim=-1))
-                attn_int8.rms_rope(kc, self._norm_w(c.k_norm), c.k_norm.eps, None, out=kc)
-            with _phase("rms_rope", s * hd * 2 * 2):
-                attn_int8.rms_rope(qc, self._norm_w(c.q_norm), c.q_norm.eps, None, out=qc)
+            if c.q_norm.eps != c.k_norm.eps:
+                self._eps_mismatch()
+            oc = attn_int8.attention_rr(qc, kc, vc, None, self._norm_w(c.q_norm), self._norm_w(c.k_norm), c.q_norm.eps,
+                                        q_roped=qc if trace is not None else None, k_roped=kc, _tag="cross")
             rec("cross_q", qc), rec("cross_k", kc), rec("cross_v", vc)
-            oc = attn_int8.attention(qc, kc, vc, _tag="cross")
             rec("cross_out", oc)
             with _phase("quant_attn_out", qbytes(hd)):
                 oq, os_ = tq.rot_quant_rows_i8(oc.view(s, hd), rotate=rot)
@@ -311,6 +320,18 @@ class FusedBlock:
         return out
 
     __call__ = forward
+
+
+def prewarm_constants(blocks, s, mod_segments, device):
+    """Create, on the current stream, every tensor the fused blocks cache per (token count, device): the row index
+    of the segmentation and the constant modulation tables of the cross-attention norm. A caller that is about to
+    run blocks on several streams calls this first."""
+    _row_index(mod_segments, s, device)
+    for fb in blocks:
+        if isinstance(fb, FusedBlock) and fb.cq_q is not None:
+            d = fb.block.norm_c.weight.shape[0]
+            fb._zeros_tab(d, device)
+            fb._const.setdefault(("idx0", s, str(device)), torch.zeros(s, dtype=torch.int32, device=device))
 
 
 def _fused_mlp(mlp, fc2q):

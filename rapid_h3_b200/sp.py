@@ -150,7 +150,7 @@ class Ulysses:
         """Attention on this rank's heads; the epilogue stores every token's output row into the rank that owns the
         token. Returns [P, S_local, (H/P)*D] as heads_to_tokens does."""
         from . import attn_int8
-        pre = attn_int8.int8_prepass(q, k, v, "self")
+        pre = attn_int8.int8_prepass(q, k, v, _tag="self")
         w = self._w
         offsets, starts = scatter_plan(self.bounds, self.rank, w)
         ptrs = [self._o_buf.ptrs[r] + offsets[r] for r in range(self.world)]

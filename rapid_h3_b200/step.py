@@ -63,32 +63,61 @@ class H3Runtime:
         return rt
 
     # -------------------------------------------------------------------------------------------
-    def step(self, latent, audio, t_emb, rope_freqs, ctx, sp=None):
+    def step(self, latent, audio, t_emb, rope_freqs, ctx, sp=None, streams=None):
         """One transformer evaluation.
 
         latent [B, C, T, H, W], audio [B, A, C] (A may be 0), t_emb [B, R, d] (row 0 video, row 1 audio),
         rope_freqs bf16 [S, 48, 2, 2] for the S = T*H*W + A packed tokens, ctx [B, Ttext, text_dim].
-        Returns (video [B, C, T, H, W], audio [B, A, C]) in bf16. With `sp` (an Ulysses group over S tokens)
-        every rank passes the same full inputs, computes its token shard and receives the full result."""
+        Returns (video [B, C, T, H, W], audio [B, A, C]) in bf16. With `sp` (an Ulysses group over S tokens, or a
+        list with one group per sample) every rank passes the same full inputs, computes its token shard and
+        receives the full result.
+
+        `streams` (a list of CUDA streams, one per sample) runs the samples of the batch side by side: the samples
+        are independent, so while one of them sits in an exchange of the sequence-parallel step (a kernel that only
+        stores over NVLink, then a barrier across the ranks) the other one's GEMMs and attention keep the SMs busy.
+        Each concurrent sample then needs its own Ulysses group, because a group owns one set of exchange buffers."""
         b = latent.shape[0]
         n_video = latent.shape[2] * latent.shape[3] * latent.shape[4]
         n_audio = audio.shape[1] if audio is not None else 0
         s = n_video + n_audio
         segs = [(0, n_video, 0)] + ([(n_video, s, 1)] if n_audio else [])
-        lo, hi = (0, s) if sp is None else (sp.lo, sp.hi)
-        segs_l = segs if sp is None else shard_segments(segs, lo, hi)
+        sps = list(sp) if isinstance(sp, (list, tuple)) else [sp] * b
+        if len(sps) != b:
+            raise RuntimeError(f"{len(sps)} sequence-parallel groups for a batch of {b}")
+        if streams is not None:
+            if len(streams) != b:
+                raise RuntimeError(f"{len(streams)} streams for a batch of {b}")
+            if sps[0] is not None and len({id(g) for g in sps}) != b:
+                raise RuntimeError("samples that run side by side need one Ulysses group each")
+        lo, hi = (0, s) if sps[0] is None else (sps[0].lo, sps[0].hi)
+        segs_l = segs if sps[0] is None else shard_segments(segs, lo, hi)
         rope_l = rope_freqs.reshape(s, 48, 2, 2)[lo:hi].contiguous()
         m = self.model
         xs = []
         for i in range(b):
             x = m.tokens(latent[i], None if audio is None else audio[i])  # per-token: embed, then take the shard
             xs.append(x[lo:hi].contiguous())
-        for fb in self.blocks:            # blocks outermost: a block's weights serve every sample of the batch
-            for i in range(b):
-                xs[i] = fb.forward(xs[i], t_emb[i], segs_l, rope_l, ctx[i], sp=sp)
+        if streams is None:
+            for fb in self.blocks:        # blocks outermost: a block's weights serve every sample of the batch
+                for i in range(b):
+                    xs[i] = fb.forward(xs[i], t_emb[i], segs_l, rope_l, ctx[i], sp=sps[i])
+        else:
+            # what the blocks cache per shape (row index, constant tables) is made here, on the caller's stream,
+            # so that no side stream ever reads a cached tensor another side stream is still filling
+            nodes.prewarm_constants(self.blocks, hi - lo, segs_l, xs[0].device)
+            main = torch.cuda.current_stream()
+            for st in streams:
+                st.wait_stream(main)
+            for fb in self.blocks:
+                for i in range(b):
+                    with torch.cuda.stream(streams[i]):
+                        xs[i] = fb.forward(xs[i], t_emb[i], segs_l, rope_l, ctx[i], sp=sps[i])
+            for i, st in enumerate(streams):
+                xs[i].record_stream(st)
+                main.wait_stream(st)
         vids, auds = [], []
         for i in range(b):
-            x = xs[i] if sp is None else sp.gather_tokens(xs[i])
+            x = xs[i] if sps[i] is None else sps[i].gather_tokens(xs[i])
             v, a = m.untokens(x, latent.shape[1:])
             vids.append(v), auds.append(a)
         return torch.stack(vids), torch.stack(auds)
