@@ -250,9 +250,12 @@ class FusedBlock:
                 # RMSNorm + RoPE of q and k run inside the attention pre-pass: q is quantized from registers, the
                 # normalised k replaces the raw one in the qkv buffer (nothing reads the raw values afterwards);
                 # when a trace is asked for, the normalised q is stored too
+                raw = (q.clone(), k.clone()) if RR_CHECK else None
                 o = attn_int8.attention_rr(q, k, v, tab, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps
                                            if a.q_norm.eps == a.k_norm.eps else self._eps_mismatch(),
                                            q_roped=q if trace is not None else None, k_roped=k, _tag="self")
+                if raw is not None:
+                    _rr_check(raw[0], raw[1], v, o, tab, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps)
                 rec("qkv_rr", qkv)
                 rec("attn_out", o)                                     # [S, H, 128] token-major
                 with _phase("quant_attn_out", qbytes(hd)):
@@ -432,24 +435,81 @@ class RapidH3LinearQuant:
         return (PatchedModel(model, by_name, forwards, wrappers, stats),)
 
 
+# When set to a file path, every fused self-attention call of a FusedBlock is verified against the unfused form on
+# its own q / k / v (RMSNorm + RoPE as a separate pass on copies, then the plain pre-pass and attention): the
+# output and every pre-pass operand must be bit-identical. One JSON line per call is appended to the file. This is
+# the reference's config-2xx self-check (`_rr_check`, __init__.py:334-349); `RapidH3Int8Attention.patch(config >= 200)`
+# switches it on with the path in $RAPIDH3_RRCHECK.
+RR_CHECK = None
+
+
+def _rr_check(q, k, v, out, tab, qw, kw, eps, block_index=None):
+    """q, k: RAW [S, H, 128] views (copies made before the fused call), v, out as the fused call saw / produced them."""
+    import json
+    qc = attn_int8.rms_rope(q, qw, eps, tab)
+    kc = attn_int8.rms_rope(k, kw, eps, tab)
+    plain = attn_int8.int8_prepass(qc, kc, v)
+    fused = attn_int8.int8_prepass(q, k, v, tab, qw, kw, eps)
+    ref = attn_int8.attention_pre(plain)
+    names = ("q8", "qs", "k8", "ks", "vt", "vscale", "vmean", "kmean")
+    rec = {"block": block_index, "S": int(q.shape[0]), "out_equal": bool(torch.equal(ref, out)),
+           "operands_equal": all(torch.equal(getattr(plain, n).view(torch.uint8), getattr(fused, n).view(torch.uint8))
+                                 for n in names),
+           "max_abs_diff": float((ref.float() - out.float()).abs().max())}
+    with open(RR_CHECK, "a") as f:
+        f.write(json.dumps(rec) + "\n")
+    return rec
+
+
 class RapidH3Int8Attention:
     """Node adapter: returns the attention override the reference installs in transformer_options
-    (reference __init__.py:995-1047). Accepts only what the reference accepts for its INT8 path (no mask,
-    [1, H, S, 128] bf16, skip_reshape); anything else raises instead of falling back."""
+    (reference __init__.py:995-1047). The override takes the calls the reference's INT8 path takes (no mask,
+    `skip_reshape`, q, k, v all [1, H, S, 128] bf16 with S >= 1024) and hands every other call on to the override
+    that was installed before it, or to the framework's own attention function `func`, exactly as the reference
+    does: those calls were never this node's. `exact_rows` names segment kinds of the packed layout
+    (transformer_options["minimax_h3_layout"].segments = [(start, stop, kind)]) whose query rows are recomputed
+    with bf16 scaled-dot-product attention after the INT8 kernel has run (the reference's patch-up, :1035-1037)."""
 
-    def patch(self, model, config=80, exact_rows=""):
-        if exact_rows:
-            raise NotImplementedError("exact_rows (bf16 SDPA patch-up) is not implemented")
+    def patch(self, model, config=80, exact_rows="", previous=None):
+        global RR_CHECK
+        import os
+        import torch.nn.functional as F
+        exact = {t.strip() for t in exact_rows.split(",") if t.strip()}
+        rmsrope = config >= 100 and not exact
+        if config >= 200:
+            RR_CHECK = os.environ.get("RAPIDH3_RRCHECK", "rapidh3_rrcheck.jsonl")
+        config = config % 100
+
+        def exact_spans(options, s):
+            layout = (options or {}).get("minimax_h3_layout")
+            if layout is None or getattr(layout, "seq_len", None) != s:
+                return []
+            spans = []
+            for a, b, kind in layout.segments:
+                if kind in exact and b > a:
+                    if spans and spans[-1][1] == a:
+                        spans[-1][1] = b       # adjacent spans are recomputed in one call
+                    else:
+                        spans.append([a, b])
+            return spans
 
         def override(func, q, k, v, heads=None, mask=None, skip_reshape=False, skip_output_reshape=False, scale=None,
                      **kwargs):
-            if not (mask is None and skip_reshape and q.dim() == 4 and q.shape[0] == 1 and q.shape[-1] == 128
-                    and q.dtype == torch.bfloat16):
-                raise NotImplementedError("RapidH3Int8Attention: unsupported attention call (no fallback path)")
-            out = attn_int8.attention_bhsd(q, k, v, scale)
+            ours = (mask is None and skip_reshape and q.dim() == 4 and q.shape[0] == 1 and q.shape == k.shape == v.shape
+                    and q.shape[-1] == 128 and q.shape[2] >= 1024 and q.dtype == torch.bfloat16 and q.is_cuda)
+            if not ours:
+                rest = dict(heads=heads, mask=mask, skip_reshape=skip_reshape, skip_output_reshape=skip_output_reshape,
+                            scale=scale, **kwargs)
+                return previous(func, q, k, v, **rest) if previous else func(q, k, v, **rest)
+            out = torch.empty_like(q)
+            attn_int8.attention(q[0].transpose(0, 1), k[0].transpose(0, 1), v[0].transpose(0, 1), scale, config=config,
+                                out=out[0].transpose(0, 1))
+            for a, b in exact_spans(kwargs.get("transformer_options"), q.shape[2]):
+                out[:, :, a:b] = F.scaled_dot_product_attention(q[:, :, a:b], k, v, scale=scale)
             return out if skip_output_reshape else out.transpose(1, 2).reshape(1, q.shape[2], -1)
 
-        override.rapidh3_rmsrope = config % 100 if config >= 100 else None
+        override.rapidh3_rmsrope = config if rmsrope else None
+        override.rapidh3_rrcheck = RR_CHECK is not None
         return (model, override)
 
 

@@ -258,3 +258,61 @@ def test_unfused_patch_paths_and_error_statistics(pkg):
         assert isinstance(patched.block_forward[1], r.nodes.FusedBlock)
         v3, _ = patched(*args)
         assert rel_l2(v3, ref_v) < 0.05
+
+
+def test_attention_override_takes_its_calls_and_hands_on_the_rest(pkg):
+    """The override of RapidH3Int8Attention: [1, H, S, 128] bf16 calls with S >= 1024 and equal shapes run the INT8
+    kernel; short, masked or differently shaped calls go to the override installed before, else to the framework's
+    function; `exact_rows` recomputes the named segments' query rows with bf16 SDPA."""
+    import types
+    r = pkg
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v = (torch.randn(1, 2, 1100, 128, device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+    calls = []
+
+    def stock(q_, k_, v_, **kw):
+        calls.append("stock")
+        return torch.nn.functional.scaled_dot_product_attention(q_, k_, v_, scale=kw.get("scale"))
+
+    _, ov = r.nodes.RapidH3Int8Attention().patch(None, config=80)
+    out = ov(stock, q, k, v, heads=2, skip_reshape=True, skip_output_reshape=True)
+    assert not calls and out.shape == q.shape
+    want = r.attn_int8.attention_bhsd(q, k, v)
+    assert torch.equal(out, want)
+    assert ov(stock, q, k, v, heads=2, skip_reshape=True).shape == (1, 1100, 256)
+    # not ours: a short sequence, a mask, k shorter than q
+    ov(stock, q[:, :, :512], k[:, :, :512], v[:, :, :512], heads=2, skip_reshape=True, skip_output_reshape=True)
+    ov(stock, q, k, v, heads=2, mask=torch.zeros(1100, 1100, device="cuda", dtype=torch.bfloat16), skip_reshape=True)
+    ov(stock, q, k[:, :, :1024], v[:, :, :1024], heads=2, skip_reshape=True, skip_output_reshape=True)
+    assert calls == ["stock"] * 3
+    # an override that was there before gets the calls that are not ours
+    _, ov2 = r.nodes.RapidH3Int8Attention().patch(None, config=80, previous=lambda f, *a, **kw: "previous")
+    assert ov2(stock, q[:, :, :100], k[:, :, :100], v[:, :, :100], skip_reshape=True) == "previous"
+    # exact rows: the audio segment's rows equal bf16 SDPA, the others the INT8 kernel
+    layout = types.SimpleNamespace(seq_len=1100, segments=[(0, 1000, "video"), (1000, 1100, "audio")])
+    _, ov3 = r.nodes.RapidH3Int8Attention().patch(None, config=80, exact_rows="audio")
+    out3 = ov3(stock, q, k, v, skip_reshape=True, skip_output_reshape=True, transformer_options={"minimax_h3_layout": layout})
+    sdpa = torch.nn.functional.scaled_dot_product_attention(q[:, :, 1000:], k, v)
+    assert torch.equal(out3[:, :, 1000:], sdpa) and torch.equal(out3[:, :, :1000], want[:, :, :1000])
+    assert ov.rapidh3_rmsrope is None and ov3.rapidh3_rmsrope is None
+
+
+def test_fused_rope_prepass_self_check(pkg, tmp_path, monkeypatch):
+    """config >= 200 switches on the per-call check of the fused RMSNorm + RoPE pre-pass against the unfused one:
+    bit-identical output and operands, one JSON line per fused self-attention call."""
+    import json
+    r = pkg
+    log = tmp_path / "rrcheck.jsonl"
+    monkeypatch.setenv("RAPIDH3_RRCHECK", str(log))
+    try:
+        _, ov = r.nodes.RapidH3Int8Attention().patch(None, config=290)
+        assert ov.rapidh3_rmsrope == 90 and ov.rapidh3_rrcheck
+        cfg = r.model.H3Config.tiny(n_blocks=2, text_dim=256)
+        model = r.model.init_weights(r.model.H3Transformer(cfg), seed=2).cuda()
+        dev = [t.cuda() for t in r.step.make_inputs(cfg, (6, 5, 4), 9, 1, 40, seed=3)]
+        r.step.H3Runtime(model).step(*dev)
+        torch.cuda.synchronize()
+    finally:
+        r.nodes.RR_CHECK = None
+    recs = [json.loads(line) for line in log.read_text().splitlines()]
+    assert len(recs) == 2 and all(x["out_equal"] and x["operands_equal"] and x["max_abs_diff"] == 0.0 for x in recs)

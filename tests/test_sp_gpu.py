@@ -1,6 +1,8 @@
-"""Sequence-parallel step on 2 GPUs (NCCL) against the single-GPU step: token shards + Ulysses exchange must
-reproduce the single-GPU result exactly (every op is row-local or head-local, and the attention statistics
-of a head always see its full sequence). Skipped when fewer than two GPUs are visible."""
+"""Sequence-parallel step on 2, 4 and 8 GPUs (NCCL) against the single-GPU step: token shards + Ulysses exchange
+must reproduce the single-GPU result exactly (every op is row-local or head-local, and the attention statistics
+of a head always see its full sequence): with the NCCL all-to-all exchanges, with the exchanges done by the
+kernels (stores into peer buffers), and with the two CFG samples side by side on two streams, each with its own
+group and buffers. A case is skipped when fewer GPUs are visible than it needs."""
 import os
 import socket
 
@@ -24,9 +26,12 @@ def _worker(rank, world, port, ret):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        cfg = r.model.H3Config.tiny(n_blocks=2, heads=4, d_model=512, mlp_hidden=1024)
+        heads = max(4, world)
+        cfg = r.model.H3Config.tiny(n_blocks=2, heads=heads, d_model=128 * heads, mlp_hidden=1024)
         model = r.model.init_weights(r.model.H3Transformer(cfg), seed=2).cuda()
-        grid, n_audio = (5, 6, 7), 11  # 221 tokens: shards of 128 + 93
+        # 221 tokens: shards of 128 + 93 on two ranks; 587 tokens: ten 64-token blocks over 4 or 8 ranks, the last
+        # shard ragged (11 tokens)
+        grid, n_audio = ((5, 6, 7), 11) if world <= 2 else ((8, 8, 9), 11)
         inputs = [t.cuda() for t in r.step.make_inputs(cfg, grid, n_audio, 2, 40, seed=3)]
         rt = r.step.H3Runtime(model)
         ref_v, ref_a = rt.step(*inputs)                       # every rank: the whole sequence on its own GPU
@@ -39,21 +44,33 @@ def _worker(rank, world, port, ret):
         for _ in range(2):  # twice: the exchange buffers are reused from call to call
             v2, a2 = rt.step(*inputs, sp=sp)
         r._lib.check_status()
-        ret[rank] = (ok, bool(torch.equal(v2, ref_v) and torch.equal(a2, ref_a)), how)
+        ok2 = bool(torch.equal(v2, ref_v) and torch.equal(a2, ref_a))
+        # the two CFG samples side by side: a stream, a process group and a set of exchange buffers each
+        sps = [r.sp.Ulysses(sp.total, group=dist.new_group(list(range(world)))) for _ in range(2)]
+        for u in sps:
+            u.enable_fused(cfg.heads, 128, torch.device("cuda", rank))
+        streams = [torch.cuda.Stream() for _ in range(2)]
+        for _ in range(2):
+            v3, a3 = rt.step(*inputs, sp=sps, streams=streams)
+        torch.cuda.synchronize()
+        r._lib.check_status()
+        ok3 = bool(torch.equal(v3, ref_v) and torch.equal(a3, ref_a))
+        ret[rank] = (ok, ok2 and ok3, how)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.timeout(300)
-def test_two_rank_step_equals_single_gpu_step():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharded_step_equals_single_gpu_step(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     out = dict(ret)
-    print("peer buffers via", out[0][2])
-    assert [out[r][:2] for r in (0, 1)] == [(True, True), (True, True)], out
+    print(f"{world} ranks: sharded step == single-GPU step: {[out[r][:2] for r in range(world)]}; peer buffers via {out[0][2]}")
+    assert [out[r][:2] for r in range(world)] == [(True, True)] * world, out
 
 
 @pytest.mark.timeout(300)
