@@ -242,6 +242,27 @@ def workload_config(name, n):
             "l2": "every step streams >16 GB of weights and activations, far larger than the 126 MB L2"}
 
 
+def vae_extras(local):
+    """The second workload of the path beside the step record: the conv3d VAE decode of the benchmark latent on one
+    GPU, latent resident, 3 warm-up + 3 timed decodes (CUDA events)."""
+    from rapid_h3_b200 import vae
+    c, t, h, w = VAE_LATENT
+    dec = vae.VAEDecoder(latent_ch=c, seed=0, device=f"cuda:{local}")
+    dev = torch.randn(1, c, t, h, w, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).cuda()
+    for _ in range(3):
+        dec.decode(dev)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        dec.decode(dev)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 3
+    return {"vae_decode_ms": round(ms, 3), "vae_decode_tflops": round(dec.flops(t, h, w) / 1e9 / ms, 1),
+            "vae_latent": list(VAE_LATENT)}
+
+
 def run_vae(args, rank, world, local):
     """VAE decode of the benchmark latent (second workload of the hot path; time-sharded for N > 1)."""
     import torch.distributed as dist
@@ -332,6 +353,7 @@ def main():
                     help="run the CFG samples of a step side by side on two streams (auto: when N > 1, where it hides "
                          "the exchanges of the sequence-parallel step)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the VAE decode timing added to the N=1 step record")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -481,6 +503,8 @@ def main():
            "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
            "gpu_launches": launches, "roofline": roof, "roofline_gemm": roof_gemm, "roofline_quant": roof_quant,
            "phases_ms_per_step": phase_ms, "exchange_ms_per_step": round(exchange_ms, 3)}
+    if world == 1 and args.workload == "full" and not args.no_extras:
+        rec["extras"] = vae_extras(local)
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             rec["cpu_baseline"] = cpu_baseline_record(args.workload)

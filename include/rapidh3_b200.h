@@ -51,6 +51,12 @@ int rh3_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q,
  * (kernels.py:75-82) and triton_fp8.quant_rows (triton_fp8.py:449-455). */
 int rh3_quant_rows_fp8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
                        cudaStream_t stream);
+/* One scale for the whole tensor: s = max(max|x| / 448, 1e-12), q = e4m3(x / s); the same s is written to every
+ * entry of s[M], so the codes go through the row-scaled GEMM unchanged. `amax` is one fp32 word of device scratch
+ * (written here: the tensor's max |x|). Two kernel launches. Replaces the "fp8_tensor" branches of
+ * kernels.quantize_weight and kernels.linear (custom_nodes/rapid_h3/kernels.py:63-65,125-128). */
+int rh3_quant_tensor_fp8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s, float* amax,
+                         cudaStream_t stream);
 /* x[M, 2F]: quantizes silu(x[:, :F]) * x[:, F:] to int8 [M, F].
  * Replaces triton_fp8.swiglu_rot_quant_rows_i8 without rotation (triton_fp8.py:437-439, prologue :137-139). */
 int rh3_swiglu_quant_rows_i8(const void* x, int64_t ldx, int64_t M, int64_t F, void* q, int64_t ldq, float* s,

@@ -50,6 +50,9 @@ def quantize_rows(x, mode):
     """(q, s[M,1]): kernels.py:75-82. int8: s = max(amax/127, 1e-12), q = clamp(round(x/s), +-127)."""
     if mode == "int8_rot":  # kernels.py:115-117: rotate, then the int8 row quantizer
         x, mode = rotate256(x.float()), "int8_rowwise"
+    if mode == "fp8_tensor":  # kernels.py:126-127: one scale for the tensor, repeated per row for the row-scaled product
+        s = (x.abs().amax().float() / FP8_MAX).clamp_min(1e-12)
+        return (x.float() / s).clamp(-FP8_MAX, FP8_MAX).to(FP8), s.reshape(1, 1).expand(x.shape[0], 1).contiguous()
     amax = x.abs().amax(dim=-1, keepdim=True).float()
     if mode == "int8_rowwise":
         s = (amax / 127.0).clamp_min(1e-12)
@@ -65,6 +68,9 @@ def quantize_weight(w, mode):
     w = w.float()
     if mode == "int8_rot":  # kernels.py:58-60: W . blockdiag(H256)^T, then int8 per output row
         w, mode = rotate256(w), "int8_rowwise"
+    if mode == "fp8_tensor":  # kernels.py:63-65 (the scalar scale repeated per output row)
+        s = (w.abs().amax() / FP8_MAX).clamp_min(1e-12)
+        return (w / s).clamp(-FP8_MAX, FP8_MAX).to(FP8), s.reshape(1, 1).expand(1, w.shape[0]).contiguous()
     if mode == "fp8_rowwise":
         s = (w.abs().amax(dim=1, keepdim=True) / FP8_MAX).clamp_min(1e-12)
         return (w / s).clamp(-FP8_MAX, FP8_MAX).to(FP8), s.t().contiguous()

@@ -40,6 +40,7 @@ struct QuantParams {
   int64_t ld_tab;
   // KIND_SWIGLU: F == K, the up half starts at column K
   int gw;  // KIND_HEADS: columns per group (128 for one head); x is [K/gw, M, gw] with group stride ldx
+  const float* tensor_amax;  // when set: one abs-max for the whole tensor replaces every row's own (per-tensor scale)
 };
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* v) {
@@ -224,7 +225,7 @@ __global__ void __launch_bounds__(T) quant_rows_kernel(const QuantParams p) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(v[i][j]));
   }
-  am = block_max<T>(am, red);
+  am = p.tensor_amax ? __ldg(p.tensor_amax) : block_max<T>(am, red);
   const float qmax = OUT_FP8 ? 448.f : 127.f;
   const float s = fmaxf(__fdiv_rn(am, qmax), 1e-12f);
   const float inv = __fdiv_rn(1.f, s);
@@ -286,6 +287,24 @@ __global__ void __launch_bounds__(T) rot_residual_quant_kernel(const float* __re
   }
 }
 
+// max |x| over a whole [M, K] bf16 tensor into *out (which the caller zeroed): |x| >= 0, so the float order is the
+// order of the bit patterns and one atomicMax on the bits per CTA finishes the reduction, in any order.
+__global__ void __launch_bounds__(256) tensor_absmax_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, int64_t M,
+                                                            int64_t K, float* __restrict__ out) {
+  __shared__ float red[8];
+  const int64_t nchunk = K >> 3, total = M * nchunk;
+  float am = 0.f;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t row = i / nchunk, c = i - row * nchunk;
+    float v[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(x + row * ldx + (c << 3))), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(v[j]));
+  }
+  am = block_max<256>(am, red);
+  if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(am));
+}
+
 template <int KIND, int OUT_FP8, int ROT = 0>
 int launch_quant(const QuantParams& p, cudaStream_t stream) {
   const int64_t nchunk = p.K >> 3;
@@ -343,6 +362,24 @@ extern "C" int rh3_quant_rows_fp8(const void* x, int64_t ldx, int64_t M, int64_t
   RH3_CHECK_ARG(ldx >= K && ldq >= K, "quant_rows_fp8: row strides smaller than K");
   QuantParams p{};
   p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = K; p.q = q; p.ldq = ldq; p.s = s;
+  return launch_quant<KIND_PLAIN, 1>(p, stream);
+}
+
+extern "C" int rh3_quant_tensor_fp8(const void* x, int64_t ldx, int64_t M, int64_t K, void* q, int64_t ldq, float* s,
+                                    float* amax, cudaStream_t stream) {
+  if (int e = check_common(x, ldx, M, K, q, ldq, s)) return e;
+  RH3_CHECK_ARG(ldx >= K && ldq >= K, "quant_tensor_fp8: row strides smaller than K");
+  RH3_CHECK_ARG(amax != nullptr, "quant_tensor_fp8: null abs-max word");
+  if (int e = check_cuda(cudaMemsetAsync(amax, 0, sizeof(float), stream), "quant_tensor_fp8 memset")) return e;
+  if (M == 0) return 0;
+  const int64_t chunks = M * (K >> 3);
+  const int64_t want = (chunks + 255) / 256, cap = static_cast<int64_t>(device_sm_count()) * 8;
+  tensor_absmax_kernel<<<static_cast<unsigned>(want < cap ? want : cap), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, M, K, amax);
+  if (int e = check_cuda(cudaGetLastError(), "tensor_absmax launch")) return e;
+  QuantParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx; p.M = M; p.K = K; p.q = q; p.ldq = ldq; p.s = s;
+  p.tensor_amax = amax;
   return launch_quant<KIND_PLAIN, 1>(p, stream);
 }
 

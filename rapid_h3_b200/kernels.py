@@ -27,7 +27,8 @@ class QWeight:
 _ROWWISE_I8 = ("int8_rowwise", "int8_fast")
 _ROT_I8 = ("int8_rot",)
 _ROWWISE_F8 = ("fp8_rowwise", "fp8_rowwise_torch")
-_UNSUPPORTED = ("nvfp4_fake", "nvfp4_rot_fake", "fp8_tensor")
+_TENSOR_F8 = ("fp8_tensor",)
+_UNSUPPORTED = ("nvfp4_fake", "nvfp4_rot_fake")
 
 
 def quantize_weight(w, mode):
@@ -37,7 +38,7 @@ def quantize_weight(w, mode):
     orthonormal, so rotated activations times rotated weights give x W^T (kernels.py:58-60)."""
     if mode in _UNSUPPORTED:
         raise NotImplementedError(f"mode {mode!r} is not implemented in rapid_h3_b200")
-    if mode not in _ROWWISE_I8 + _ROWWISE_F8 + _ROT_I8:
+    if mode not in _ROWWISE_I8 + _ROWWISE_F8 + _ROT_I8 + _TENSOR_F8:
         raise ValueError(mode)
     w = w.detach()
     if w.dtype != torch.bfloat16:
@@ -45,6 +46,10 @@ def quantize_weight(w, mode):
         if not torch.equal(w.to(torch.bfloat16).to(w.dtype), w):
             raise RuntimeError("quantize_weight: weight is not bf16-representable")
         w = w.to(torch.bfloat16)
+    if mode in _TENSOR_F8:
+        # one scale for the whole weight (kernels.py:63-65); kept as [1, N] equal entries for the row-scaled GEMM
+        q, s = _tq.quant_tensor(w.contiguous())
+        return QWeight(q, s.t().contiguous())
     fn = _tq.rot_quant_rows_i8 if mode in _ROT_I8 else (_tq.quant_rows_i8 if mode in _ROWWISE_I8 else _tq.quant_rows)
     q, s = fn(w.contiguous())
     return QWeight(q, s.t().contiguous())
@@ -58,6 +63,8 @@ def quantize_rows(x, mode):
         return _tq.rot_quant_rows_i8(x)
     if mode in _ROWWISE_F8:
         return _tq.quant_rows(x)
+    if mode in _TENSOR_F8:
+        return _tq.quant_tensor(x)
     raise ValueError(mode)
 
 
@@ -71,6 +78,6 @@ def linear(x, qw, mode):
     if mode in _UNSUPPORTED:
         raise NotImplementedError(f"mode {mode!r} is not implemented in rapid_h3_b200")
     xq, sa = quantize_rows(x.contiguous(), mode)
-    if mode in _ROWWISE_F8:
+    if mode in _ROWWISE_F8 + _TENSOR_F8:
         return _cf.fp8_gemm(xq, sa, qw.q, qw.scale)
     return _cf.int8_gemm(xq, sa, qw.q, qw.scale)

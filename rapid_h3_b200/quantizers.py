@@ -44,6 +44,19 @@ def quant_rows(x):
     return q, s
 
 
+def quant_tensor(x):
+    """FP8 e4m3 with one scale for the whole tensor: s = max|x| / 448. Returns (q fp8 [M,K], s fp32 [M,1]) with the
+    same s in every row, so the pair feeds the row-scaled GEMM as it is."""
+    _check_rows(x)
+    m, k = x.shape
+    q = torch.empty((m, k), device=x.device, dtype=FP8)
+    s = torch.empty((m, 1), device=x.device, dtype=torch.float32)
+    amax = torch.empty(1, device=x.device, dtype=torch.float32)
+    _lib.call("rh3_quant_tensor_fp8", x.data_ptr(), x.stride(0), m, k, q.data_ptr(), q.stride(0), s.data_ptr(),
+              amax.data_ptr(), _lib.stream())
+    return q, s
+
+
 def _rot_width(k):
     if k % ROT_GROUP:
         raise RuntimeError(f"the rotated width {k} must be a multiple of {ROT_GROUP}")

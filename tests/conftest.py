@@ -16,3 +16,9 @@ def pytest_configure(config):
 def golden_linear():
     import torch
     return torch.load(os.path.join(ROOT, "tests", "golden", "linear_ref.pt"))
+
+
+@pytest.fixture(scope="session")
+def golden_tensor():
+    import torch
+    return torch.load(os.path.join(ROOT, "tests", "golden", "tensor_ref.pt"))

@@ -12,6 +12,9 @@ rot_ref.pt holds what the reference's own H256 ConvRot code gives on CPU: the ma
 `triton_fp8.regular_hadamard(256)`, `triton_fp8.convrot(x)` of seeded activations, the yardstick
 quantizer of bench/rot_test.py:16-19 on them, and `kernels.quantize_weight(w, "int8_rot")`.
 
+tensor_ref.pt holds `kernels.quantize_weight(w, "fp8_tensor")` and `kernels.linear(x, qw, "fp8_tensor")`
+(kernels.py:63-65, :125-128) of one seeded case.
+
 attn_ref.pt holds the operand fake-quantizers of bench/attn_emulate.py (`q8(x, 1, 64)`, `f8(x, 0)`,
 :10-23) applied to seeded q / k - kmean / v - vmean, and the output of its `attn(..., pmode="run_fp8")`
 (:33-65) on those operands. The K / V channel means are an input of those functions; they are taken
@@ -51,6 +54,7 @@ def main(ref_root):
     print(path, os.path.getsize(path), "bytes")
     rot_fixture(ref, here)
     attn_fixture(ref_root, here)
+    tensor_fixture(ref, here)
 
 
 def rot_fixture(ref, here):
@@ -68,6 +72,17 @@ def rot_fixture(ref, here):
            "x_q": (r / s).round().clamp(-127, 127).to(torch.int8), "x_s": s,
            "w": w, "w_q": qw.q, "w_s": qw.scale}
     path = os.path.join(here, "rot_ref.pt")
+    torch.save(out, path)
+    print(path, os.path.getsize(path), "bytes")
+
+
+def tensor_fixture(ref, here):
+    """The per-tensor FP8 mode through the reference's own branches (kernels.py:63-65 and :125-128)."""
+    from oracle import inputs
+    x, w, _ = inputs.linear_case(72, 384, 136, seed=5, outlier_frac=0.02)
+    qw = ref.quantize_weight(w, "fp8_tensor")
+    out = {"x": x, "w": w, "wq": qw.q.view(torch.uint8), "ws": qw.scale, "y": ref.linear(x, qw, "fp8_tensor")}
+    path = os.path.join(here, "tensor_ref.pt")
     torch.save(out, path)
     print(path, os.path.getsize(path), "bytes")
 

@@ -180,3 +180,23 @@ def test_config1_full_size_properties(ops):
     out_p = attn.attention(q, k[perm], v[perm])
     assert rel_l2(out_p, out) < 3e-3  # bf16 output rounding amplifies last-bit changes of the statistics
     assert torch.isfinite(out.float()).all()
+
+
+def test_prepass_operands_match_the_reference_emulation_fixture(ops):
+    """The CUDA pre-pass against the fake-quantized tensors the reference's bench/attn_emulate.py produced on CPU
+    (`q8(q, 1, 64)`, `q8(k - kmean, 1, 64)`, `f8(v - vmean, 0)`; tests/golden/attn_ref.pt): codes x scales equal them
+    bit for bit, and the channel means the fixture was made with are the ones the kernels compute."""
+    import os
+    attn, lib = ops
+    g = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attn_ref.pt"))
+    q, k, v = g["q"], g["k"], g["v"]
+    l = q.shape[0]
+    pre = attn.int8_prepass(q.cuda(), k.cuda(), v.cuda())
+    lib.check_status()
+    assert torch.equal(pre.kmean.cpu(), g["kmean"]) and torch.equal(pre.vmean.cpu(), g["vmean"])
+    blk = torch.arange(l) // 64
+    for h, ref in enumerate(g["heads"]):
+        assert torch.equal(pre.q8[h, :l].cpu().float() * pre.qs[h].cpu()[blk][:, None], ref["q_fq"])
+        assert torch.equal(pre.k8[h, :l].cpu().float() * pre.ks[h].cpu()[blk][:, None], ref["k_fq"])
+        vdec = pre.vt[h, :, :l].cpu().float().t() * pre.vscale[h].cpu()[None]
+        assert torch.equal(vdec, ref["v_fq"])

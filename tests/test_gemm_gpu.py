@@ -89,6 +89,33 @@ def test_linear_matches_reference_golden(ops, golden_linear, case):
     assert rel_l2(y8.cpu(), g8["y"]) < 4e-3  # the reference rounds the product to bf16 before scaling
 
 
+def test_fp8_tensor_mode(ops, golden_tensor):
+    """One scale per tensor (kernels.py:63-65, :125-128): codes and scales bit-exact against the oracle and the
+    reference-made fixture, the product within the bf16 tolerance."""
+    gemm, kernels, lib = ops
+    c = golden_tensor
+    qw = kernels.quantize_weight(c["w"].cuda(), "fp8_tensor")
+    assert torch.equal(qw.q.cpu().view(torch.uint8), c["wq"])
+    assert torch.equal(qw.scale.cpu(), c["ws"].reshape(1, 1).expand(1, c["w"].shape[0]))
+    xq, xs = kernels.quantize_rows(c["x"].cuda(), "fp8_tensor")
+    xq_r, xs_r = ol.quantize_rows(c["x"], "fp8_tensor")
+    assert torch.equal(xq.cpu().view(torch.uint8), xq_r.view(torch.uint8)) and torch.equal(xs.cpu(), xs_r)
+    y = kernels.linear(c["x"].cuda(), qw, "fp8_tensor")
+    lib.check_status()
+    y_r = ol.linear(c["x"], *ol.quantize_weight(c["w"], "fp8_tensor"), "fp8_tensor")
+    assert rel_l2(y.cpu(), y_r) <= TOL
+    assert rel_l2(y.cpu(), c["y"]) < 4e-3
+    # a larger ragged case with an all-zero tensor row block and a strided view
+    x, w, _ = inputs.linear_case(333, 1024, 264, seed=9, outlier_frac=0.01)
+    x[7] = 0
+    xq, xs = kernels.quantize_rows(x.cuda(), "fp8_tensor")
+    xq_r, xs_r = ol.quantize_rows(x, "fp8_tensor")
+    assert torch.equal(xq.cpu().view(torch.uint8), xq_r.view(torch.uint8)) and torch.equal(xs.cpu(), xs_r)
+    z = torch.zeros(16, 64, dtype=torch.bfloat16)
+    zq, zs = kernels.quantize_rows(z.cuda(), "fp8_tensor")
+    assert torch.equal(zs.cpu(), torch.full((16, 1), 1e-12)) and not zq.view(torch.uint8).any()
+
+
 @pytest.mark.parametrize("shape", [(256, 256, 256), (777, 1024, 2048)])
 def test_fp8_gemm(ops, shape):
     gemm, kernels, lib = ops

@@ -224,3 +224,18 @@ def test_int8_rot_linear_beats_rowwise_on_outliers(ops):
         assert torch.equal(y.cpu(), yr)
         err[mode] = ((y.cpu().double() - ref).norm() / ref.norm()).item()
     assert err["int8_rot"] < 0.5 * err["int8_rowwise"], err
+
+
+def test_rotated_codes_match_the_reference_convrot_fixture(ops):
+    """The CUDA H256 rotation + int8 row quantizer against what the reference's own `triton_fp8.convrot` and
+    `kernels.quantize_weight(w, "int8_rot")` produced on CPU (tests/golden/rot_ref.pt): its own criterion, at most
+    one step apart on fewer than 1e-3 of the codes, scales equal to fp32 rounding."""
+    import os
+    from rapid_h3_b200 import kernels, quantizers
+    g = torch.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "rot_ref.pt"))
+    for got, want_q, want_s in ((quantizers.rot_quant_rows_i8(g["x"].cuda()), g["x_q"], g["x_s"]),
+                                (kernels.quantize_weight(g["w"].cuda(), "int8_rot"), g["w_q"], g["w_s"])):
+        q, s = (got.q, got.scale) if hasattr(got, "q") else got
+        d = (q.cpu().int() - want_q.int()).abs()
+        assert (d > 0).float().mean().item() < 1e-3 and int(d.max()) <= 1
+        assert ((s.cpu().reshape(-1) - want_s.reshape(-1)).abs() / want_s.reshape(-1)).max() < 1e-6
