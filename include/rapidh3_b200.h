@@ -168,6 +168,28 @@ int rh3_attn_prepass(const void* q, int64_t q_ss, int64_t q_sh, int64_t Lq, int6
                      int64_t qr_ss, int64_t qr_sh, void* k_roped, int64_t kr_ss, int64_t kr_sh, void* scratch,
                      int64_t scratch_bytes, void* q8, float* qs, void* k8, float* ks, void* vt, float* vscale,
                      float* vmean, float* kmean, cudaStream_t stream);
+/* ---- token-scaled attention: the numerics of the reference's production attention ("config 80" family incl.
+ * 90 / 94 / 190 / 194: custom_nodes/rapid_h3/csrc/README.md "What it computes", csrc/attn_cake/DESIGN.md section 2,
+ * dispatch attn_int8.cu:2568-2644, kernels cake/attn_cake.cuh:113-491) ---- */
+/* Pre-pass (five launches), arguments as rh3_attn_prepass except:
+ *   q8 [H,Lq_pad,128], k8 [H,Lk_pad,128]: int8 codes of the 128-point Hadamard rotation of q and of k - kmean,
+ *   ONE SCALE PER TOKEN: qs [H,Lq_pad]; ksb [H,Lk_pad/128,2,128] = per key tile 128 multipliers (key scale / 128:
+ *   the unnormalised rotation multiplies Q.K^T by 128) followed by 128 biases (0; -inf for the padding keys);
+ *   vt [H,128,Lk_pad] = int8((v - vmean) / vscale) with vscale = max|v - vmean| / 127 per channel. */
+int rh3_attn_tok_prepass(const void* q, int64_t q_ss, int64_t q_sh, int64_t Lq, int64_t Lq_pad, const void* k,
+                         int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t Lk,
+                         int64_t Lk_pad, int64_t H, const void* q_weight, const void* k_weight, float eps,
+                         const void* rope_table, void* q_roped, int64_t qr_ss, int64_t qr_sh, void* k_roped,
+                         int64_t kr_ss, int64_t kr_sh, void* scratch, int64_t scratch_bytes, void* q8, float* qs,
+                         void* k8, float* ksb, void* vt, float* vscale, float* vmean, float* kmean,
+                         cudaStream_t stream);
+/* Main kernel on those operands: int8 Q.K^T into int32, t_j = s * ksb scale + ksb bias, P = u8 against each key
+ * tile's own row maximum, u8 x s8 P.V into int32 per tile, folded into the fp32 output with
+ * ts = 2^(tile max - running max); row sums from the quantized P; out = (O/l) * vscale + vmean, bf16
+ * [Lq, H, 128] (element strides o_ss, o_sh). */
+int rh3_attn_int8_tok(const void* q8, const float* qs, const void* k8, const float* ksb, const void* vt,
+                      const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk, int64_t Lk_pad,
+                      int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh, cudaStream_t stream);
 /* out[Lq, H, 128] bf16 (element strides o_ss, o_sh) = softmax(Q.K^T * softmax_scale) . V from the
  * pre-pass operands: int8 Q.K^T into int32, base-2 online softmax in fp32, P as e4m3 against the
  * running maximum, e4m3 P.V into fp32, out = (O/l) * vscale + vmean. Lq may differ from Lk.

@@ -48,6 +48,9 @@ SIGNATURES = {
     "rh3_attn_kv_stats_noalloc": [_P, _I64, _I64, _P, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
     "rh3_attn_prepass": [_P, _I64, _I64, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, _F, _P, _P,
                          _I64, _I64, _P, _I64, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P],
+    "rh3_attn_tok_prepass": [_P, _I64, _I64, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _I64, _I64, _I64, _P, _P, _F, _P, _P,
+                         _I64, _I64, _P, _I64, _I64, _P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P],
+    "rh3_attn_int8_tok": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _I64, _I64, _P],
     "rh3_attn_quant_qk": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
     "rh3_attn_quant_v": [_P, _I64, _I64, _I64, _I64, _I64, _P, _P, _P, _P],
     "rh3_attn_int8": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _I64, _I64, _P],
@@ -68,7 +71,7 @@ KIND_I8, KIND_F8 = 0, 1
 _lib = None
 
 # kernels launched per entry point (for launch accounting in benchmarks)
-LAUNCHES = {"rh3_attn_kv_stats": 2, "rh3_attn_kv_stats_noalloc": 2, "rh3_attn_prepass": 3, "rh3_quant_tensor_fp8": 2, "rh3_version": 0, "rh3_sm_count": 0, "rh3_check_status": 0,
+LAUNCHES = {"rh3_attn_kv_stats": 2, "rh3_attn_kv_stats_noalloc": 2, "rh3_attn_prepass": 3, "rh3_attn_tok_prepass": 5, "rh3_quant_tensor_fp8": 2, "rh3_version": 0, "rh3_sm_count": 0, "rh3_check_status": 0,
             "rh3_attn_kv_stats_scratch_bytes": 0, "rh3_conv3d_gn_part_rows": 0}
 launch_count = 0
 

@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(256, 2) rope_stats_kernel(const RopeStatsParam
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) kv_stats_final_kernel(const float* __restrict__ part, int nchunk, int64_t L,
                                                              float* __restrict__ kmean, float* __restrict__ vmean,
-                                                             float* __restrict__ vscale) {
+                                                             float* __restrict__ vscale, float v_qmax) {
   const int h = blockIdx.x, c = threadIdx.x;
   const float* p = part + static_cast<int64_t>(h) * nchunk * 4 * D + c;
   float ksum = 0.f, vsum = 0.f, vhi = -INFINITY, vlo = INFINITY;
@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(128) kv_stats_final_kernel(const float* __rest
   kmean[h * D + c] = mk;
   vmean[h * D + c] = mv;
   // largest |v - mean| from the two extrema (the subtraction is monotonic, so this is the abs-max of v - mean)
-  vscale[h * D + c] = __fdiv_rn(fmaxf(fmaxf(__fsub_rn(vhi, mv), __fsub_rn(mv, vlo)), 1e-8f), 448.f);
+  vscale[h * D + c] = __fdiv_rn(fmaxf(fmaxf(__fsub_rn(vhi, mv), __fsub_rn(mv, vlo)), 1e-8f), v_qmax);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -359,7 +359,15 @@ __global__ void __launch_bounds__(128) kv_stats_final_kernel(const float* __rest
 // (v - mean) / scale written row-major into a 16 KB shared tile and read back by channel, 32 keys (two 16-byte
 // stores, one full 32-byte sector) at a time.
 // ---------------------------------------------------------------------------------------------
-template <bool DO_K, bool DO_V>
+// Eight int8 codes of values that each have their own scale: rint(y / s) with the IEEE quotient.
+__device__ __forceinline__ uint2 quant8_i8_per_channel(const float* y, const float* s) {
+  uint32_t w[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) w[j] = __float_as_uint(__fadd_rn(__fdiv_rn(y[j], s[j]), 12582912.f));
+  return make_uint2(pack_low_bytes(w[0], w[1], w[2], w[3]), pack_low_bytes(w[4], w[5], w[6], w[7]));
+}
+
+template <bool DO_K, bool DO_V, bool V_I8 = false>
 __global__ void __launch_bounds__(256, 3) quant_kv_kernel(const __nv_bfloat16* __restrict__ K, int64_t k_ss, int64_t k_sh,
                                                        const __nv_bfloat16* __restrict__ V, int64_t v_ss, int64_t v_sh,
                                                        int64_t L, int64_t Lpad, const float* __restrict__ kmean,
@@ -438,7 +446,7 @@ __global__ void __launch_bounds__(256, 3) quant_kv_kernel(const __nv_bfloat16* _
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = __fsub_rn(v[j], mean[j]);
       *reinterpret_cast<uint2*>(tile + (hw * 8 + i) * D + l16 * 8) =
-          tok0 + i < L ? quant8_e4m3_per_channel(v, sc, inv) : make_uint2(0, 0);
+          tok0 + i < L ? (V_I8 ? quant8_i8_per_channel(v, sc) : quant8_e4m3_per_channel(v, sc, inv)) : make_uint2(0, 0);
     }
     __syncthreads();
     // item = (channel d, group of 32 keys): consecutive threads take consecutive channels, so one load instruction
@@ -456,6 +464,94 @@ __global__ void __launch_bounds__(256, 3) quant_kv_kernel(const __nv_bfloat16* _
       uint4* dst = reinterpret_cast<uint4*>(Vt + (static_cast<int64_t>(h) * D + d) * Lpad + tile0 + grp * 32);
       dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
       dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-token operands of the token-scaled attention kernel (attn_tok.cu). A half-warp per (token, head) row:
+//   (RMSNorm + RoPE when asked) -> minus the channel mean (K) -> 128-point Hadamard rotation, unnormalised:
+//   butterflies (a, b) -> (a + b, a - b) over channel distance 1, 2, 4 inside the lane's 8 channels, then over lane
+//   distance 1, 2, 4, 8 (channel distance 8 .. 64), every add a correctly rounded fp32 add -> abs-max of the row ->
+//   s = max(amax, 1e-8) / 127, code = rint(y / s).
+// Q rows store s; K rows store the pair (s / 128, 0) the main kernel multiplies the integer scores with (the
+// rotation multiplies Q.K^T by 128) and (0, -inf) for the padding keys, whose codes are zero.
+// Reference: the per-token Q/K quantizer with `hadamard128` of custom_nodes/rapid_h3/csrc/README.md ("Q, K -> int8,
+// per token"), kernels attn_int8.cu:130-170.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void hadamard128(float* v, int lane) {
+#pragma unroll
+  for (int d = 1; d < 8; d <<= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if ((j & d) == 0) {
+        const float a = v[j], b = v[j + d];
+        v[j] = __fadd_rn(a, b);
+        v[j + d] = __fsub_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 1; o < 16; o <<= 1) {
+    const bool upper = (lane & o) != 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[j], o);
+      v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+    }
+  }
+}
+
+template <bool IS_K>
+__global__ void __launch_bounds__(256) quant_tok_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_ss, int64_t x_sh,
+                                                        int64_t L, int64_t Lpad, int H,
+                                                        const __nv_bfloat16* __restrict__ w, float eps,
+                                                        const __nv_bfloat16* __restrict__ tab,
+                                                        __nv_bfloat16* __restrict__ x_out, int64_t xo_ss, int64_t xo_sh,
+                                                        const float* __restrict__ mean, int8_t* __restrict__ q8,
+                                                        float* __restrict__ scales) {
+  const int lane = threadIdx.x & 31, l16 = lane & 15;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * HW_PER_CTA + (threadIdx.x >> 4);
+  const bool in_grid = row < Lpad * H;
+  const int64_t s = in_grid ? row / H : 0;
+  const int h = in_grid ? static_cast<int>(row - s * H) : 0;
+  const bool live = in_grid && s < L;
+  float v[8];
+  unpack8(load_row16(x + (live ? s : 0) * x_ss + h * x_sh, l16), v);
+  if (!live) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;   // padding rows: zero codes and the smallest scale
+  }
+  if (w) {
+    NormRope nr;
+    load_norm_weight(w, l16, nr);
+    if (tab) load_rope_row(tab + (live ? s : 0) * 48 * 4, l16, nr);
+    norm_rope_row(v, nr, eps, tab != nullptr, lane);
+    if (x_out && live) *reinterpret_cast<uint4*>(x_out + s * xo_ss + h * xo_sh + l16 * 8) = pack8(v);
+  }
+  if (IS_K && mean) {
+    const float4 m0 = *reinterpret_cast<const float4*>(mean + h * D + l16 * 8);
+    const float4 m1 = *reinterpret_cast<const float4*>(mean + h * D + l16 * 8 + 4);
+    const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __fsub_rn(v[j], mm[j]);
+  }
+  hadamard128(v, lane);   // both half-warps take part in the shuffles
+  float am = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) am = fmaxf(am, fabsf(v[j]));
+  am = half_warp_max(am);
+  const float scale = __fdiv_rn(fmaxf(am, 1e-8f), 127.f), inv = __fdiv_rn(1.f, scale);
+  if (!in_grid) return;
+  *reinterpret_cast<uint2*>(q8 + (static_cast<int64_t>(h) * Lpad + s) * D + l16 * 8) =
+      live ? quant8_i8(v, scale, inv) : make_uint2(0, 0);
+  if (l16 == 0) {
+    if (IS_K) {
+      float* t = scales + (static_cast<int64_t>(h) * (Lpad / 128) + s / 128) * 256 + (s & 127);
+      t[0] = live ? __fmul_rn(scale, 0.0078125f) : 0.f;
+      t[128] = live ? 0.f : -INFINITY;
+    } else {
+      scales[static_cast<int64_t>(h) * Lpad + s] = scale;
     }
   }
 }
@@ -482,7 +578,7 @@ int kv_stats_run(const void* k, int64_t k_ss, int64_t k_sh, const void* v, int64
   p.Lk = L; p.part = part; p.nchunk_k = static_cast<int>(nchunk); p.H = static_cast<int>(H);
   if (int e = launch_rope_stats(p, static_cast<int>(nchunk * H), stream)) return e;
   kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(part, static_cast<int>(nchunk), L, kmean, vmean,
-                                                                      vscale);
+                                                                      vscale, 448.f);
   return check_cuda(cudaGetLastError(), "attention pre-pass (statistics) launch");
 }
 
@@ -679,7 +775,7 @@ extern "C" int rh3_attn_prepass(const void* q, int64_t q_ss, int64_t q_sh, int64
   p.tab = static_cast<const __nv_bfloat16*>(rope_table); p.eps = eps; p.H = static_cast<int>(H);
   p.q_ctas = static_cast<int>(nchunk_q * H);
   if (int e = launch_rope_stats(p, static_cast<int>(nchunk_k * H), stream)) return e;
-  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(p.part, p.nchunk_k, Lk, kmean, vmean, vscale);
+  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(p.part, p.nchunk_k, Lk, kmean, vmean, vscale, 448.f);
   if (int e = check_cuda(cudaGetLastError(), "attn_prepass statistics launch")) return e;
   // K is read where the first launch left it: the normalised copy when there is one
   const __nv_bfloat16* kq = k_weight ? static_cast<const __nv_bfloat16*>(k_roped) : static_cast<const __nv_bfloat16*>(k);
@@ -688,4 +784,65 @@ extern "C" int rh3_attn_prepass(const void* q, int64_t q_ss, int64_t q_sh, int64
       kq, kq_ss, kq_sh, static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, Lk, Lk_pad, kmean, vmean, vscale,
       static_cast<int8_t*>(k8), ks, static_cast<uint8_t*>(vt));
   return check_cuda(cudaGetLastError(), "attn_prepass quantizer launch");
+}
+
+// The pre-pass of the token-scaled attention kernel (rh3_attn_int8_tok): K/V statistics (the K side also applies and
+// stores RMSNorm + RoPE when the weights are given), per-token rotated int8 Q and K, int8 V^T. Five launches.
+extern "C" int rh3_attn_tok_prepass(const void* q, int64_t q_ss, int64_t q_sh, int64_t Lq, int64_t Lq_pad, const void* k,
+                                    int64_t k_ss, int64_t k_sh, const void* v, int64_t v_ss, int64_t v_sh, int64_t Lk,
+                                    int64_t Lk_pad, int64_t H, const void* q_weight, const void* k_weight, float eps,
+                                    const void* rope_table, void* q_roped, int64_t qr_ss, int64_t qr_sh, void* k_roped,
+                                    int64_t kr_ss, int64_t kr_sh, void* scratch, int64_t scratch_bytes, void* q8,
+                                    float* qs, void* k8, float* ksb, void* vt, float* vscale, float* vmean,
+                                    float* kmean, cudaStream_t stream) {
+  RH3_CHECK_ARG(Lq > 0 && Lk > 0 && H > 0 && H < 65536, "attn_tok_prepass: bad shape Lq=%lld Lk=%lld H=%lld",
+                (long long)Lq, (long long)Lk, (long long)H);
+  RH3_CHECK_ARG(Lq_pad >= Lq && Lq_pad % 256 == 0 && Lk_pad >= Lk && Lk_pad % 128 == 0,
+                "attn_tok_prepass: Lq_pad must be a multiple of 256 and Lk_pad a multiple of 128, covering Lq / Lk");
+  RH3_CHECK_ARG(q && k && v && scratch && q8 && qs && k8 && ksb && vt && vscale && vmean && kmean,
+                "attn_tok_prepass: null pointer");
+  RH3_CHECK_ARG((q_weight == nullptr) == (k_weight == nullptr), "attn_tok_prepass: q and k norm weights come together");
+  RH3_CHECK_ARG(!rope_table || (q_weight && Lq == Lk), "attn_tok_prepass: a rope table needs the norm weights and Lq == Lk");
+  RH3_CHECK_ARG(!k_weight || k_roped, "attn_tok_prepass: the normalised k needs a place to go (k_roped; it may be k itself)");
+  RH3_CHECK_ARG(aligned(q, 16) && aligned(k, 16) && aligned(v, 16) && strides16(q_ss, q_sh) && strides16(k_ss, k_sh) &&
+                    strides16(v_ss, v_sh) && (!q_roped || (aligned(q_roped, 16) && strides16(qr_ss, qr_sh))) &&
+                    (!k_roped || (aligned(k_roped, 16) && strides16(kr_ss, kr_sh))),
+                "attn_tok_prepass: rows must be 16-byte aligned (strides multiples of 8 elements)");
+  RH3_CHECK_ARG(aligned(scratch, 16) && aligned(q8, 16) && aligned(k8, 16) && aligned(vt, 16) && aligned(vscale, 16) &&
+                    aligned(vmean, 16) && aligned(kmean, 16) && aligned(ksb, 16) &&
+                    (!q_weight || (aligned(q_weight, 16) && aligned(k_weight, 16))) &&
+                    (!rope_table || aligned(rope_table, 16)),
+                "attn_tok_prepass: operand buffers, weights and the rope table must be 16-byte aligned");
+  RH3_CHECK_ARG(scratch_bytes >= rh3_attn_kv_stats_scratch_bytes(Lk, H), "attn_tok_prepass: scratch too small (%lld < %lld)",
+                (long long)scratch_bytes, (long long)rh3_attn_kv_stats_scratch_bytes(Lk, H));
+  const int64_t nchunk_k = (Lk + CHUNK - 1) / CHUNK;
+  const int64_t q_ctas = (Lq_pad * H + HW_PER_CTA - 1) / HW_PER_CTA, k_ctas = (Lk_pad * H + HW_PER_CTA - 1) / HW_PER_CTA;
+  RH3_CHECK_ARG(nchunk_k * H < (1ll << 31) && q_ctas < (1ll << 31) && k_ctas < (1ll << 31), "attn_tok_prepass: L x H too large");
+  // 1 + 2: K (norm + rope, stored) and V chunk partials -> means and the int8 V scale
+  RopeStatsParams p{};
+  p.k = static_cast<const __nv_bfloat16*>(k); p.k_ss = k_ss; p.k_sh = k_sh;
+  p.k_w = static_cast<const __nv_bfloat16*>(k_weight);
+  p.k_out = static_cast<__nv_bfloat16*>(k_roped); p.ko_ss = kr_ss; p.ko_sh = kr_sh;
+  p.v = static_cast<const __nv_bfloat16*>(v); p.v_ss = v_ss; p.v_sh = v_sh;
+  p.Lk = Lk; p.part = static_cast<float*>(scratch); p.nchunk_k = static_cast<int>(nchunk_k);
+  p.tab = static_cast<const __nv_bfloat16*>(rope_table); p.eps = eps; p.H = static_cast<int>(H);
+  if (int e = launch_rope_stats(p, static_cast<int>(nchunk_k * H), stream)) return e;
+  kv_stats_final_kernel<<<static_cast<unsigned>(H), 128, 0, stream>>>(p.part, p.nchunk_k, Lk, kmean, vmean, vscale, 127.f);
+  if (int e = check_cuda(cudaGetLastError(), "attn_tok_prepass statistics launch")) return e;
+  // 3: Q rows (norm + rope fused), 4: K rows from the normalised copy, 5: V
+  quant_tok_kernel<false><<<static_cast<unsigned>(q_ctas), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(q), q_ss, q_sh, Lq, Lq_pad, static_cast<int>(H),
+      static_cast<const __nv_bfloat16*>(q_weight), eps, static_cast<const __nv_bfloat16*>(rope_table),
+      static_cast<__nv_bfloat16*>(q_roped), qr_ss, qr_sh, nullptr, static_cast<int8_t*>(q8), qs);
+  if (int e = check_cuda(cudaGetLastError(), "attn_tok_prepass Q launch")) return e;
+  const __nv_bfloat16* kq = k_weight ? static_cast<const __nv_bfloat16*>(k_roped) : static_cast<const __nv_bfloat16*>(k);
+  const int64_t kq_ss = k_weight ? kr_ss : k_ss, kq_sh = k_weight ? kr_sh : k_sh;
+  quant_tok_kernel<true><<<static_cast<unsigned>(k_ctas), 256, 0, stream>>>(
+      kq, kq_ss, kq_sh, Lk, Lk_pad, static_cast<int>(H), nullptr, eps, nullptr, nullptr, 0, 0, kmean,
+      static_cast<int8_t*>(k8), ksb);
+  if (int e = check_cuda(cudaGetLastError(), "attn_tok_prepass K launch")) return e;
+  quant_kv_kernel<false, true, true><<<dim3(static_cast<unsigned>(Lk_pad / 128), static_cast<unsigned>(H)), 256, 0, stream>>>(
+      nullptr, 0, 0, static_cast<const __nv_bfloat16*>(v), v_ss, v_sh, Lk, Lk_pad, nullptr, vmean, vscale, nullptr, nullptr,
+      static_cast<uint8_t*>(vt));
+  return check_cuda(cudaGetLastError(), "attn_tok_prepass V launch");
 }

@@ -1,0 +1,395 @@
+// INT8 flash attention with per-token Q / K scales, INT8 V and 8-bit P against each tile's own maximum
+// (head_dim 128, non-causal). The arithmetic of the reference's production attention (its "config 80" family:
+// custom_nodes/rapid_h3/csrc/README.md "What it computes", csrc/attn_cake/DESIGN.md section 2), laid out for the
+// Blackwell tensor cores:
+//
+//   operands   Q' = H128 . q, K' = H128 . (k - kmean)   (128-point Hadamard rotation, exact for Q.K^T up to the
+//              factor 128 folded into the key scales), int8 with ONE SCALE PER TOKEN; V8 = int8((v - vmean)/vscale)
+//              per channel, stored transposed
+//   S = Q8 . K8^T             int8 x int8 -> int32 in TMEM (tcgen05 kind::i8)
+//   t_j = s * kscale_j + kbias_j        kscale_j = (key scale) / 128, kbias_j = 0, or -inf for the padding keys
+//   tm = max_j t_j                      the tile's own row maximum
+//   P_j = u8(rint(255 * 2^((t_j - tm) * c)))          c = qscale(row) * softmax_scale * log2 e
+//   m' = max(m, tm * c),  a = 2^(m - m'),  ts = 2^(tm * c - m')
+//   l = ts * sum_j P_j + a * l          row sums from the QUANTIZED P, so numerator and denominator agree
+//   A = P . V8                u8 x s8 -> int32 in TMEM, one tile at a time (|A| <= 128 * 255 * 127 < 2^22)
+//   O = ts * A + a * O        the per-tile fold, fp32, in registers
+//   out = bf16((O / l) * vscale + vmean)
+//
+// Integers become floats without a conversion instruction: for |x| < 2^22 the int32 x + 0x4B400000 is the bit
+// pattern of the float 1.5*2^23 + x, and subtracting 1.5*2^23 from that float is exact.
+//
+// One CTA = two 128-query tiles of one head, 384 threads: warp 0 = TMA producer (K tile, V^T tile and the 1 KB of
+// key scales / biases per step, 3-stage ring), warp 1 = MMA issuer, warps 4..11 = softmax, one query row per
+// thread with its 128 fp32 output values in registers (232 registers per softmax thread after the register
+// re-split). The scores are read from TMEM twice, 32 columns at a time (maximum, then exponentials), so that the
+// output row fits beside them. TMEM (512 columns): S0 | S1 | A0 | A1.
+#include <limits.h>
+
+#include "common.cuh"
+#include "rapidh3_b200.h"
+
+namespace rh3 {
+namespace {
+
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int QG = 2;
+constexpr int TILE_BYTES = 128 * 128;
+constexpr int KSB_BYTES = 2 * BKV * 4;                   // per key tile: 128 scales, then 128 biases
+constexpr int STAGE_BYTES = 2 * TILE_BYTES + KSB_BYTES;  // K | V^T | scales, biases
+constexpr int KV_STAGES = 3;
+constexpr int TOK_THREADS = 384;
+
+struct TokParams {
+  const float* qs;      // [H][Lq_pad]  one scale per query token
+  const float* ksb;     // [H][Lk_pad/128][2][128]
+  const float* vscale;  // [H][128]
+  const float* vmean;   // [H][128]
+  __nv_bfloat16* out;
+  int64_t o_ss, o_sh;
+  int Lq, Lk, Lq_pad, Lk_pad, H;
+  float sl2;
+  int* status;
+};
+
+struct __align__(8) TokSmemTail {
+  uint64_t q_full;
+  uint64_t kv_full[KV_STAGES];
+  uint64_t kv_empty[KV_STAGES];
+  uint64_t s_full[QG], s_empty[QG], p_full[QG], pv_done[QG];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr int TOK_SMEM_BYTES = 2 * QG * TILE_BYTES + KV_STAGES * STAGE_BYTES + sizeof(TokSmemTail) + 1024;
+
+constexpr float kMagic = 12582912.f;          // 1.5 * 2^23
+constexpr uint32_t kMagicBits = 0x4B400000u;
+constexpr float kLog2_255 = 7.99435343685886f;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// exact float value of an int32 of magnitude below 2^22
+__device__ __forceinline__ float int_as_float_exact(uint32_t x) {
+  return __fsub_rn(__uint_as_float(x + kMagicBits), kMagic);
+}
+__device__ __forceinline__ float4 lds4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+// plain (untiled) bulk copy global -> shared, completion counted on an mbarrier; 16-byte aligned, size % 16 == 0
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+constexpr int REGS_COMPILED = 168, REGS_SERVICE = 40, REGS_SOFTMAX = 232;
+static_assert(128 * REGS_SERVICE + 256 * REGS_SOFTMAX == TOK_THREADS * REGS_COMPILED, "register pool must balance");
+__device__ __forceinline__ void reg_release_service() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+__device__ __forceinline__ void reg_take_softmax() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
+
+// Maximum over one 32-column chunk of t = s * kscale + kbias.
+__device__ __forceinline__ float chunk_tmax(const uint32_t* r, uint32_t ks_addr, uint32_t kb_addr, float tm) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 s4 = lds4(ks_addr + i * 4), b4 = lds4(kb_addr + i * 4);
+    const float t0 = fmaf(int_as_float_exact(r[i]), s4.x, b4.x), t1 = fmaf(int_as_float_exact(r[i + 1]), s4.y, b4.y);
+    const float t2 = fmaf(int_as_float_exact(r[i + 2]), s4.z, b4.z), t3 = fmaf(int_as_float_exact(r[i + 3]), s4.w, b4.w);
+    tm = fmaxf(fmaxf(tm, fmaxf(t0, t1)), fmaxf(t2, t3));
+  }
+  return tm;
+}
+
+// One 32-column chunk: P = u8(rint(2^(t * c + off))) written to 16-byte chunks 2k, 2k+1 of the row of P in shared
+// memory (XOR-swizzled like the TMA tiles), the integer codes added to `rs`.
+__device__ __forceinline__ void chunk_p(const uint32_t* r, uint32_t ks_addr, uint32_t kb_addr, float c, float off, int k,
+                                        uint8_t* p_row, int sw, uint32_t& rs) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 s4 = lds4(ks_addr + i * 16), b4 = lds4(kb_addr + i * 16);
+    const float t0 = fmaf(int_as_float_exact(r[4 * i]), s4.x, b4.x), t1 = fmaf(int_as_float_exact(r[4 * i + 1]), s4.y, b4.y);
+    const float t2 = fmaf(int_as_float_exact(r[4 * i + 2]), s4.z, b4.z), t3 = fmaf(int_as_float_exact(r[4 * i + 3]), s4.w, b4.w);
+    // p <= 255 * (1 + 2^-20): adding 1.5*2^23 leaves rint(p) (ties to even) in the low byte
+    const float p0 = __fadd_rn(ex2_approx(fmaf(t0, c, off)), kMagic), p1 = __fadd_rn(ex2_approx(fmaf(t1, c, off)), kMagic);
+    const float p2 = __fadd_rn(ex2_approx(fmaf(t2, c, off)), kMagic), p3 = __fadd_rn(ex2_approx(fmaf(t3, c, off)), kMagic);
+    w[i] = pack_low_bytes(__float_as_uint(p0), __float_as_uint(p1), __float_as_uint(p2), __float_as_uint(p3));
+    rs = __dp4a(w[i], 0x01010101u, rs);
+  }
+  *reinterpret_cast<uint4*>(p_row + (((2 * k) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  *reinterpret_cast<uint4*>(p_row + (((2 * k + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+__global__ void __launch_bounds__(TOK_THREADS, 1)
+attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
+                const __grid_constant__ CUtensorMap tma_v, const TokParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sP = smem + QG * TILE_BYTES;
+  uint8_t* sKV = smem + 2 * QG * TILE_BYTES;  // stage s at +s*STAGE_BYTES: K, V^T, scales + biases
+  TokSmemTail* tail = reinterpret_cast<TokSmemTail*>(sKV + KV_STAGES * STAGE_BYTES);
+  volatile int* abort_flag = &tail->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_pair = blockIdx.x, h = blockIdx.y;
+  const int n_kv = (p.Lk + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&tail->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&tail->kv_full[s], 1);
+      mbar_init(&tail->kv_empty[s], 1);
+    }
+    for (int g = 0; g < QG; ++g) {
+      mbar_init(&tail->s_full[g], 1);
+      mbar_init(&tail->s_empty[g], 4);  // one arrival per softmax warp
+      mbar_init(&tail->p_full[g], 4);
+      mbar_init(&tail->pv_done[g], 1);
+    }
+    tail->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tail->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  if (warp < 4) {
+    reg_release_service();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      tma_prefetch_desc(&tma_q);
+      tma_prefetch_desc(&tma_k);
+      tma_prefetch_desc(&tma_v);
+      mbar_arrive_expect_tx(&tail->q_full, QG * TILE_BYTES);
+      tma_load_2d(sQ, &tma_q, 0, h * p.Lq_pad + q_pair * (QG * BQ), &tail->q_full);
+      const float* ksb_h = p.ksb + static_cast<int64_t>(h) * (p.Lk_pad / BKV) * (2 * BKV);
+      for (int j = 0; j < n_kv; ++j) {
+        const int stage = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait_relaxed(&tail->kv_empty[stage], ph ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY, 400)) break;
+        uint8_t* sk = sKV + stage * STAGE_BYTES;
+        mbar_arrive_expect_tx(&tail->kv_full[stage], STAGE_BYTES);
+        tma_load_2d(sk, &tma_k, 0, h * p.Lk_pad + j * BKV, &tail->kv_full[stage]);
+        tma_load_2d(sk + TILE_BYTES, &tma_v, j * BKV, h * HD, &tail->kv_full[stage]);
+        bulk_load(sk + 2 * TILE_BYTES, ksb_h + static_cast<int64_t>(j) * (2 * BKV), KSB_BYTES, &tail->kv_full[stage]);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------ MMA issuer ------------------------------
+      constexpr uint32_t idesc_qk = make_idesc(2, 1, 1, BQ, BKV);  // s32 = s8 * s8
+      constexpr uint32_t idesc_pv = make_idesc(2, 0, 1, BQ, HD);   // s32 = u8 * s8
+      auto issue_qk = [&](int g, int j) {
+        const uint32_t q_addr = smem_u32(sQ + g * TILE_BYTES);
+        const uint32_t k_addr = smem_u32(sKV + (j % KV_STAGES) * STAGE_BYTES);
+        mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 0);
+        mma_commit(&tail->s_full[g]);
+      };
+      bool ok = mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
+                mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
+      if (ok) {
+        tc_fence_after();
+        for (int g = 0; g < QG; ++g) issue_qk(g, 0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          const int ns = (j + 1) % KV_STAGES;
+          ok = mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 64);
+          for (int g = 0; g < QG && ok; ++g) {
+            // completion j of s_empty: the softmax warps have read the scores of key tile j for the last time
+            ok = mbar_wait_relaxed(&tail->s_empty[g], j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64);
+            if (ok) {
+              tc_fence_after();
+              issue_qk(g, j + 1);
+            }
+          }
+          if (!ok) break;
+        }
+        const int stage = j % KV_STAGES;
+        const uint32_t v_addr = smem_u32(sKV + stage * STAGE_BYTES + TILE_BYTES);
+        for (int g = 0; g < QG && ok; ++g) {
+          // P of tile j is in shared memory, and the same threads have folded the accumulator of tile j-1 before
+          ok = mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 64);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);
+          mma4_i8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, 0);
+          mma_commit(&tail->pv_done[g]);
+        }
+        if (ok) mma_commit(&tail->kv_empty[stage]);
+      }
+    }
+  } else {
+    // ============================ softmax warp groups ============================
+    reg_take_softmax();
+    const int g = (warp >> 2) - 1;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_row = tmem_base + g * 128 + lane_off;
+    const uint32_t a_row = tmem_base + 256 + g * 128 + lane_off;
+    const int64_t q_row = static_cast<int64_t>(q_pair) * (QG * BQ) + g * BQ + row;
+    const float c_row = __fmul_rn(p.qs[static_cast<int64_t>(h) * p.Lq_pad + q_row], p.sl2);
+    uint8_t* p_row = sP + g * TILE_BYTES + row * 128;
+    const int sw = row & 7;
+    uint64_t* s_full = &tail->s_full[g];
+    uint64_t* s_empty = &tail->s_empty[g];
+    uint64_t* p_full = &tail->p_full[g];
+    uint64_t* pv_done = &tail->pv_done[g];
+    float O[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) O[i] = 0.f;
+    float m = -INFINITY, l = 0.f, a_prev = 0.f, ts_prev = 0.f;
+    bool ok = true;
+
+    // O = ts * A + a * O for the tile whose P.V has just finished
+    auto fold = [&](float a, float ts) {
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(a_row + c * 32, r);
+        tmem_ld_wait_regs(r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) O[c * 32 + i] = fmaf(ts, int_as_float_exact(r[i]), __fmul_rn(O[c * 32 + i], a));
+      }
+    };
+
+    for (int j = 0; j < n_kv; ++j) {
+      const int stage = j % KV_STAGES;
+      const uint32_t ks_addr = smem_u32(sKV + stage * STAGE_BYTES + 2 * TILE_BYTES), kb_addr = ks_addr + BKV * 4;
+      // the key scales of this stage came by bulk copy: observe its barrier before reading them
+      if (!mbar_wait_relaxed(&tail->kv_full[stage], (j / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 32)) { ok = false; break; }
+      if (!mbar_wait_relaxed(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_FULL, 32)) { ok = false; break; }
+      tc_fence_after();
+      // ---- pass 1: the tile's row maximum ----
+      float tm = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        tmem_ld_wait_regs(r);
+        tm = chunk_tmax(r, ks_addr + c * 128, kb_addr + c * 128, tm);
+      }
+      const float tmc = __fmul_rn(tm, c_row);
+      const float m_new = fmaxf(m, tmc);
+      const float a = ex2_approx(__fsub_rn(m, m_new)), ts = ex2_approx(__fsub_rn(tmc, m_new));
+      const float off = __fsub_rn(kLog2_255, tmc);
+      m = m_new;
+      if (j > 0) {
+        // P.V of the previous tile has finished: fold its accumulator; the P buffer is free again
+        if (!mbar_wait_relaxed(pv_done, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE, 32)) { ok = false; break; }
+        fold(a_prev, ts_prev);
+      }
+      // ---- pass 2: P into shared memory, integer row sum ----
+      uint32_t rs = 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(t_row + c * 32, r);
+        tmem_ld_wait_regs(r);
+        if (c == 3) {
+          // the scores have been read for the last time: the next Q.K^T may overwrite them
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty);
+        }
+        chunk_p(r, ks_addr + c * 128, kb_addr + c * 128, c_row, off, c, p_row, sw, rs);
+      }
+      l = fmaf(ts, static_cast<float>(rs), __fmul_rn(l, a));
+      a_prev = a;
+      ts_prev = ts;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---- epilogue ----
+    if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) {
+      fold(a_prev, ts_prev);
+      if (q_row < p.Lq) {
+        const float inv_l = __fdiv_rn(1.f, l);
+        const float* vs = p.vscale + h * HD;
+        const float* vm = p.vmean + h * HD;
+        __nv_bfloat16* o = p.out + q_row * p.o_ss + static_cast<int64_t>(h) * p.o_sh;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int d = c * 8 + 2 * i;
+            w[i] = pack_bf16x2(fmaf(O[d] * inv_l, vs[d], vm[d]), fmaf(O[d + 1] * inv_l, vs[d + 1], vm[d + 1]));
+          }
+          *reinterpret_cast<uint4*>(o + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  __syncwarp();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+}  // namespace rh3
+
+using namespace rh3;
+
+extern "C" int rh3_attn_int8_tok(const void* q8, const float* qs, const void* k8, const float* ksb, const void* vt,
+                                 const float* vscale, const float* vmean, int64_t Lq, int64_t Lq_pad, int64_t Lk,
+                                 int64_t Lk_pad, int64_t H, float softmax_scale, void* out, int64_t o_ss, int64_t o_sh,
+                                 cudaStream_t stream) {
+  RH3_CHECK_ARG(Lq > 0 && Lk > 0 && H > 0 && H < 65536, "attn_int8_tok: bad shape Lq=%lld Lk=%lld H=%lld", (long long)Lq,
+                (long long)Lk, (long long)H);
+  RH3_CHECK_ARG(Lq_pad >= Lq && Lk_pad >= Lk && Lq_pad % 256 == 0 && Lk_pad % 128 == 0,
+                "attn_int8_tok: Lq_pad must be a multiple of 256 and Lk_pad a multiple of 128, covering Lq / Lk");
+  RH3_CHECK_ARG(H * Lq_pad < (1ll << 31) && H * Lk_pad < (1ll << 31), "attn_int8_tok: H * Lpad too large");
+  RH3_CHECK_ARG(q8 && qs && k8 && ksb && vt && vscale && vmean && out, "attn_int8_tok: null pointer");
+  RH3_CHECK_ARG(aligned16(q8) && aligned16(k8) && aligned16(vt) && aligned16(ksb) && aligned16(out) && o_ss % 8 == 0 &&
+                    o_sh % 8 == 0,
+                "attn_int8_tok: operands must be 16-byte aligned, output strides multiples of 8 elements");
+  RH3_CHECK_ARG(softmax_scale > 0.f, "attn_int8_tok: softmax scale must be positive");
+  CUtensorMap tq, tk, tv;
+  if (int e = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q8, HD, H * Lq_pad, HD, HD, QG * BQ,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return e;
+  if (int e = make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k8, HD, H * Lk_pad, HD, HD, BKV,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return e;
+  if (int e = make_tmap_2d(&tv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, vt, Lk_pad, H * HD, Lk_pad, BKV, HD,
+                           CU_TENSOR_MAP_SWIZZLE_128B))
+    return e;
+  TokParams p{};
+  p.qs = qs; p.ksb = ksb; p.vscale = vscale; p.vmean = vmean;
+  p.out = static_cast<__nv_bfloat16*>(out); p.o_ss = o_ss; p.o_sh = o_sh;
+  p.Lq = (int)Lq; p.Lk = (int)Lk; p.Lq_pad = (int)Lq_pad; p.Lk_pad = (int)Lk_pad; p.H = (int)H;
+  p.sl2 = static_cast<float>(static_cast<double>(softmax_scale) * 1.4426950408889634);
+  p.status = device_status_word();
+  const dim3 grid(static_cast<unsigned>((Lq + QG * BQ - 1) / (QG * BQ)), static_cast<unsigned>(H));
+  if (int e = check_cuda(cudaFuncSetAttribute(attn_tok_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TOK_SMEM_BYTES),
+                         "attn_tok smem attribute"))
+    return e;
+  attn_tok_kernel<<<grid, TOK_THREADS, TOK_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  return check_cuda(cudaGetLastError(), "attn_int8_tok launch");
+}
