@@ -232,12 +232,17 @@ def run_reference(args, rank):
     print(json.dumps(rec), flush=True)
 
 
-def workload_config(name, n):
+ATTN_TEXT = {"fast": "int8 QK^T (block-64 scales, K smoothing) + fp8 e4m3 PV",
+             "reference": "int8 QK^T (per-token scales after a 128-point Hadamard rotation, K smoothing) + u8 P x int8 V "
+                          "with a per-tile fold"}
+
+
+def workload_config(name, n, attn="fast"):
     grid, n_audio, batch, text_len, blocks = WORKLOADS[name]
     return {"workload": f"h3_dit_step_{name}", "token_grid": list(grid), "video_tokens": grid[0] * grid[1] * grid[2],
             "audio_tokens": n_audio, "cfg_batch": batch, "text_tokens": text_len, "blocks": blocks, "d_model": 4096,
             "heads": 32, "head_dim": 128, "mlp_hidden": 16384, "linear": "w8a8 int8 row-wise",
-            "attention": "int8 QK^T (block-64 scales, K smoothing) + fp8 e4m3 PV",
+            "attention": ATTN_TEXT[attn],
             "parallelism": "single GPU" if n == 1 else f"sequence-parallel sp{n} (token shards + Ulysses all-to-all)",
             "l2": "every step streams >16 GB of weights and activations, far larger than the 126 MB L2"}
 
@@ -352,6 +357,9 @@ def main():
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
                     help="run the CFG samples of a step side by side on two streams (auto: when N > 1, where it hides "
                          "the exchanges of the sequence-parallel step)")
+    ap.add_argument("--attn", default="fast", choices=["fast", "reference"],
+                    help="attention numerics: fast = block-64 Q/K, e4m3 V and P (the headline kernel); reference = "
+                         "per-token rotated Q/K, int8 V, u8 P against the tile maximum (the reference's production numerics)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the VAE decode timing added to the N=1 step record")
     args = ap.parse_args()
@@ -379,6 +387,9 @@ def main():
     grid, n_audio, batch, text_len, blocks = WORKLOADS[args.workload]
     cfg = H3Config(n_blocks=blocks)
     rt = r.step.H3Runtime.random(cfg, seed=0, device=f"cuda:{local}", mode=args.mode)
+    r.nodes.ATTN_ROTATE = args.attn == "reference"
+    if r.nodes.ATTN_ROTATE and world > 1 and args.exchange == "auto":
+        args.exchange = "nccl"   # the token-scaled kernel has no scattering epilogue
     s_total = grid[0] * grid[1] * grid[2] + n_audio
     # the CFG samples of a step are independent: with --overlap each runs on its own stream, and (N > 1) with its own
     # process group and exchange buffers, so one sample's exchanges hide under the other's kernels
@@ -469,8 +480,10 @@ def main():
                 "frac": achieved / peak8, "ms_per_launch": ph["ms"] / ph["n"], "launches": ph["n"],
                 "share_of_step": ph["ms"] / total_ms, "peak_note": peak_note, "frac_of_nominal_int8": achieved / 4500.0}
 
-    roof = tensor_roof("attn_self_main", "attn_int8_kernel")
-    if roof:
+    roof = tensor_roof("attn_self_main", "attn_tok_kernel" if args.attn == "reference" else "attn_int8_kernel")
+    if roof and args.attn != "fast":
+        roof["traffic"], roof["traffic_unit"] = None, "no capture of the token-scaled kernel"
+    elif roof:
         ph = phases["attn_self_main"]
         lq = lk = s_total
         heads_local = cfg.heads // world
@@ -497,7 +510,7 @@ def main():
     rec = {"metric": "H3 DiT step seconds @768x1344x141f", "value": ms_step / 1e3, "unit": "s/step", "n_gpus": world,
            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": False,
            "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-           "config": workload_config(args.workload, world), "variant": {"linear_mode": args.mode, "exchange": exchange,
+           "config": workload_config(args.workload, world, args.attn), "variant": {"linear_mode": args.mode, "attention": args.attn, "exchange": exchange,
                        "cfg_samples": "side by side on two streams" if side_by_side else "one after the other"},
            "clocks": clocks,
            "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

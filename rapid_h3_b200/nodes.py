@@ -240,6 +240,8 @@ class FusedBlock:
             # both exchanges done by the kernels: rope + scatter to the head owners, attention epilogue scatters back
             if a.q_norm.eps != a.k_norm.eps:
                 raise NotImplementedError("fused exchange: q and k norms must share eps")
+            if ATTN_ROTATE:
+                raise NotImplementedError("the token-scaled attention has no scattering epilogue: use the all-to-all exchange")
             with _phase("exchange_rope_scatter", s * hd * 2 * 3 * 2):
                 qg, kg, vg = sp.rope_scatter(qkv, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps, tab)
             o = sp.attention_scatter(qg, kg, vg)                    # [P, S_local, (H/P)*128] group-major
@@ -253,7 +255,8 @@ class FusedBlock:
                 raw = (q.clone(), k.clone()) if RR_CHECK else None
                 o = attn_int8.attention_rr(q, k, v, tab, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps
                                            if a.q_norm.eps == a.k_norm.eps else self._eps_mismatch(),
-                                           q_roped=q if trace is not None else None, k_roped=k, _tag="self")
+                                           q_roped=q if trace is not None else None, k_roped=k, _tag="self",
+                                           rotate=ATTN_ROTATE)
                 if raw is not None:
                     _rr_check(raw[0], raw[1], v, o, tab, self._norm_w(a.q_norm), self._norm_w(a.k_norm), a.q_norm.eps)
                 rec("qkv_rr", qkv)
@@ -266,7 +269,7 @@ class FusedBlock:
                     attn_int8.rms_rope(k, self._norm_w(a.k_norm), a.k_norm.eps, tab, out=k)
                 with _phase("exchange_all_to_all"):
                     qg, kg, vg = sp.tokens_to_heads(qkv, a.heads, a.head_dim)  # [S_total, H/P, 128] each
-                og = attn_int8.attention(qg, kg, vg, _tag="self")
+                og = attn_int8.attention(qg, kg, vg, _tag="self", rotate=ATTN_ROTATE)
                 with _phase("exchange_all_to_all"):
                     o = sp.heads_to_tokens(og)                          # [P, S_local, (H/P)*128] group-major
                 with _phase("quant_attn_out", qbytes(hd)):
@@ -295,7 +298,8 @@ class FusedBlock:
             if c.q_norm.eps != c.k_norm.eps:
                 self._eps_mismatch()
             oc = attn_int8.attention_rr(qc, kc, vc, None, self._norm_w(c.q_norm), self._norm_w(c.k_norm), c.q_norm.eps,
-                                        q_roped=qc if trace is not None else None, k_roped=kc, _tag="cross")
+                                        q_roped=qc if trace is not None else None, k_roped=kc, _tag="cross",
+                                        rotate=ATTN_ROTATE)
             rec("cross_q", qc), rec("cross_k", kc), rec("cross_v", vc)
             rec("cross_out", oc)
             with _phase("quant_attn_out", qbytes(hd)):
@@ -442,6 +446,12 @@ class RapidH3LinearQuant:
 # switches it on with the path in $RAPIDH3_RRCHECK.
 RR_CHECK = None
 
+# Which attention numerics the fused blocks and the attention override use: False = the fast kernel (block-64 Q/K,
+# e4m3 V and P), True = the reference's production numerics (per-token Q/K after the 128-point Hadamard rotation,
+# int8 V, u8 P against the tile maximum; attn_int8.attention(..., rotate=True)). Set by
+# RapidH3Int8Attention.patch(numerics=...).
+ATTN_ROTATE = False
+
 
 def _rr_check(q, k, v, out, tab, qw, kw, eps, block_index=None):
     """q, k: RAW [S, H, 128] views (copies made before the fused call), v, out as the fused call saw / produced them."""
@@ -470,8 +480,16 @@ class RapidH3Int8Attention:
     (transformer_options["minimax_h3_layout"].segments = [(start, stop, kind)]) whose query rows are recomputed
     with bf16 scaled-dot-product attention after the INT8 kernel has run (the reference's patch-up, :1035-1037)."""
 
-    def patch(self, model, config=80, exact_rows="", previous=None):
-        global RR_CHECK
+    NUMERICS = ["fast", "reference"]
+
+    def patch(self, model, config=80, exact_rows="", previous=None, numerics="fast"):
+        """`numerics`: "fast" = the block-64 / e4m3 kernel (the reference's FP8-P.V family, its configs 50-56);
+        "reference" = the token-scaled kernel with the arithmetic of the reference's production configs
+        (80 / 90 / 94 and their 1xx / 2xx forms). The choice also applies to the fused blocks' own attention calls."""
+        global RR_CHECK, ATTN_ROTATE
+        if numerics not in self.NUMERICS:
+            raise ValueError(numerics)
+        ATTN_ROTATE = rotate = numerics == "reference"
         import os
         import torch.nn.functional as F
         exact = {t.strip() for t in exact_rows.split(",") if t.strip()}
@@ -503,7 +521,7 @@ class RapidH3Int8Attention:
                 return previous(func, q, k, v, **rest) if previous else func(q, k, v, **rest)
             out = torch.empty_like(q)
             attn_int8.attention(q[0].transpose(0, 1), k[0].transpose(0, 1), v[0].transpose(0, 1), scale, config=config,
-                                out=out[0].transpose(0, 1))
+                                rotate=rotate, out=out[0].transpose(0, 1))
             for a, b in exact_spans(kwargs.get("transformer_options"), q.shape[2]):
                 out[:, :, a:b] = F.scaled_dot_product_attention(q[:, :, a:b], k, v, scale=scale)
             return out if skip_output_reshape else out.transpose(1, 2).reshape(1, q.shape[2], -1)
