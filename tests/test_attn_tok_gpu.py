@@ -105,6 +105,17 @@ def test_token_attention_rr_and_strided_output(ops):
     assert torch.equal(qd, raw_q) and torch.equal(kd.cpu(), kn)       # q untouched, k normalised in place
     ref = ot.attention(qn, kn, v)
     assert rel_l2(o[0].transpose(0, 1).cpu(), ref) <= TOL
+    # the reference's own check of this fusion (bench/rmsrope_fuse.py:87-115): RMSNorm + RoPE as a separate pass, then
+    # the plain call, gives the same bits as the fused pre-pass, operand by operand and in the output
+    b2 = buf.cuda()
+    q2, k2, v2 = views(b2, h)
+    qc = attn.rms_rope(q2, qw.cuda(), 1e-5, tab.cuda())
+    kc = attn.rms_rope(k2, kw.cuda(), 1e-5, tab.cuda())
+    plain = attn.tok_prepass(qc, kc, v2)
+    fused = attn.tok_prepass(q2, k2, v2, tab.cuda(), qw.cuda(), kw.cuda(), 1e-5)
+    for name in ("q8", "qs", "k8", "ksb", "vt", "vscale", "vmean", "kmean"):
+        assert torch.equal(getattr(plain, name), getattr(fused, name)), name
+    assert torch.equal(attn.attention_tok_pre(plain), o[0].transpose(0, 1))
 
 
 def test_token_attention_constant_v_and_one_dominant_key(ops):
