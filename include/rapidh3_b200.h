@@ -273,6 +273,11 @@ int rh3_vae_out_quant(const void* o_f16, int64_t B, int64_t H, int64_t S, int64_
  * custom_nodes/rapid_h3/vae_fast.py:71-85). */
 int rh3_vae_quant_rows(const void* x_f16, int64_t ldx, int64_t M, int64_t K, void* q, float* scales,
                        cudaStream_t stream);
+/* The same quantizer with the fused activation prologue of vae_fast._quantize's `act` argument (vae_fast.py:71-85):
+ * act 1 = "rms_norm": x [M, K], y = (x / sqrt(mean(x^2) + eps)) * act_weight (fp16 [K], may be NULL);
+ * act 2 = "swiglu": x [M, 2K] = [gate | up], y = gate / (1 + e^-gate) * up. y is kept in fp32 into the rotation. */
+int rh3_vae_quant_rows_act(const void* x_f16, int64_t ldx, int64_t M, int64_t K, int act, const void* act_weight_f16,
+                           float eps, void* q, float* scales, cudaStream_t stream);
 int rh3_vae_gemm(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws, const void* bias_f16,
                  const void* rscale_f16, const void* resid_f16, int64_t ldr, int64_t M, int64_t N, int64_t K,
                  void* out_f16, int64_t ldo, cudaStream_t stream);

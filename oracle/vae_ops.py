@@ -30,9 +30,48 @@ def fht256(y):
     return v.reshape(m, k)
 
 
-def quant_rows_f16(x):
-    """x fp16 [M, K] -> (q int8 [M, K], scale fp32 [M]): rotation + the fp16-rounded division (vae_ops.cu:139-147)."""
-    y = fht256(nan_to_num_f16(x))
+def _sumsq_rows(x):
+    """Row sums of squares in the kernel's order: the 8 values of a thread in order, an xor butterfly (16, 8, 4, 2, 1)
+    over the 32 threads of a warp (= 256 columns), then the warps in order."""
+    m, k = x.shape
+    sq = (x * x).view(m, k // 256, 32, 8)
+    acc = torch.zeros(m, k // 256, 32, dtype=torch.float32)
+    for j in range(8):
+        acc = acc + sq[..., j]
+    lanes = torch.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        acc = acc + acc[:, :, lanes ^ o]
+    tot = acc[:, 0, 0]
+    for w in range(1, k // 256):
+        tot = tot + acc[:, w, 0]
+    return tot
+
+
+def act_prologue(x, act, weight=None, eps=0.0):
+    """fp32 rows the quantizer rotates: "none" = nan_to_num(x); "rms_norm" = (x * r) * weight with
+    r = 1 / sqrt(mean(x^2) + eps); "swiglu" = gate / (1 + e^-gate) * up of x = [gate | up] (the `act` argument of the
+    quantizer called in custom_nodes/rapid_h3/vae_fast.py:71-85; its per-row arithmetic lives in a third-party binary
+    that is not part of the reference repository, so this definition is this project's own: parity unpinned)."""
+    from .quant import ieee_sqrt
+    v = nan_to_num_f16(x)
+    if act in (None, "none"):
+        return v
+    if act == "rms_norm":
+        k = v.shape[1]
+        r = 1.0 / ieee_sqrt(_sumsq_rows(v) / float(k) + torch.tensor(eps, dtype=torch.float32))
+        y = v * r[:, None]
+        return y * weight.float()[None, :] if weight is not None else y
+    if act == "swiglu":
+        k = v.shape[1] // 2
+        g, u = v[:, :k], v[:, k:]
+        return (g * (1.0 / (1.0 + torch.exp(-g)))) * u
+    raise ValueError(act)
+
+
+def quant_rows_f16(x, act="none", weight=None, eps=0.0):
+    """x fp16 [M, K] -> (q int8 [M, K], scale fp32 [M]): prologue, rotation, the fp16-rounded division
+    (vae_ops.cu:139-147)."""
+    y = fht256(act_prologue(x, act, weight, eps))
     amax = y.abs().amax(dim=1)
     scale = (amax.clamp(max=65504.0) * torch.tensor(1.0 / 127.0, dtype=torch.float32)).clamp_min(1.0e-30)
     sh = scale.half().float()
@@ -56,6 +95,22 @@ def vae_gemm(xq, wq, xs, ws, bias, rscale=None, resid=None):
     if resid is None:
         return y
     return (y.float() * rscale.float()[None, :] + resid.float()).half()
+
+
+def ff_forward(x, norm_w, eps, w1q, w1s, b1, w2q, w2s, b2, residual, residual_scale, swiglu_epilogue=True):
+    """The decoder's feed-forward block on fp16 x [M, K] (custom_nodes/rapid_h3/vae_fast.py:298-318):
+    h = SwiGLU(w1(rms_norm(x))), out = w2(h) * residual_scale + residual. With `swiglu_epilogue` the SwiGLU is w1's
+    GEMM epilogue (h rounded to fp16 once, :265-296), otherwise w1 writes fp16 [M, 2F] and the SwiGLU is the prologue
+    of w2's quantizer. w1q / w1s / b1 are in the module's row order [gate | up]."""
+    n = w1q.shape[0]
+    xq, xs = quant_rows_f16(x, "rms_norm", norm_w, eps)
+    if swiglu_epilogue:
+        h = vae_gemm_swiglu(xq, interleave_rows(w1q, n), xs, interleave_rows(w1s, n), interleave_rows(b1, n))
+        hq, hs = quant_rows_f16(h)
+    else:
+        h = vae_gemm(xq, w1q, xs, w1s, b1)
+        hq, hs = quant_rows_f16(h, "swiglu")
+    return vae_gemm(hq, w2q, hs, w2s, b2, residual_scale, residual)
 
 
 def interleave_rows(t, n):

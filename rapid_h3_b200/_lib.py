@@ -37,6 +37,7 @@ SIGNATURES = {
     "rh3_attn_int8_scatter": [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _P, _P, _I64, _I64, _I64, _P],
     "rh3_vae_out_quant": [_P, _I64, _I64, _I64, _I64, _P, _P, _P],
     "rh3_vae_quant_rows": [_P, _I64, _I64, _I64, _P, _P, _P],
+    "rh3_vae_quant_rows_act": [_P, _I64, _I64, _I64, _I, _P, _F, _P, _P, _P],
     "rh3_vae_gemm": [_P, _I64, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _I64, _P],
     "rh3_vae_gemm_swiglu": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I64, _P, _I64, _P],
     "rh3_gemm_w8a8": [_P, _I64, _P, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I64, _P, _P],

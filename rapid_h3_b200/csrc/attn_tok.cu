@@ -16,13 +16,15 @@
 //   O = ts * A + a * O        the per-tile fold, fp32, in registers
 //   out = bf16((O / l) * vscale + vmean)
 //
-// Integers become floats without a conversion instruction: for |x| < 2^22 the int32 x + 0x4B400000 is the bit
-// pattern of the float 1.5*2^23 + x, and subtracting 1.5*2^23 from that float is exact.
+// Integers become floats without a conversion instruction: both accumulators are pre-biased with 0x4B400000 (the
+// softmax warps store it into TMEM before each tile's MMAs, which then accumulate onto it), so for |x| < 2^22 their
+// bits are the float 1.5*2^23 + x, and subtracting 1.5*2^23 from that float is exact. The per-score arithmetic runs
+// two values per instruction (fma/add/mul.rn.f32x2).
 //
 // One CTA = two 128-query tiles of one head, 384 threads: warp 0 = TMA producer (K tile, V^T tile and the 1 KB of
 // key scales / biases per step, 3-stage ring), warp 1 = MMA issuer, warps 4..11 = softmax, one query row per
 // thread with its 128 fp32 output values in registers (232 registers per softmax thread after the register
-// re-split). The scores are read from TMEM twice, 32 columns at a time (maximum, then exponentials), so that the
+// re-split). The scores are read from TMEM twice, 16 columns at a time (maximum, then exponentials), so that the
 // output row fits beside them. TMEM (512 columns): S0 | S1 | A0 | A1.
 #include <limits.h>
 
@@ -72,14 +74,37 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// exact float value of an int32 of magnitude below 2^22
-__device__ __forceinline__ float int_as_float_exact(uint32_t x) {
-  return __fsub_rn(__uint_as_float(x + kMagicBits), kMagic);
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
 }
-__device__ __forceinline__ float4 lds4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-  return v;
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// two fp32 operations per instruction
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// The accumulators are pre-biased with 1.5*2^23 (see the kernel), so their bits ARE the float 1.5*2^23 + x; for
+// |x| < 2^22 subtracting the bias is exact: two exact integer values per instruction.
+__device__ __forceinline__ uint64_t unbias2(uint32_t lo, uint32_t hi) {
+  return add2(pack2(__uint_as_float(lo), __uint_as_float(hi)), pack2(-kMagic, -kMagic));
+}
+__device__ __forceinline__ void lds4x2(uint32_t addr, uint64_t& a, uint64_t& b) {
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
 }
 // plain (untiled) bulk copy global -> shared, completion counted on an mbarrier; 16-byte aligned, size % 16 == 0
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -94,36 +119,57 @@ static_assert(128 * REGS_SERVICE + 256 * REGS_SOFTMAX == TOK_THREADS * REGS_COMP
 __device__ __forceinline__ void reg_release_service() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
 __device__ __forceinline__ void reg_take_softmax() { asm volatile("setmaxnreg.inc.sync.aligned.u32 232;"); }
 
-// Maximum over one 32-column chunk of t = s * kscale + kbias.
-__device__ __forceinline__ float chunk_tmax(const uint32_t* r, uint32_t ks_addr, uint32_t kb_addr, float tm) {
+// t = x * kscale for four columns; on the last key tile (`bias`, uniform over the CTA) the bias is added, which is 0
+// for real keys and -inf for the padding keys. rn(x * s) + 0 is the same number as fma(x, s, 0).
+__device__ __forceinline__ void scores4(const uint32_t* r, uint32_t ks_addr, uint32_t kb_addr, bool bias, uint64_t& t01,
+                                        uint64_t& t23) {
+  uint64_t s01, s23;
+  lds4x2(ks_addr, s01, s23);
+  t01 = mul2(unbias2(r[0], r[1]), s01);
+  t23 = mul2(unbias2(r[2], r[3]), s23);
+  if (bias) {
+    uint64_t b01, b23;
+    lds4x2(kb_addr, b01, b23);
+    t01 = add2(t01, b01);
+    t23 = add2(t23, b23);
+  }
+}
+
+// Maximum over one 16-column chunk of t.
+__device__ __forceinline__ float chunk_tmax(const uint32_t* r, uint32_t ks_addr, uint32_t kb_addr, bool bias, float tm) {
 #pragma unroll
-  for (int i = 0; i < 32; i += 4) {
-    const float4 s4 = lds4(ks_addr + i * 4), b4 = lds4(kb_addr + i * 4);
-    const float t0 = fmaf(int_as_float_exact(r[i]), s4.x, b4.x), t1 = fmaf(int_as_float_exact(r[i + 1]), s4.y, b4.y);
-    const float t2 = fmaf(int_as_float_exact(r[i + 2]), s4.z, b4.z), t3 = fmaf(int_as_float_exact(r[i + 3]), s4.w, b4.w);
+  for (int i = 0; i < 16; i += 4) {
+    uint64_t t01, t23;
+    scores4(r + i, ks_addr + i * 4, kb_addr + i * 4, bias, t01, t23);
+    float t0, t1, t2, t3;
+    unpack2(t01, t0, t1);
+    unpack2(t23, t2, t3);
     tm = fmaxf(fmaxf(tm, fmaxf(t0, t1)), fmaxf(t2, t3));
   }
   return tm;
 }
 
-// One 32-column chunk: P = u8(rint(2^(t * c + off))) written to 16-byte chunks 2k, 2k+1 of the row of P in shared
-// memory (XOR-swizzled like the TMA tiles), the integer codes added to `rs`.
-__device__ __forceinline__ void chunk_p(const uint32_t* r, uint32_t ks_addr, uint32_t kb_addr, float c, float off, int k,
-                                        uint8_t* p_row, int sw, uint32_t& rs) {
-  uint32_t w[8];
+// One 16-column chunk: P = u8(rint(2^(t * c + off))) written to 16-byte chunk k of the row of P in shared memory
+// (XOR-swizzled like the TMA tiles), the integer codes added to `rs`.
+__device__ __forceinline__ void chunk_p(const uint32_t* r, uint32_t ks_addr, uint32_t kb_addr, bool bias, float c, float off,
+                                        int k, uint8_t* p_row, int sw, uint32_t& rs) {
+  const uint64_t c2 = pack2(c, c), off2 = pack2(off, off), magic2 = pack2(kMagic, kMagic);
+  uint32_t w[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float4 s4 = lds4(ks_addr + i * 16), b4 = lds4(kb_addr + i * 16);
-    const float t0 = fmaf(int_as_float_exact(r[4 * i]), s4.x, b4.x), t1 = fmaf(int_as_float_exact(r[4 * i + 1]), s4.y, b4.y);
-    const float t2 = fmaf(int_as_float_exact(r[4 * i + 2]), s4.z, b4.z), t3 = fmaf(int_as_float_exact(r[4 * i + 3]), s4.w, b4.w);
+  for (int i = 0; i < 4; ++i) {
+    uint64_t t01, t23;
+    scores4(r + 4 * i, ks_addr + i * 16, kb_addr + i * 16, bias, t01, t23);
+    float e0, e1, e2, e3;
+    unpack2(fma2(t01, c2, off2), e0, e1);
+    unpack2(fma2(t23, c2, off2), e2, e3);
     // p <= 255 * (1 + 2^-20): adding 1.5*2^23 leaves rint(p) (ties to even) in the low byte
-    const float p0 = __fadd_rn(ex2_approx(fmaf(t0, c, off)), kMagic), p1 = __fadd_rn(ex2_approx(fmaf(t1, c, off)), kMagic);
-    const float p2 = __fadd_rn(ex2_approx(fmaf(t2, c, off)), kMagic), p3 = __fadd_rn(ex2_approx(fmaf(t3, c, off)), kMagic);
+    float p0, p1, p2, p3;
+    unpack2(add2(pack2(ex2_approx(e0), ex2_approx(e1)), magic2), p0, p1);
+    unpack2(add2(pack2(ex2_approx(e2), ex2_approx(e3)), magic2), p2, p3);
     w[i] = pack_low_bytes(__float_as_uint(p0), __float_as_uint(p1), __float_as_uint(p2), __float_as_uint(p3));
     rs = __dp4a(w[i], 0x01010101u, rs);
   }
-  *reinterpret_cast<uint4*>(p_row + (((2 * k) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-  *reinterpret_cast<uint4*>(p_row + (((2 * k + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+  *reinterpret_cast<uint4*>(p_row + ((k ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 __global__ void __launch_bounds__(TOK_THREADS, 1)
@@ -192,22 +238,27 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       auto issue_qk = [&](int g, int j) {
         const uint32_t q_addr = smem_u32(sQ + g * TILE_BYTES);
         const uint32_t k_addr = smem_u32(sKV + (j % KV_STAGES) * STAGE_BYTES);
-        mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 0);
+        mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 1);  // onto the bias
         mma_commit(&tail->s_full[g]);
       };
       bool ok = mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
                 mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
-      if (ok) {
-        tc_fence_after();
-        for (int g = 0; g < QG; ++g) issue_qk(g, 0);
+      for (int g = 0; g < QG && ok; ++g) {
+        // completion 0 of s_empty: the softmax warps have biased both accumulators of this query tile
+        ok = mbar_wait(&tail->s_empty[g], 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
+        if (ok) {
+          tc_fence_after();
+          issue_qk(g, 0);
+        }
       }
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) {
           const int ns = (j + 1) % KV_STAGES;
           ok = mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 64);
           for (int g = 0; g < QG && ok; ++g) {
-            // completion j of s_empty: the softmax warps have read the scores of key tile j for the last time
-            ok = mbar_wait_relaxed(&tail->s_empty[g], j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64);
+            // completion j+1 of s_empty: the softmax warps have read the scores of key tile j for the last time and
+            // put the bias back
+            ok = mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64);
             if (ok) {
               tc_fence_after();
               issue_qk(g, j + 1);
@@ -223,7 +274,7 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
           if (!ok) break;
           tc_fence_after();
           const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);
-          mma4_i8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, 0);
+          mma4_i8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, 1);  // onto the bias
           mma_commit(&tail->pv_done[g]);
         }
         if (ok) mma_commit(&tail->kv_empty[stage]);
@@ -246,40 +297,67 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     uint64_t* s_empty = &tail->s_empty[g];
     uint64_t* p_full = &tail->p_full[g];
     uint64_t* pv_done = &tail->pv_done[g];
-    float O[HD];
+    float O[HD];   // the output row
 #pragma unroll
     for (int i = 0; i < HD; ++i) O[i] = 0.f;
     float m = -INFINITY, l = 0.f, a_prev = 0.f, ts_prev = 0.f;
     bool ok = true;
 
-    // O = ts * A + a * O for the tile whose P.V has just finished
-    auto fold = [&](float a, float ts) {
+    auto splat4 = [](uint32_t base) {
+      tmem_st32_splat(base, kMagicBits);
+      tmem_st32_splat(base + 32, kMagicBits);
+      tmem_st32_splat(base + 64, kMagicBits);
+      tmem_st32_splat(base + 96, kMagicBits);
+    };
+    // O = ts * A + a * O for the tile whose P.V has just finished; the accumulator gets its bias back
+    auto fold = [&](float a, float ts, bool rebias) {
       tc_fence_after();
+      // two register sets: the load of the next 16 columns is in flight while these are folded
+      uint32_t ra[16], rb[16];
+      tmem_ld16_async(a_row, ra);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(a_row + c * 32, r);
-        tmem_ld_wait_regs(r);
+      for (int c = 0; c < 8; ++c) {
+        uint32_t* r = (c & 1) ? rb : ra;
+        tmem_ld_wait16(r);
+        if (c + 1 < 8) tmem_ld16_async(a_row + (c + 1) * 16, (c & 1) ? ra : rb);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) O[c * 32 + i] = fmaf(ts, int_as_float_exact(r[i]), __fmul_rn(O[c * 32 + i], a));
+        for (int i = 0; i < 16; ++i)
+          O[c * 16 + i] = fmaf(ts, __fsub_rn(__uint_as_float(r[i]), kMagic), __fmul_rn(O[c * 16 + i], a));
+      }
+      if (rebias) {
+        splat4(a_row);
+        tmem_st_wait();
       }
     };
+
+    // bias both accumulators of this query tile for key tile 0
+    splat4(t_row);
+    splat4(a_row);
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(s_empty);
 
     for (int j = 0; j < n_kv; ++j) {
       const int stage = j % KV_STAGES;
       const uint32_t ks_addr = smem_u32(sKV + stage * STAGE_BYTES + 2 * TILE_BYTES), kb_addr = ks_addr + BKV * 4;
+      const bool last = j == n_kv - 1;   // only the last key tile has padding keys (bias -inf)
       // the key scales of this stage came by bulk copy: observe its barrier before reading them
       if (!mbar_wait_relaxed(&tail->kv_full[stage], (j / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 32)) { ok = false; break; }
       if (!mbar_wait_relaxed(s_full, j & 1, abort_flag, p.status, ST_TIMEOUT_ACC_FULL, 32)) { ok = false; break; }
       tc_fence_after();
       // ---- pass 1: the tile's row maximum ----
       float tm = -INFINITY;
+      {
+        uint32_t ra[16], rb[16];
+        tmem_ld16_async(t_row, ra);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_row + c * 32, r);
-        tmem_ld_wait_regs(r);
-        tm = chunk_tmax(r, ks_addr + c * 128, kb_addr + c * 128, tm);
+        for (int c = 0; c < 8; ++c) {
+          uint32_t* r = (c & 1) ? rb : ra;
+          tmem_ld_wait16(r);
+          if (c + 1 < 8) tmem_ld16_async(t_row + (c + 1) * 16, (c & 1) ? ra : rb);
+          tm = chunk_tmax(r, ks_addr + c * 64, kb_addr + c * 64, last, tm);
+        }
       }
       const float tmc = __fmul_rn(tm, c_row);
       const float m_new = fmaxf(m, tmc);
@@ -289,22 +367,26 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (j > 0) {
         // P.V of the previous tile has finished: fold its accumulator; the P buffer is free again
         if (!mbar_wait_relaxed(pv_done, (j - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE, 32)) { ok = false; break; }
-        fold(a_prev, ts_prev);
+        fold(a_prev, ts_prev, true);
       }
       // ---- pass 2: P into shared memory, integer row sum ----
       uint32_t rs = 0;
+      uint32_t ra[16], rb[16];
+      tmem_ld16_async(t_row, ra);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(t_row + c * 32, r);
-        tmem_ld_wait_regs(r);
-        if (c == 3) {
-          // the scores have been read for the last time: the next Q.K^T may overwrite them
+      for (int c = 0; c < 8; ++c) {
+        uint32_t* r = (c & 1) ? rb : ra;
+        tmem_ld_wait16(r);
+        if (c + 1 < 8) tmem_ld16_async(t_row + (c + 1) * 16, (c & 1) ? ra : rb);
+        if (c == 7) {
+          // the scores have been read for the last time: bias the accumulator for the next Q.K^T and hand it back
+          splat4(t_row);
+          tmem_st_wait();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(s_empty);
         }
-        chunk_p(r, ks_addr + c * 128, kb_addr + c * 128, c_row, off, c, p_row, sw, rs);
+        chunk_p(r, ks_addr + c * 64, kb_addr + c * 64, last, c_row, off, c, p_row, sw, rs);
       }
       l = fmaf(ts, static_cast<float>(rs), __fmul_rn(l, a));
       a_prev = a;
@@ -316,7 +398,7 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
     }
     // ---- epilogue ----
     if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, abort_flag, p.status, ST_TIMEOUT_PV_DONE)) {
-      fold(a_prev, ts_prev);
+      fold(a_prev, ts_prev, false);
       if (q_row < p.Lq) {
         const float inv_l = __fdiv_rn(1.f, l);
         const float* vs = p.vscale + h * HD;

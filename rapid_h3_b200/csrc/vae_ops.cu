@@ -76,7 +76,13 @@ __device__ __forceinline__ void fht256(float* x, int lane) {
   }
 }
 
+enum { ACT_NONE = 0, ACT_RMS_NORM = 1, ACT_SWIGLU = 2 };
+
 struct OutQuantParams {
+  int act;                // prologue applied to the loaded row before the rotation
+  const __half* act_w;    // ACT_RMS_NORM: norm weight [K] or null
+  float eps;              // ACT_RMS_NORM
+  int64_t up_offset;      // ACT_SWIGLU: the "up" half of a row starts this many elements after the gate half
   const __half* o;
   int8_t* q;
   float* scales;
@@ -105,6 +111,43 @@ __global__ void __launch_bounds__(T) vae_out_quant_kernel(const OutQuantParams p
     } else {
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+    if (p.act == ACT_RMS_NORM) {
+      // y = (x * r) * w, r = 1 / sqrt(mean(x^2) + eps); the sum of squares in a fixed order: the 8 values of a
+      // thread in order, an xor butterfly over the warp, then the warps in order
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(v[j], v[j]));
+      ss = warp_sum_xor(ss);
+      if ((tid & 31) == 0) red[tid >> 5] = ss;
+      __syncthreads();
+      ss = red[0];
+#pragma unroll
+      for (int w = 1; w < T / 32; ++w) ss = __fadd_rn(ss, red[w]);
+      __syncthreads();
+      const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, static_cast<float>(K)), p.eps)));
+      if (active) {
+        float wv[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+        if (p.act_w) {
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.act_w + col));
+          const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) wv[j] = __half2float(h[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], r), wv[j]);
+      }
+    } else if (p.act == ACT_SWIGLU) {
+      // y = silu(gate) * up with gate = this row's first K values, up = the K values up_offset further on
+      if (active) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p.o + head * p.head_stride + row * p.row_stride + d + p.up_offset));
+        const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float g = v[j], u = nan_to_num_h(h[j]);
+          v[j] = __fmul_rn(__fmul_rn(g, __fdiv_rn(1.f, __fadd_rn(1.f, expf(-g)))), u);
+        }
+      }
     }
     if (tid - (tid & 31) < (K >> 3)) fht256(v, tid & 31);  // warp-uniform: K is a multiple of 256
     float am = 0.f;
@@ -183,8 +226,8 @@ extern "C" int rh3_vae_out_quant(const void* o_f16, int64_t B, int64_t H, int64_
   return 0;
 }
 
-// The same row arithmetic on a row-major fp16 matrix x [M, K] (row stride ldx): the plain-activation case of the
-// quantizer the decoder's linears call on their inputs (vae_fast._quantize, custom_nodes/rapid_h3/vae_fast.py:71-85).
+// The same row arithmetic on a row-major fp16 matrix x [M, K] (row stride ldx): the quantizer the decoder's linears
+// call on their inputs (vae_fast._quantize, custom_nodes/rapid_h3/vae_fast.py:71-85).
 extern "C" int rh3_vae_quant_rows(const void* x_f16, int64_t ldx, int64_t M, int64_t K, void* q, float* scales,
                                   cudaStream_t stream) {
   RH3_CHECK_ARG(M >= 0 && K > 0 && K % 256 == 0 && K <= 8192, "vae_quant_rows: K=%lld must be a multiple of 256, <= 8192",
@@ -195,6 +238,37 @@ extern "C" int rh3_vae_quant_rows(const void* x_f16, int64_t ldx, int64_t M, int
   RH3_CHECK_ARG((reinterpret_cast<uintptr_t>(x_f16) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
                 "vae_quant_rows: x must be 16-byte aligned and q 8-byte aligned");
   OutQuantParams p{};
+  p.o = static_cast<const __half*>(x_f16);
+  p.q = static_cast<int8_t*>(q);
+  p.scales = scales;
+  p.K = (int)K; p.D = 256; p.head_stride = 256; p.row_stride = ldx; p.rows = M;
+  return out_quant_launch(p, stream);
+}
+
+// The quantizer with a fused activation prologue (the `act` argument of the quantizer the reference calls in
+// vae_fast._quantize, vae_fast.py:71-85: "rms_norm" for the inputs of to_qkv and w1, "swiglu" for the input of w2
+// when the SwiGLU is not in w1's epilogue). act 1: x [M, K], y = (x * r) * weight (fp16 [K] or NULL),
+// r = 1 / sqrt(mean(x^2) + eps); act 2: x [M, 2K] = [gate | up], y = gate / (1 + e^-gate) * up. y stays fp32 into
+// the rotation. The per-row arithmetic of that fused form lives in a third-party binary (comfy-kitchen) whose source
+// is not part of the reference repository; this entry defines it with IEEE operations (CPU oracle: oracle/vae_ops.py).
+extern "C" int rh3_vae_quant_rows_act(const void* x_f16, int64_t ldx, int64_t M, int64_t K, int act,
+                                      const void* act_weight_f16, float eps, void* q, float* scales,
+                                      cudaStream_t stream) {
+  RH3_CHECK_ARG(act == ACT_RMS_NORM || act == ACT_SWIGLU, "vae_quant_rows_act: act must be 1 (rms_norm) or 2 (swiglu)");
+  RH3_CHECK_ARG(M >= 0 && K > 0 && K % 256 == 0 && K <= 8192, "vae_quant_rows_act: K=%lld must be a multiple of 256, <= 8192",
+                (long long)K);
+  RH3_CHECK_ARG(M < (1ll << 31) && ldx >= (act == ACT_SWIGLU ? 2 * K : K) && ldx % 8 == 0,
+                "vae_quant_rows_act: bad M or row stride");
+  if (M == 0) return 0;
+  RH3_CHECK_ARG(x_f16 && q && scales, "vae_quant_rows_act: null pointer");
+  RH3_CHECK_ARG((reinterpret_cast<uintptr_t>(x_f16) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(act_weight_f16) & 15) == 0,
+                "vae_quant_rows_act: x and the norm weight must be 16-byte aligned and q 8-byte aligned");
+  OutQuantParams p{};
+  p.act = act;
+  p.act_w = act == ACT_RMS_NORM ? static_cast<const __half*>(act_weight_f16) : nullptr;
+  p.eps = eps;
+  p.up_offset = K;
   p.o = static_cast<const __half*>(x_f16);
   p.q = static_cast<int8_t*>(q);
   p.scales = scales;

@@ -192,6 +192,16 @@ class VAEDecoder:
                 total += 2 * sites * c * self.widths[si + 1] * 27
         return total + 2 * sites * self.widths[-1] * 192 * 27
 
+    RATIO = 32  # output pixels per latent cell along height and width
+
+    def tiled_decode(self, latent, tile=512, overlap=128, batch=4):
+        """Decode in spatial tiles of `tile` output pixels sharing `overlap` pixels, `batch` tiles per decoder call
+        across tile rows, seams cross-faded (vae_fast.tiled_decode_batched; the reference's whole-chunk tile
+        batching, custom_nodes/rapid_h3/vae_fast.py:336-400). For latents whose activations do not fit at once; the
+        GroupNorm statistics are then per tile, so the picture is not the untiled one."""
+        from . import vae_fast
+        return vae_fast.tiled_decode_batched(lambda z: self.decode(z.contiguous()), latent, self.RATIO, tile, overlap, batch)
+
     def decode(self, latent, sp=None):
         """latent [N, C, T, H, W] bf16 -> RGB [N, 3, 4T-3, 32H, 32W] bf16 (with `sp`: this rank's frames).
         With `sp` every activation that feeds a convolution is produced straight into a halo-padded buffer, the

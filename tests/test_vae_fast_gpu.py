@@ -118,3 +118,78 @@ def test_vae_linear_end_to_end(vf):
     xq, xs = ov.quant_rows_f16(x)
     assert torch.equal(y.cpu(), ov.vae_gemm(xq, wq, xs, ws, b, rs, resid))
     del ol
+
+
+@pytest.mark.parametrize("shape", [(1000, 2048), (77, 8192), (5, 256)])
+@pytest.mark.parametrize("with_weight", [True, False])
+def test_vae_quantizer_rms_norm_prologue(vf, shape, with_weight):
+    """`act="rms_norm"`: the quantizer of the inputs of to_qkv and w1. Scales bit-exact, codes bit-exact (every
+    operation of the prologue is an IEEE operation in a fixed order)."""
+    vae_fast, lib = vf
+    g = inputs.gen(shape[0] + 1)
+    x = (torch.randn(shape, generator=g) * (0.5 + torch.rand(shape[0], 1, generator=g))).half()
+    x[:, 5] *= 25.0
+    if shape[0] > 3:
+        x[3] = 0
+    w = (1 + 0.2 * torch.randn(shape[1], generator=g)).half() if with_weight else None
+    q, s = vae_fast._quantize(x.cuda(), "rms_norm", None if w is None else w.cuda(), 1e-6)
+    lib.check_status()
+    qr, sr = ov.quant_rows_f16(x, "rms_norm", w, 1e-6)
+    assert torch.equal(s.cpu().reshape(-1), sr) and torch.equal(q.cpu(), qr)
+
+
+@pytest.mark.parametrize("shape", [(700, 2048), (33, 4096)])
+def test_vae_quantizer_swiglu_prologue(vf, shape):
+    """`act="swiglu"`: x = [gate | up]. The device's expf may differ from the CPU's in the last place, so codes are
+    held to the reference's own criterion for fused quantizers (at most one step apart on < 1e-3 of the elements,
+    bench/rot_test.py:36-40) and scales to 1e-6."""
+    vae_fast, lib = vf
+    m, k = shape
+    x = torch.randn(m, 2 * k, generator=inputs.gen(m)).half()
+    q, s = vae_fast._quantize(x.cuda(), "swiglu")
+    lib.check_status()
+    qr, sr = ov.quant_rows_f16(x, "swiglu")
+    assert q.shape == (m, k)
+    assert torch.allclose(s.cpu().reshape(-1), sr, rtol=1e-6, atol=0)
+    d = (q.cpu().int() - qr.int()).abs()
+    assert d.max() <= 1 and (d != 0).float().mean() < 1e-3
+
+
+@pytest.mark.parametrize("epilogue", [True, False])
+def test_vae_ff_forward(vf, epilogue):
+    """The decoder's feed-forward block (rms_norm -> w1 -> SwiGLU -> w2 -> * residual_scale + residual) on its two
+    routes: SwiGLU in w1's epilogue, or as the prologue of w2's quantizer. Decoder shapes: dim 2048, hidden 8192."""
+    vae_fast, lib = vf
+    g = inputs.gen(21)
+    m, k, f = 600, 2048, 8192
+
+    def rotated_weight(n, kk):
+        w = (torch.randn(n, kk, generator=g) / kk ** 0.5).half()
+        wr = ov.fht256(w.float())
+        ws = wr.abs().amax(dim=1) / 127.0
+        return w, (wr / ws[:, None]).round().clamp(-127, 127).to(torch.int8), ws
+
+    w1, w1q, w1s = rotated_weight(2 * f, k)
+    w2, w2q, w2s = rotated_weight(k, f)
+    b1, b2 = (0.05 * torch.randn(2 * f, generator=g)).half(), (0.05 * torch.randn(k, generator=g)).half()
+    x = torch.randn(m, k, generator=g).half()
+    nw = (1 + 0.1 * torch.randn(k, generator=g)).half()
+    resid, rs = torch.randn(m, k, generator=g).half(), (1 + 0.1 * torch.randn(k, generator=g)).half()
+    l1 = vae_fast.Int8Linear(w1q.cuda(), w1s.cuda(), b1.cuda())
+    l2 = vae_fast.Int8Linear(w2q.cuda(), w2s.cuda(), b2.cuda())
+    vae_fast.install_swiglu(epilogue)
+    try:
+        y = vae_fast._ff_forward(l1, l2, x.cuda().view(2, m // 2, k), nw.cuda(), 1e-6, resid.cuda().view(2, m // 2, k), rs.cuda())
+    finally:
+        vae_fast.install_swiglu(True)
+    lib.check_status()
+    assert y.shape == (2, m // 2, k) and y.dtype == torch.float16
+    ref = ov.ff_forward(x, nw, 1e-6, w1q, w1s, b1, w2q, w2s, b2, resid, rs, swiglu_epilogue=epilogue)
+    rel = ((y.cpu().reshape(m, k).float() - ref.float()).norm() / ref.float().norm()).item()
+    assert rel < 1e-3          # the SwiGLU exponential is the only inexact step between the two sides
+    # and the quantized block stays close to the fp32 block
+    xn = x.float() * torch.rsqrt(x.float().pow(2).mean(1, keepdim=True) + 1e-6) * nw.float()
+    hh = xn @ w1.float().t() + b1.float()
+    hh = torch.nn.functional.silu(hh[:, :f]) * hh[:, f:]
+    full = (hh @ w2.float().t() + b2.float()) * rs.float() + resid.float()
+    assert ((y.cpu().reshape(m, k).float() - full).norm() / full.norm()).item() < 2e-2

@@ -156,3 +156,30 @@ def test_depth_to_space_is_the_head_permutation(vae):
     lib.check_status()
     ref = y.view(n, t, h, w, 3, 8, 8).permute(0, 4, 1, 2, 5, 3, 6).reshape(n, 3, t, h * 8, w * 8)
     assert torch.equal(rgb, ref)
+
+
+def test_tiled_decode_batches_tiles_across_rows(vae):
+    """Spatial tiles, several per decoder call: every decoder call sees at least two tiles, the canvas has the
+    untiled shape, and a region no seam touches equals that tile decoded in the same group (the per-tile arithmetic
+    does not depend on the other tiles of the call: every op is per sample)."""
+    v, lib = vae
+    from rapid_h3_b200 import vae_fast
+    dec = v.VAEDecoder(seed=4, widths=(128, 64, 64), blocks_per_stage=1)
+    latent = torch.randn(1, 16, 2, 5, 7, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16).cuda()
+    calls = []
+    plain_decode = dec.decode
+
+    def counting(z, sp=None):
+        calls.append(z.shape[0])
+        return plain_decode(z, sp)
+
+    dec.decode = counting
+    rgb = dec.tiled_decode(latent, tile=96, overlap=32, batch=3)
+    lib.check_status()
+    assert rgb.shape == (1, 3, 5, 160, 224) and torch.isfinite(rgb.float()).all()
+    ny, nx = len(vae_fast.split_tiles(160, 96, 32)[0]), len(vae_fast.split_tiles(224, 96, 32)[0])
+    assert calls == vae_fast._tile_groups(ny * nx, 3) and min(calls) >= 2
+    # tile (0, 0): its first 64 x 64 pixels lie before the first seams
+    first = torch.cat([latent[..., 0:3, 0:3], latent[..., 0:3, 2:5], latent[..., 0:3, 4:7]])[: calls[0]]
+    alone = plain_decode(first.contiguous())[0:1]
+    assert torch.equal(rgb[..., :64, :64], alone[..., :64, :64])
