@@ -44,6 +44,8 @@ def main():
     ap.add_argument("--Cin", type=int, default=512)
     ap.add_argument("--Cout", type=int, default=512)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--rotate", action="store_true", help="attn / prepass: the token-scaled numerics")
+    ap.add_argument("--rope", action="store_true", help="prepass: with the per-head RMSNorm + RoPE fused in")
     a = ap.parse_args()
     g = torch.Generator(device="cuda").manual_seed(0)
 
@@ -69,14 +71,20 @@ def main():
         q = randn(a.L, a.H, 128).to(torch.bfloat16)
         k = (randn(a.L, a.H, 128) + 2 * randn(1, a.H, 128)).to(torch.bfloat16)
         v = randn(a.L, a.H, 128).to(torch.bfloat16)
+        pre_fn = attn_int8.tok_prepass if a.rotate else attn_int8.int8_prepass
+        main_fn = attn_int8.attention_tok_pre if a.rotate else attn_int8.attention_pre
         if a.case == "prepass":
-            ms = _time(lambda: attn_int8.int8_prepass(q, k, v), a.iters)
-            print(f"prepass L={a.L} H={a.H}: {ms:.3f} ms")
+            args = ()
+            if a.rope:
+                w = torch.ones(128, device="cuda", dtype=torch.bfloat16)
+                args = (randn(a.L, 48, 2, 2).to(torch.bfloat16), w, w, 1e-5, None, k)
+            ms = _time(lambda: pre_fn(q, k, v, *args), a.iters)
+            print(f"prepass L={a.L} H={a.H} rotate={a.rotate} rope={a.rope}: {ms:.3f} ms")
             return
-        pre = attn_int8.int8_prepass(q, k, v)
+        pre = pre_fn(q, k, v)
         out = torch.empty(a.L, a.H, 128, device="cuda", dtype=torch.bfloat16)
-        ms = _time(lambda: attn_int8.attention_pre(pre, out=out), a.iters)
-        print(f"attn L={a.L} H={a.H}: {ms:.3f} ms, {4 * a.L * a.L * 128 * a.H / ms / 1e9:.1f} TFLOP/s")
+        ms = _time(lambda: main_fn(pre, out=out), a.iters)
+        print(f"attn L={a.L} H={a.H} rotate={a.rotate}: {ms:.3f} ms, {4 * a.L * a.L * 128 * a.H / ms / 1e9:.1f} TFLOP/s")
     elif a.case == "gemm":
         xq = torch.randint(-127, 128, (a.M, a.K), device="cuda", dtype=torch.int8, generator=g)
         wq = torch.randint(-127, 128, (a.N, a.K), device="cuda", dtype=torch.int8, generator=g)
