@@ -10,6 +10,7 @@ counterpart in the reference (parity unpinned); it is built from the same quanti
 import torch
 
 from . import attention as oa
+from . import attention_tok as ot
 from . import linear as ol
 from . import quant as oq
 
@@ -21,14 +22,17 @@ def _qlinear(x, weight):
 
 
 def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None, mode="int8_rowwise", adaln=None,
-                replay=None):
-    """`adaln`: the six fp32 modulation tables, when the caller wants the block checked on given tables (the AdaLN
+                replay=None, attn="fast"):
+    """`attn`: "fast" = the block-64 / e4m3 attention (oracle.attention), "token" = the token-scaled one
+    (oracle.attention_tok), for self- and cross-attention alike.
+    `adaln`: the six fp32 modulation tables, when the caller wants the block checked on given tables (the AdaLN
     projection is a plain bf16 matrix product of the host framework whose summation order differs between devices;
     it is an input of the quantized path, not part of it).
     `replay`: {"x_attn": ..., "x_cross": ...}: residual streams to start the cross-attention and the MLP stage from,
     instead of this function's own (a checker passes what the device produced, so that every stage is compared on
     identical inputs and a last-bit difference of one stage is not amplified through the next quantizer)."""
     s, d = x.shape
+    attention = {"fast": oa.attention, "token": ot.attention}[attn]
     a = block.attn
     hd = a.heads * a.head_dim
     sh1, sc1, g1, sh2, sc2, g2 = block.adaln_proj(t_emb) if adaln is None else adaln
@@ -63,7 +67,7 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None,
     q = oa.rmsnorm_rope(q, a.q_norm.weight.detach(), a.q_norm.eps, tab)
     k = oa.rmsnorm_rope(k, a.k_norm.weight.detach(), a.k_norm.eps, tab)
     rec("qkv_rr", torch.cat([q.reshape(s, hd), k.reshape(s, hd), v.reshape(s, hd)], 1))
-    o = oa.attention(q, k, v)
+    o = attention(q, k, v)
     rec("attn_out", o)
     oq8, os_ = ol.quantize_rows(o.reshape(s, hd), mode)
     wq, ws = q_weight(a.out_proj)
@@ -87,7 +91,7 @@ def fused_block(block, x, t_emb, mod_segments, rope_freqs, ctx=None, trace=None,
         qc = oa.rmsnorm_rope(qc, c.q_norm.weight.detach(), c.q_norm.eps, None)
         kc = oa.rmsnorm_rope(kc, c.k_norm.weight.detach(), c.k_norm.eps, None)
         rec("cross_q", qc), rec("cross_k", kc), rec("cross_v", vc)
-        oc = oa.attention(qc, kc, vc)
+        oc = attention(qc, kc, vc)
         rec("cross_out", oc)
         oq8, os_ = ol.quantize_rows(oc.reshape(s, hd), mode)
         wq, ws = q_weight(c.out_proj)

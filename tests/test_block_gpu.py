@@ -96,7 +96,8 @@ def test_step_matches_manual_chain_and_bf16_noise_floor(pkg, mode):
 
 
 @pytest.mark.parametrize("mode", ["int8_rowwise", "int8_rot"])
-def test_fused_block_at_the_benchmark_width_matches_oracle(pkg, mode):
+@pytest.mark.parametrize("attn", ["fast", "token"])
+def test_fused_block_at_the_benchmark_width_matches_oracle(pkg, mode, attn):
     """One block of the benchmark configuration (d_model 4096, 32 heads x 128, MLP hidden 16384, cross-attention
     to 512 text tokens of width 4096) on 4096 video + 148 audio tokens: two modality segments, a ragged last
     64-token block, K = 16384 rows in the fc2 quantizer. Stage by stage against the CPU oracle."""
@@ -115,15 +116,19 @@ def test_fused_block_at_the_benchmark_width_matches_oracle(pkg, mode):
     adaln = tuple(t.cpu() for t in model.blocks[0].adaln_proj(t_emb[0].cuda()))
     patched, = r.nodes.RapidH3LinearQuant().patch(model, mode)
     trace = {}
-    out = patched.block_forward[0].forward(x.cuda(), t_emb[0].cuda(), segs, rope.cuda(), ctx[0].cuda(), trace=trace)
-    r._lib.check_status()
+    r.nodes.ATTN_ROTATE = attn == "token"     # both attention numerics go through the same block and the same checks
+    try:
+        out = patched.block_forward[0].forward(x.cuda(), t_emb[0].cuda(), segs, rope.cuda(), ctx[0].cuda(), trace=trace)
+        r._lib.check_status()
+    finally:
+        r.nodes.ATTN_ROTATE = False
     got = {k: v.cpu() for k, v in trace.items()}
     # every stage of the oracle starts from the residual stream the device produced, so each stage is compared on
     # identical inputs: what is integer (codes, scales, and the bf16 GEMM outputs that follow from them) must be
     # bit-identical, what passes through the attention kernel's exponentials is held to 1e-3
     want = {}
     ref = ob.fused_block(blk, x, t_emb[0], segs, rope, ctx[0], trace=want, mode=mode, adaln=adaln,
-                         replay={k: got[k] for k in ("x_attn", "x_cross", "mlp_h")})
+                         replay={k: got[k] for k in ("x_attn", "x_cross", "mlp_h")}, attn=attn)
     for name in ("attn_in_q", "attn_in_s", "qkv", "qkv_rr", "cross_in_q", "cross_in_s", "cross_q", "cross_k", "cross_v",
                  "mlp_in_q", "mlp_in_s", "fc2_in_q", "fc2_in_s"):
         assert torch.equal(got[name], want[name]), name
