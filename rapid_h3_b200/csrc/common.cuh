@@ -56,9 +56,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_addr(uint32_t bar_addr) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_addr) : "memory");
-}
 __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -125,42 +122,6 @@ __device__ __forceinline__ bool bar_sync_or(int id, int nthreads, bool pred) {
       : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(nthreads)
       : "memory");
   return r != 0;
-}
-
-// The same waits for single-thread roles whose whole instruction stream is on the critical path (an MMA issuer): the
-// barrier is named by its 32-bit shared-memory address (computed once, outside the loop), and the completed case is
-// one try_wait and one branch; everything else (polling, sleeping, the abort flag, the status word) is out of line.
-__device__ __forceinline__ uint32_t mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar_addr), "r"(parity)
-      : "memory");
-  return ok;
-}
-__device__ __forceinline__ bool mbar_wait_addr_slow(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag, int* status,
-                                                 int code) {
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
-    if (mbar_try_wait_addr(bar_addr, parity)) return true;
-    if (it > 16) __nanosleep(32);
-    if (it > 64 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  if (status) atomicCAS(status, 0, code);
-  return false;
-}
-__device__ __forceinline__ bool mbar_wait_addr(uint32_t bar_addr, uint32_t parity, volatile int* abort_flag, int* status,
-                                               int code) {
-  if (mbar_try_wait_addr(bar_addr, parity)) return true;
-  return mbar_wait_addr_slow(bar_addr, parity, abort_flag, status, code);
-}
-__device__ __forceinline__ void mma_commit_addr(uint32_t bar_addr) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -279,47 +240,6 @@ RH3_DEFINE_MMA4(mma4_f8_ss, "f8f6f4")
 RH3_DEFINE_MMA4(mma4_f16_ss, "f16")
 #undef RH3_DEFINE_MMA4
 
-// The same four MMAs with the descriptors given as (low word, shared high word): the low word carries the start
-// address (16-byte units) and the unused leading-offset field, the high word is the same for every 128-byte-swizzled
-// K-major tile (see make_desc_k128), so stepping along K or to another tile is a 32-bit add.
-constexpr uint32_t kDescK128Hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_k128_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFF) >> 4) | (1u << 16); }
-#define RH3_DEFINE_MMA4_LO(NAME, KIND)                                                                         \
-  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,           \
-                                       uint32_t acc_first) {                                                    \
-    asm volatile(                                                                                              \
-        "{\n\t"                                                                                                \
-        ".reg .pred p, q;\n\t"                                                                                 \
-        ".reg .b32 a1, a2, a3, b1, b2, b3;\n\t"                                                                \
-        ".reg .b64 da, db;\n\t"                                                                                \
-        "setp.ne.b32 p, %4, 0;\n\t"                                                                            \
-        "setp.eq.b32 q, 0, 0;\n\t"                                                                             \
-        "add.u32 a1, %1, 2;\n\t"                                                                               \
-        "add.u32 b1, %2, 2;\n\t"                                                                               \
-        "add.u32 a2, %1, 4;\n\t"                                                                               \
-        "add.u32 b2, %2, 4;\n\t"                                                                               \
-        "add.u32 a3, %1, 6;\n\t"                                                                               \
-        "add.u32 b3, %2, 6;\n\t"                                                                               \
-        "mov.b64 da, {%1, %5};\n\t"                                                                            \
-        "mov.b64 db, {%2, %5};\n\t"                                                                            \
-        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, p;\n\t"                                     \
-        "mov.b64 da, {a1, %5};\n\t"                                                                            \
-        "mov.b64 db, {b1, %5};\n\t"                                                                            \
-        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, q;\n\t"                                     \
-        "mov.b64 da, {a2, %5};\n\t"                                                                            \
-        "mov.b64 db, {b2, %5};\n\t"                                                                            \
-        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, q;\n\t"                                     \
-        "mov.b64 da, {a3, %5};\n\t"                                                                            \
-        "mov.b64 db, {b3, %5};\n\t"                                                                            \
-        "tcgen05.mma.cta_group::1.kind::" KIND " [%0], da, db, %3, q;\n\t"                                     \
-        "}\n" ::"r"(d_tmem),                                                                                   \
-        "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(acc_first), "r"(kDescK128Hi)                                     \
-        : "memory");                                                                                           \
-  }
-RH3_DEFINE_MMA4_LO(mma4_i8_lo, "i8")
-RH3_DEFINE_MMA4_LO(mma4_f8_lo, "f8f6f4")
-#undef RH3_DEFINE_MMA4_LO
-
 // all previously issued MMAs of this thread arrive on `bar` when they retire
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -337,17 +257,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
 // 32 lanes x 8 consecutive columns (small-footprint variants for rarely taken paths)
@@ -375,16 +284,6 @@ __device__ __forceinline__ void tmem_ld_wait16(uint32_t* r) {
                :
                : "memory");
 }
-// 32 lanes x 16 consecutive columns, load and wait in one statement
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
-               "tcgen05.wait::ld.sync.aligned;"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr)
-               : "memory");
-}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
                "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -399,7 +298,6 @@ __device__ __forceinline__ void tmem_st32_splat(uint32_t taddr, uint32_t v) {
       "r"(v)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Same wait, tied to the 32 destination registers of an earlier tmem_ld32 so that the compiler cannot
 // move arithmetic on them above the wait (the load delivers its registers asynchronously).
 __device__ __forceinline__ void tmem_ld_wait_regs(uint32_t* r) {
