@@ -145,6 +145,24 @@ def cpu_port_step_seconds(workload, rows=1024, attn_rows=256):
         else:
             ol.swiglu_epilogue(acc, xs, ws)
         lin += time.perf_counter() - t1
+    # per-head RMSNorm + 3-D RoPE of q and k (self-attention) and RMSNorm of q (cross-attention), on `rows` tokens
+    from oracle import inputs as oi
+    rr_rows = min(rows, 2048)
+    qk = torch.randn(rr_rows, cfg.heads, 128, generator=g).to(torch.bfloat16)
+    rope_tab = oi.rope_table(oi.random_positions(rr_rows, seed=1))
+    t1 = time.perf_counter()
+    oa.rmsnorm_rope(qk, w_norm[:128], 1e-5, rope_tab)
+    oa.rmsnorm_rope(qk, w_norm[:128], 1e-5, rope_tab)
+    oa.rmsnorm_rope(qk, w_norm[:128], 1e-5, None)
+    t_rr = (time.perf_counter() - t1) * (rows / rr_rows)
+    # AdaLN projection of the timestep embedding and the text K/V projection: once per block-sample, not per token
+    t1 = time.perf_counter()
+    torch.nn.functional.linear(torch.randn(1, d, generator=g).to(torch.bfloat16),
+                               torch.randn(6 * d, d, generator=g).to(torch.bfloat16))
+    cq, cs = ol.quantize_rows(torch.randn(text_len, cfg.text_dim, generator=g).to(torch.bfloat16), "int8_rowwise")
+    wq, ws = qw(2 * d, cfg.text_dim)
+    ol.dequant(ol.int_mm(cq, wq), cs, ws)
+    t_once = time.perf_counter() - t1
     q, k, v = (torch.randn(s, 1, 128, generator=g).to(torch.bfloat16) for _ in range(3))
     t1 = time.perf_counter()
     pre = oa.prepass(q, k, v)
@@ -152,10 +170,16 @@ def cpu_port_step_seconds(workload, rows=1024, attn_rows=256):
     t1 = time.perf_counter()
     oa.attention_pre(pre, rows=torch.arange(attn_rows))
     t_attn = time.perf_counter() - t1
-    per_block_sample = lin * (s / rows) + cfg.heads * (t_pre + t_attn * (s / attn_rows))
+    # cross-attention: the same rows against the text keys
+    t1 = time.perf_counter()
+    oa.attention(q[:attn_rows], k[:text_len], v[:text_len])
+    t_cross = time.perf_counter() - t1
+    per_block_sample = ((lin + t_rr) * (s / rows) + t_once +
+                        cfg.heads * (t_pre + (t_attn + t_cross) * (s / attn_rows)))
     total = per_block_sample * blocks * batch
     return total, {"rows": rows, "attn_rows": attn_rows, "sample_seconds": time.perf_counter() - t0,
-                   "linear_s_per_rows": lin, "attn_s_per_head_rows": t_attn, "prepass_s_per_head": t_pre}
+                   "linear_s_per_rows": lin, "attn_s_per_head_rows": t_attn, "prepass_s_per_head": t_pre,
+                   "rmsnorm_rope_s_per_rows": t_rr, "cross_attn_s_per_head_rows": t_cross, "once_per_block_s": t_once}
 
 
 # bounded CPU sample shared by the cpu_baseline leg and the --impl reference arm (5-10 s of CPU work per step)
@@ -168,9 +192,10 @@ def cpu_baseline_record(workload):
     cpu_port_step_seconds(workload, rows=128, attn_rows=32)  # warm-up
     val, info = cpu_port_step_seconds(workload, rows=CPU_SAMPLE_ROWS, attn_rows=CPU_SAMPLE_ATTN_ROWS)
     return {"value": val, "unit": "s/step", "cores": cores, "kind": "port",
-            "sample": (f"row-local ops of one block on {info['rows']} of the tokens, attention of 1 head on "
-                       f"{info['attn_rows']} query rows x all keys ({info['sample_seconds']:.1f} s of CPU work), "
-                       "scaled linearly to all rows, heads, blocks and the CFG batch")}
+            "sample": (f"row-local ops of one block (quantizers, six GEMMs with their epilogues, RMSNorm + RoPE) on "
+                       f"{info['rows']} of the tokens, self- and cross-attention of 1 head on {info['attn_rows']} query "
+                       f"rows x all keys, AdaLN and the text K/V projection once ({info['sample_seconds']:.1f} s of CPU "
+                       "work), scaled linearly to all rows, heads, blocks and the CFG batch")}
 
 
 def vae_cpu_seconds():
