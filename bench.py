@@ -249,10 +249,11 @@ def run_reference(args, rank):
            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "int8",
            "data": "synthetic", "config": workload_config(args.workload, args.gpus),
            "cpu_baseline": {"value": val, "unit": "s/step", "cores": cores, "kind": "port",
-                            "sample": f"per step: row-local ops of one block on {CPU_SAMPLE_ROWS} tokens + attention of "
-                                      f"1 head on {CPU_SAMPLE_ATTN_ROWS} query rows x all keys "
-                                      f"({info['sample_seconds']:.1f} s of CPU work), scaled linearly to the full step; "
-                                      "the same sample as the cpu_baseline leg of the GPU arm"},
+                            "sample": f"per step: row-local ops of one block (quantizers, six GEMMs with their "
+                                      f"epilogues, RMSNorm + RoPE) on {CPU_SAMPLE_ROWS} tokens + self- and cross-attention "
+                                      f"of 1 head on {CPU_SAMPLE_ATTN_ROWS} query rows x all keys + AdaLN and the text K/V "
+                                      f"projection once ({info['sample_seconds']:.1f} s of CPU work), scaled linearly to "
+                                      "the full step; the same sample as the cpu_baseline leg of the GPU arm"},
            "e2e": {"value": val, "unit": "s/step", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(rec), flush=True)
 
