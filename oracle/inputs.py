@@ -69,5 +69,24 @@ def attention_case(l, h, seed=0, d=128, k_offset_std=2.0):
     return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
 
 
+def attention_outlier_case(l, h, seed=0, d=128, device="cpu"):
+    """The value distribution of the reference's synthetic attention benchmark (bench/attn_cake.py:20-35): N(0,1) q
+    and k times 1.6, four outlier channels per head scaled by 3 that also carry a per-head K offset ~ 6 N(0,1), V with a
+    per-channel scale in [1, 2) and a heavy tail 0.05 N(0,1)^3. bf16 [L, H, D]."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = torch.randn(l, h, d, generator=g, device=device)
+    k = torch.randn(l, h, d, generator=g, device=device)
+    idx = torch.randint(0, d, (h, 4), generator=g, device=device)
+    kbias = torch.zeros(1, h, d, device=device)
+    kbias.scatter_(2, idx.view(1, h, 4), 6.0 * torch.randn(1, h, 4, generator=g, device=device))
+    boost = torch.ones(1, h, d, device=device)
+    boost.scatter_(2, idx.view(1, h, 4), 3.0)
+    q = q * boost * 1.6
+    k = k * boost * 1.6 + kbias
+    v = torch.randn(l, h, d, generator=g, device=device) * (1 + torch.rand(1, h, d, generator=g, device=device))
+    v = v + 0.05 * torch.randn(l, h, d, generator=g, device=device).pow(3)
+    return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
 def softmax_scale(d=128):
     return 1.0 / math.sqrt(d)

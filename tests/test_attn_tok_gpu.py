@@ -158,3 +158,25 @@ def test_token_attention_full_size_sampled_rows(ops):
     ref = ot.attention(q[:, heads].cpu(), k[:, heads].cpu(), v[:, heads].cpu(), rows=rows)
     assert rel_l2(out[rows][:, heads].cpu(), ref) <= TOL
     assert torch.isfinite(out.float()).all()
+
+
+def test_error_against_fp32_on_the_reference_benchmark_distribution(ops):
+    """The reference reports 2.06 % (S = 22,332) for its production numerics against fp32 attention on its synthetic
+    outlier inputs, and about 2.3x less on real activations (csrc/attn_cake/DESIGN.md, "Correctness"). The same
+    distribution, same size, two heads: the token-scaled kernel must land there, and the fast kernel's e4m3 numerics
+    are recorded beside it."""
+    attn, lib = ops
+    s, h = 22332, 2
+    q, k, v = inputs.attention_outlier_case(s, h, seed=0, device="cuda")
+    out_tok = attn.attention(q, k, v, rotate=True)
+    out_fast = attn.attention(q, k, v)
+    lib.check_status()
+    ref = torch.empty(s, h, 128, device="cuda")
+    for hh in range(h):
+        for r0 in range(0, s, 4096):
+            w = torch.softmax((q[r0:r0 + 4096, hh].float() @ k[:, hh].float().t()) * 128 ** -0.5, -1)
+            ref[r0:r0 + 4096, hh] = w @ v[:, hh].float()
+    e_tok, e_fast = rel_l2(out_tok, ref), rel_l2(out_fast, ref)
+    print(f"error vs fp32 at S={s} on the outlier distribution: token-scaled {e_tok:.4f}, fast (e4m3 P, V) {e_fast:.4f}")
+    assert 0.017 < e_tok < 0.024      # observed 0.0204; the reference's figure for its kernel is 0.0206
+    assert e_tok < e_fast
