@@ -273,6 +273,33 @@ def workload_config(name, n, attn="fast"):
             "l2": "every step streams >16 GB of weights and activations, far larger than the 126 MB L2"}
 
 
+def tensor_probe():
+    """Retire rate of back-to-back tcgen05 MMAs from shared memory on pseudo-random operands, held for about a
+    second per kind (rh3_selftest_mma_rate): what the tensor pipe sustains under this GPU's power cap for int8 and
+    e4m3 operands. MEASURED_PEAKS.json holds no 8-bit figure; this is the live one, reported beside it."""
+    import ctypes
+    import rapid_h3_b200 as r
+    out = {}
+    for kind, name in ((0, "int8_tops"), (1, "e4m3_tops")):
+        ops = ctypes.c_double(0)
+
+        def fn():
+            r._lib.call("rh3_selftest_mma_rate", kind, 20000, 1, ctypes.addressof(ops), r._lib.stream())
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(8):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = round(ops.value * 8 / e0.elapsed_time(e1) / 1e9, 1)
+    r._lib.check_status()
+    out["note"] = ("128x256x32 MMAs issued back to back by one thread per SM on pseudo-random shared-memory operands, "
+                   "8 launches of about 0.1 s, CUDA events")
+    return out
+
+
 def vae_extras(local):
     """The second workload of the path beside the step record: the conv3d VAE decode of the benchmark latent on one
     GPU, latent resident, 3 warm-up + 3 timed decodes (CUDA events)."""
@@ -542,6 +569,15 @@ def main():
            "e2e": {"value": ms_e2e / 1e3, "unit": "s/step", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
            "gpu_launches": launches, "roofline": roof, "roofline_gemm": roof_gemm, "roofline_quant": roof_quant,
            "phases_ms_per_step": phase_ms, "exchange_ms_per_step": round(exchange_ms, 3)}
+    if world == 1 and not args.no_extras:
+        probe = tensor_probe()
+        rec["tensor_probe"] = probe
+        if roof:
+            # the attention kernel runs half of its operations on int8 and half on e4m3 operands
+            mixed = 2.0 / (1.0 / probe["int8_tops"] + 1.0 / probe["e4m3_tops"])
+            roof["frac_of_probe"] = roof["achieved"] / (probe["int8_tops"] if args.attn == "reference" else mixed)
+        if roof_gemm:
+            roof_gemm["frac_of_probe"] = roof_gemm["achieved"] / probe["int8_tops"]
     if world == 1 and args.workload == "full" and not args.no_extras:
         rec["extras"] = vae_extras(local)
     if rank == 0:

@@ -40,6 +40,12 @@ int rh3_check_status(cudaStream_t stream, int* status_out);
  * how the path "a wait ran out" of every kernel of the library is exercised. It has no counterpart in the
  * reference (whose kernels wait without a limit). */
 int rh3_selftest_wait_expiry(int64_t max_polls, int* left_normally, cudaStream_t stream);
+/* Issue-rate probe of the tensor pipe (no reference counterpart): every SM issues groups * 64 MMAs of 128 x 256 x 32
+ * (kind 0 = int8, 1 = e4m3) or 128 x 256 x 16 (kind 2 = bf16) on shared-memory operands that are zero or, with
+ * random_operands != 0, a fixed pseudo-random pattern (the switching activity of real data, which the power cap
+ * responds to); the caller times the launch with CUDA events and divides *ops_out (operations of the launch) by it:
+ * the retire rate of the MMAs under the clocks the GPU holds, the denominator of the 8-bit tensor rooflines. */
+int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, double* ops_out, cudaStream_t stream);
 
 /* ---- per-token quantizers (HBM-bound) ------------------------------------------------------ */
 /* q[M,K] int8, s[M] fp32: s = max(amax/127, 1e-12), q = clamp(rint(x/s), +-127).

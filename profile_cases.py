@@ -30,7 +30,7 @@ def _time(fn, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["attn", "gemm", "quant", "prepass", "conv", "vae"])
+    ap.add_argument("case", choices=["attn", "gemm", "quant", "prepass", "conv", "vae", "mma_rate"])
     ap.add_argument("--L", type=int, default=16384)
     ap.add_argument("--H", type=int, default=8)
     ap.add_argument("--M", type=int, default=8192)
@@ -52,6 +52,21 @@ def main():
     def randn(*shape):
         return torch.randn(*shape, device="cuda", generator=g)
 
+    if a.case == "mma_rate":
+        # retire rate of back-to-back tcgen05 MMAs from shared memory, per operand kind; short bursts and a run of
+        # about a second (the clocks the GPU holds under its power cap differ between the two)
+        import ctypes
+        for kind, name in ((0, "int8"), (1, "e4m3"), (2, "bf16")):
+            for rnd in (0, 1):
+                for groups, reps, label in ((2000, 3, "burst"), (20000, 12, "sustained")):
+                    ops = ctypes.c_double(0)
+
+                    def fn():
+                        _lib.call("rh3_selftest_mma_rate", kind, groups, rnd, ctypes.addressof(ops), _lib.stream())
+                    ms = _time(fn, reps)
+                    print(f"mma_rate {name} {'random' if rnd else 'zero'} operands, {label}: {ms:.3f} ms per launch, "
+                          f"{ops.value / ms / 1e9:.0f} TOP/s", flush=True)
+        return
     if a.case == "conv":
         from rapid_h3_b200 import vae
         x = randn(1, a.T, a.HH, a.WW, a.Cin).to(torch.bfloat16)

@@ -123,7 +123,95 @@ __global__ void wait_expiry_kernel(uint32_t max_polls, int* status, int* left_no
   }
 }
 
+// Issue-rate probe of the tensor pipe: one CTA per SM, one thread issues `groups` groups of 64 MMAs of 128 x 256 x 32
+// (8-bit kinds) or 128 x 256 x 16 (bf16) on zeroed shared-memory operands, alternating between two TMEM accumulators,
+// with a commit per group and a bounded wait for the group before the previous one (so two groups are always in
+// flight). The accumulators just keep accumulating (int32 wraps, floats may saturate: the values are not read). No
+// memory traffic beyond shared memory: what it measures is the rate the MMAs retire at under the clocks
+// the GPU actually holds, the denominator for the 8-bit kernels' tensor rooflines.
+template <int KIND>   // 0 = kind::i8, 1 = kind::f8f6f4 (e4m3), 2 = kind::f16 (bf16)
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random_operands, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  // operands: zeros, or a fixed pseudo-random byte pattern (switching activity like real data, which is what the
+  // power cap responds to; for e4m3 / bf16 the exponent bits are masked so that every value is finite)
+  for (int i = threadIdx.x; i < (128 + 256) * 128 / 4; i += blockDim.x) {
+    uint32_t w = 0;
+    if (random_operands) {
+      w = (static_cast<uint32_t>(i) + 1u) * 2654435761u;
+      w ^= w >> 15;
+      w *= 2246822519u;
+      w ^= w >> 13;
+      if (KIND == 1) w &= 0xBFBFBFBFu;      // e4m3: clear the top exponent bit of every byte (|x| < 2)
+      if (KIND == 2) w &= 0xBFFFBFFFu;      // bf16: clear the top exponent bit of both halves (|x| < 2)
+    }
+    reinterpret_cast<uint32_t*>(smem)[i] = w;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  fence_proxy_async_smem();
+  if (threadIdx.x < 32) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  if (threadIdx.x == 0) {
+    const uint64_t a_desc = make_desc_k128(smem_u32(smem)), b_desc = make_desc_k128(smem_u32(smem + 128 * 128));
+    constexpr uint32_t idesc = KIND == 0 ? make_idesc(2, 1, 1, 128, 256) : (KIND == 1 ? make_idesc(1, 0, 0, 128, 256)
+                                                                                        : make_idesc(1, 1, 1, 128, 256));
+    bool ok = true;
+    for (int g = 0; g < groups && ok; ++g) {
+#pragma unroll 1
+      for (int i = 0; i < 16; ++i) {   // 16 x 4 MMAs
+        const uint32_t d = tmem_base + (i & 1) * 256;
+        if (KIND == 0) mma4_i8_ss(d, a_desc, b_desc, idesc, 1);
+        else if (KIND == 1) mma4_f8_ss(d, a_desc, b_desc, idesc, 1);
+        else mma4_f16_ss(d, a_desc, b_desc, idesc, 1);
+      }
+      mma_commit(&bar[g & 1]);
+      if (g > 0) ok = mbar_wait(&bar[(g - 1) & 1], ((g - 1) >> 1) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+    }
+    if (ok && groups > 0) mbar_wait(&bar[(groups - 1) & 1], ((groups - 1) >> 1) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 }  // namespace rh3
+
+// Launches the issue-rate probe on every SM; the caller times it with CUDA events. Operations per launch:
+// sm_count * groups * 64 * 2 * 128 * 256 * (32 for kind 0 / 1, 16 for kind 2); *ops_out receives that number.
+extern "C" int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, double* ops_out, cudaStream_t stream) {
+  RH3_CHECK_ARG(kind >= 0 && kind <= 2, "selftest_mma_rate: kind must be 0 (i8), 1 (e4m3) or 2 (bf16)");
+  RH3_CHECK_ARG(groups >= 1 && groups <= (1 << 16), "selftest_mma_rate: groups=%lld must be in [1, 65536]", (long long)groups);
+  int* w = rh3::device_status_word();
+  if (!w) return rh3::set_error(RH3_ARG_ERROR, "no device status word (is a CUDA device current?)");
+  const int sms = rh3::device_sm_count();
+  const int smem = (128 + 256) * 128 + 1024;
+  auto launch = [&](auto kern) {
+    if (int e = rh3::check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "mma_rate smem"))
+      return e;
+    kern<<<sms, 128, smem, stream>>>(static_cast<int>(groups), random_operands, w);
+    return rh3::check_cuda(cudaGetLastError(), "selftest_mma_rate launch");
+  };
+  int e = kind == 0 ? launch(rh3::mma_rate_kernel<0>) : (kind == 1 ? launch(rh3::mma_rate_kernel<1>) : launch(rh3::mma_rate_kernel<2>));
+  if (ops_out) *ops_out = static_cast<double>(sms) * static_cast<double>(groups) * 64.0 * 2.0 * 128.0 * 256.0 * (kind == 2 ? 16.0 : 32.0);
+  return e;
+}
 
 extern "C" int rh3_selftest_wait_expiry(int64_t max_polls, int* left_normally, cudaStream_t stream) {
   RH3_CHECK_ARG(max_polls >= 1 && max_polls <= (1 << 20), "selftest_wait_expiry: max_polls=%lld must be in [1, 2^20]",
