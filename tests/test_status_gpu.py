@@ -36,3 +36,32 @@ def test_check_status_raises_on_a_recorded_code():
     with pytest.raises(RuntimeError, match="190"):
         lib.check_status()
     lib.check_status()
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("random_operands", [0, 1])
+def test_tensor_pipe_probe_returns_and_reports_a_plausible_rate(kind, random_operands):
+    """The issue-rate probe (no reference counterpart) comes back by itself with a clean status word, counts its
+    operations as documented, and retires above half of the nominal rate of its operand kind."""
+    from rapid_h3_b200 import _lib as lib
+    ops = ctypes.c_double(0)
+    groups = 400
+
+    def run():
+        lib.call("rh3_selftest_mma_rate", kind, groups, random_operands, ctypes.addressof(ops), lib.stream())
+
+    run()
+    lib.check_status()
+    sms = lib.lib().rh3_sm_count()
+    assert ops.value == sms * groups * 64 * 2 * 128 * 256 * (16 if kind == 2 else 32)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    lib.check_status()
+    tops = ops.value * 3 / e0.elapsed_time(e1) / 1e9
+    assert tops > (1100 if kind == 2 else 2200), tops
+    with pytest.raises(RuntimeError):
+        lib.call("rh3_selftest_mma_rate", 3, groups, 0, ctypes.addressof(ops), lib.stream())
