@@ -284,7 +284,7 @@ def tensor_probe():
         ops = ctypes.c_double(0)
 
         def fn():
-            r._lib.call("rh3_selftest_mma_rate", kind, 20000, 1, ctypes.addressof(ops), r._lib.stream())
+            r._lib.call("rh3_selftest_mma_rate", kind, 20000, 1, 0, ctypes.addressof(ops), r._lib.stream())
         fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -44,8 +44,13 @@ int rh3_selftest_wait_expiry(int64_t max_polls, int* left_normally, cudaStream_t
  * (kind 0 = int8, 1 = e4m3) or 128 x 256 x 16 (kind 2 = bf16) on shared-memory operands that are zero or, with
  * random_operands != 0, a fixed pseudo-random pattern (the switching activity of real data, which the power cap
  * responds to); the caller times the launch with CUDA events and divides *ops_out (operations of the launch) by it:
- * the retire rate of the MMAs under the clocks the GPU holds, the denominator of the 8-bit tensor rooflines. */
-int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, double* ops_out, cudaStream_t stream);
+ * the retire rate of the MMAs under the clocks the GPU holds, the denominator of the 8-bit tensor rooflines.
+ * pattern 0: 64 MMAs per commit; 1 and 2: the issue pattern of a pipelined GEMM main loop (four-stage ring: per four
+ * MMAs a wait on the stage's barrier, the descriptors and a commit), descriptors rebuilt per stage (1) or kept in
+ * registers (2), or with the whole warp in the loop and one elected lane issuing (3): what the issuing thread's own
+ * instruction stream costs. */
+int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, int pattern, double* ops_out,
+                          cudaStream_t stream);
 
 /* ---- per-token quantizers (HBM-bound) ------------------------------------------------------ */
 /* q[M,K] int8, s[M] fp32: s = max(amax/127, 1e-12), q = clamp(rint(x/s), +-127).

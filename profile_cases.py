@@ -62,10 +62,20 @@ def main():
                     ops = ctypes.c_double(0)
 
                     def fn():
-                        _lib.call("rh3_selftest_mma_rate", kind, groups, rnd, ctypes.addressof(ops), _lib.stream())
+                        _lib.call("rh3_selftest_mma_rate", kind, groups, rnd, 0, ctypes.addressof(ops), _lib.stream())
                     ms = _time(fn, reps)
                     print(f"mma_rate {name} {'random' if rnd else 'zero'} operands, {label}: {ms:.3f} ms per launch, "
                           f"{ops.value / ms / 1e9:.0f} TOP/s", flush=True)
+        # the issuing thread's own cost: the GEMM main loop's issue pattern on zero operands at full clock
+        for pattern, name in ((0, "64 MMAs per commit"), (1, "ring, descriptors rebuilt per stage"),
+                              (2, "ring, descriptors kept in registers"),
+                              (3, "ring, whole warp in the loop, one elected lane issues"), (0, "64 MMAs per commit (again)")):
+            ops = ctypes.c_double(0)
+
+            def fn():
+                _lib.call("rh3_selftest_mma_rate", 0, 2000, 0, pattern, ctypes.addressof(ops), _lib.stream())
+            ms = _time(fn, 3)
+            print(f"mma_rate int8 zero operands, {name}: {ms:.3f} ms per launch, {ops.value / ms / 1e9:.0f} TOP/s", flush=True)
         return
     if a.case == "conv":
         from rapid_h3_b200 import vae

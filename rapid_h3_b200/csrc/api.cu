@@ -130,10 +130,10 @@ __global__ void wait_expiry_kernel(uint32_t max_polls, int* status, int* left_no
 // memory traffic beyond shared memory: what it measures is the rate the MMAs retire at under the clocks
 // the GPU actually holds, the denominator for the 8-bit kernels' tensor rooflines.
 template <int KIND>   // 0 = kind::i8, 1 = kind::f8f6f4 (e4m3), 2 = kind::f16 (bf16)
-__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random_operands, int* status) {
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random_operands, int pattern, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar[2];
+  __shared__ uint64_t bar[4];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
   // operands: zeros, or a fixed pseudo-random byte pattern (switching activity like real data, which is what the
@@ -151,8 +151,7 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random
     reinterpret_cast<uint32_t*>(smem)[i] = w;
   }
   if (threadIdx.x == 0) {
-    mbar_init(&bar[0], 1);
-    mbar_init(&bar[1], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar[i], 1);
     abort_flag = 0;
     fence_barrier_init();
   }
@@ -165,23 +164,94 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && pattern != 3) {
     const uint64_t a_desc = make_desc_k128(smem_u32(smem)), b_desc = make_desc_k128(smem_u32(smem + 128 * 128));
     constexpr uint32_t idesc = KIND == 0 ? make_idesc(2, 1, 1, 128, 256) : (KIND == 1 ? make_idesc(1, 0, 0, 128, 256)
                                                                                         : make_idesc(1, 1, 1, 128, 256));
     bool ok = true;
-    for (int g = 0; g < groups && ok; ++g) {
+    auto mma4 = [&](uint32_t d, uint64_t a, uint64_t b) {
+      if (KIND == 0) mma4_i8_ss(d, a, b, idesc, 1);
+      else if (KIND == 1) mma4_f8_ss(d, a, b, idesc, 1);
+      else mma4_f16_ss(d, a, b, idesc, 1);
+    };
+    if (pattern == 0) {
+      for (int g = 0; g < groups && ok; ++g) {
 #pragma unroll 1
-      for (int i = 0; i < 16; ++i) {   // 16 x 4 MMAs
-        const uint32_t d = tmem_base + (i & 1) * 256;
-        if (KIND == 0) mma4_i8_ss(d, a_desc, b_desc, idesc, 1);
-        else if (KIND == 1) mma4_f8_ss(d, a_desc, b_desc, idesc, 1);
-        else mma4_f16_ss(d, a_desc, b_desc, idesc, 1);
+        for (int i = 0; i < 16; ++i) mma4(tmem_base + (i & 1) * 256, a_desc, b_desc);   // 16 x 4 MMAs
+        mma_commit(&bar[g & 1]);
+        if (g > 0) ok = mbar_wait(&bar[(g - 1) & 1], ((g - 1) >> 1) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
       }
-      mma_commit(&bar[g & 1]);
-      if (g > 0) ok = mbar_wait(&bar[(g - 1) & 1], ((g - 1) >> 1) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+      if (ok && groups > 0) mbar_wait(&bar[(groups - 1) & 1], ((groups - 1) >> 1) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+    } else {
+      // The issue pattern of a pipelined GEMM main loop: a four-stage ring, and per stage (four MMAs) one wait on the
+      // stage's barrier, the descriptors, the MMAs and one commit on the same barrier, which therefore completes four
+      // stages later, when those MMAs have retired. pattern 1 builds the descriptors from the stage index every time;
+      // pattern 2 keeps one descriptor pair per stage in registers and selects by a switch.
+      const int n = groups * 16;
+      const int stage_stride = (groups >> 20) * 1024;
+      uint64_t a_s[4], b_s[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) a_s[q] = a_desc, b_s[q] = b_desc;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < n && ok; ++i) {
+        if (i >= 4) ok = mbar_wait(&bar[stage], phase ^ 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+        tc_fence_after();
+        const uint32_t d = tmem_base + (i & 1) * 256;
+        if (pattern == 1) {
+          // the same tile for every stage, but computed from the stage index as a main loop would (stage_stride is
+          // zero at run time, which the compiler cannot know)
+          const uint32_t a_addr = smem_u32(smem + stage * stage_stride);
+          mma4(d, make_desc_k128(a_addr), make_desc_k128(a_addr + 128 * 128));
+        } else {
+          switch (stage) {
+            case 0: mma4(d, a_s[0], b_s[0]); break;
+            case 1: mma4(d, a_s[1], b_s[1]); break;
+            case 2: mma4(d, a_s[2], b_s[2]); break;
+            default: mma4(d, a_s[3], b_s[3]); break;
+          }
+        }
+        mma_commit(&bar[stage]);
+        if (++stage == 4) { stage = 0; phase ^= 1; }
+      }
+      // drain: the last commit of every stage
+      for (int q = 0; q < 4 && ok; ++q) {
+        const int last = n - 1 - ((n - 1 - q) % 4 + 4) % 4;   // last iteration that used stage q
+        if (last >= 0 && (last % 4) == q) ok = mbar_wait(&bar[q], (last / 4) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+      }
     }
-    if (ok && groups > 0) mbar_wait(&bar[(groups - 1) & 1], ((groups - 1) >> 1) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+  }
+  if (pattern == 3 && threadIdx.x < 32) {
+    // The same ring with the WHOLE warp in the loop (waits, counters and descriptors are warp-uniform, so they can live
+    // in the uniform datapath) and one elected lane issuing the MMAs and the commit.
+    const uint64_t a_desc = make_desc_k128(smem_u32(smem)), b_desc = make_desc_k128(smem_u32(smem + 128 * 128));
+    constexpr uint32_t idesc = KIND == 0 ? make_idesc(2, 1, 1, 128, 256) : (KIND == 1 ? make_idesc(1, 0, 0, 128, 256)
+                                                                                        : make_idesc(1, 1, 1, 128, 256));
+    const int n = groups * 16;
+    const int stage_stride = (groups >> 20) * 1024;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int i = 0; i < n && ok; ++i) {
+      if (i >= 4) ok = mbar_wait(&bar[stage], phase ^ 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+      const uint32_t d = tmem_base + (i & 1) * 256;
+      const uint32_t a_addr = smem_u32(smem + stage * stage_stride);
+      if (elect_one()) {
+        if (KIND == 0) mma4_i8_ss(d, make_desc_k128(a_addr), make_desc_k128(a_addr + 128 * 128), idesc, 1);
+        else if (KIND == 1) mma4_f8_ss(d, make_desc_k128(a_addr), make_desc_k128(a_addr + 128 * 128), idesc, 1);
+        else mma4_f16_ss(d, make_desc_k128(a_addr), make_desc_k128(a_addr + 128 * 128), idesc, 1);
+        mma_commit(&bar[stage]);
+      }
+      __syncwarp();
+      if (++stage == 4) { stage = 0; phase ^= 1; }
+    }
+    for (int q = 0; q < 4 && ok; ++q) {
+      const int last = n - 1 - ((n - 1 - q) % 4 + 4) % 4;
+      if (last >= 0 && (last % 4) == q) ok = mbar_wait(&bar[q], (last / 4) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST);
+    }
+    (void)a_desc; (void)b_desc;
   }
   tc_fence_before();
   __syncthreads();
@@ -195,9 +265,11 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random
 
 // Launches the issue-rate probe on every SM; the caller times it with CUDA events. Operations per launch:
 // sm_count * groups * 64 * 2 * 128 * 256 * (32 for kind 0 / 1, 16 for kind 2); *ops_out receives that number.
-extern "C" int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, double* ops_out, cudaStream_t stream) {
+extern "C" int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, int pattern, double* ops_out,
+                                     cudaStream_t stream) {
   RH3_CHECK_ARG(kind >= 0 && kind <= 2, "selftest_mma_rate: kind must be 0 (i8), 1 (e4m3) or 2 (bf16)");
   RH3_CHECK_ARG(groups >= 1 && groups <= (1 << 16), "selftest_mma_rate: groups=%lld must be in [1, 65536]", (long long)groups);
+  RH3_CHECK_ARG(pattern >= 0 && pattern <= 3, "selftest_mma_rate: pattern must be 0..3");
   int* w = rh3::device_status_word();
   if (!w) return rh3::set_error(RH3_ARG_ERROR, "no device status word (is a CUDA device current?)");
   const int sms = rh3::device_sm_count();
@@ -205,7 +277,7 @@ extern "C" int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operan
   auto launch = [&](auto kern) {
     if (int e = rh3::check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "mma_rate smem"))
       return e;
-    kern<<<sms, 128, smem, stream>>>(static_cast<int>(groups), random_operands, w);
+    kern<<<sms, 128, smem, stream>>>(static_cast<int>(groups), random_operands, pattern, w);
     return rh3::check_cuda(cudaGetLastError(), "selftest_mma_rate launch");
   };
   int e = kind == 0 ? launch(rh3::mma_rate_kernel<0>) : (kind == 1 ? launch(rh3::mma_rate_kernel<1>) : launch(rh3::mma_rate_kernel<2>));

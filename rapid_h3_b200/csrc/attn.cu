@@ -268,22 +268,26 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         tma_load_2d(sk, &tma_k, 0, h * p.Lk_pad + j * BKV, &tail->kv_full[stage]);
         tma_load_2d(sk + TILE_BYTES, &tma_v, j * BKV, h * HD, &tail->kv_full[stage]);
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
       // ------------------------------ MMA issuer ------------------------------
+      // The whole warp runs the loop converged (waits, counters, addresses are warp-uniform and can live in the
+      // uniform datapath the MMA instruction reads its operands from); one elected lane issues MMAs and commits.
       constexpr uint32_t idesc_qk = make_idesc(2, 1, 1, BQ, BKV);  // s32 += s8 * s8
       constexpr uint32_t idesc_pv = make_idesc(1, 0, 0, BQ, HD);   // f32 += e4m3 * e4m3
-      // S is pre-biased by the softmax warps: completion k of s_empty[g] precedes Q.K^T of key tile k,
-      // which therefore always accumulates onto the bias.
       auto issue_qk = [&](int g, int j) {
         const uint32_t q_addr = smem_u32(sQ + g * TILE_BYTES);
         const uint32_t k_addr = smem_u32(sKV + (j % KV_STAGES) * 2 * TILE_BYTES);
-        mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 1);
-        mma_commit(&tail->s_full[g]);
+        if (elect_one()) {
+          mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 1);
+          mma_commit(&tail->s_full[g]);
+        }
+        __syncwarp();
       };
-      bool ok = mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
-                mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
+      auto all_ok = [](bool ok) { return __all_sync(0xffffffffu, ok) != 0; };
+      bool ok = all_ok(mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
+                       mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL));
       for (int g = 0; g < QG && ok; ++g) {
-        ok = mbar_wait(&tail->s_empty[g], 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
+        ok = all_ok(mbar_wait(&tail->s_empty[g], 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY));
         if (ok) {
           tc_fence_after();
           issue_qk(g, 0);
@@ -292,9 +296,9 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) {
           const int ns = (j + 1) % KV_STAGES;
-          ok = mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 64);
+          ok = all_ok(mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 64));
           for (int g = 0; g < QG && ok; ++g) {
-            ok = mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64);
+            ok = all_ok(mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64));
             if (ok) {
               tc_fence_after();
               issue_qk(g, j + 1);
@@ -305,14 +309,20 @@ attn_int8_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constan
         const int stage = j % KV_STAGES;
         const uint32_t v_addr = smem_u32(sKV + stage * 2 * TILE_BYTES + TILE_BYTES);
         for (int g = 0; g < QG && ok; ++g) {
-          ok = mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 64);
+          ok = all_ok(mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 64));
           if (!ok) break;
           tc_fence_after();
           const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);
-          mma4_f8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, j != 0);
-          mma_commit(&tail->pv_done[g]);
+          if (elect_one()) {
+            mma4_f8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, j != 0);
+            mma_commit(&tail->pv_done[g]);
+          }
+          __syncwarp();
         }
-        if (ok) mma_commit(&tail->kv_empty[stage]);  // both query tiles have read this K / V^T stage
+        if (ok) {
+          if (elect_one()) mma_commit(&tail->kv_empty[stage]);  // both query tiles have read this K / V^T stage
+          __syncwarp();
+        }
       }
     }
   } else {

@@ -231,21 +231,27 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         tma_load_2d(sk + TILE_BYTES, &tma_v, j * BKV, h * HD, &tail->kv_full[stage]);
         bulk_load(sk + 2 * TILE_BYTES, ksb_h + static_cast<int64_t>(j) * (2 * BKV), KSB_BYTES, &tail->kv_full[stage]);
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
       // ------------------------------ MMA issuer ------------------------------
+      // The whole warp runs the loop converged (waits, counters, addresses are warp-uniform and can live in the
+      // uniform datapath the MMA instruction reads its operands from); one elected lane issues MMAs and commits.
       constexpr uint32_t idesc_qk = make_idesc(2, 1, 1, BQ, BKV);  // s32 = s8 * s8
       constexpr uint32_t idesc_pv = make_idesc(2, 0, 1, BQ, HD);   // s32 = u8 * s8
+      auto all_ok = [](bool ok) { return __all_sync(0xffffffffu, ok) != 0; };
       auto issue_qk = [&](int g, int j) {
         const uint32_t q_addr = smem_u32(sQ + g * TILE_BYTES);
         const uint32_t k_addr = smem_u32(sKV + (j % KV_STAGES) * STAGE_BYTES);
-        mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 1);  // onto the bias
-        mma_commit(&tail->s_full[g]);
+        if (elect_one()) {
+          mma4_i8_ss(tmem_base + g * 128, make_desc_k128(q_addr), make_desc_k128(k_addr), idesc_qk, 1);  // onto the bias
+          mma_commit(&tail->s_full[g]);
+        }
+        __syncwarp();
       };
-      bool ok = mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
-                mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL);
+      bool ok = all_ok(mbar_wait(&tail->q_full, 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL) &&
+                       mbar_wait(&tail->kv_full[0], 0, abort_flag, p.status, ST_TIMEOUT_TMA_FULL));
       for (int g = 0; g < QG && ok; ++g) {
         // completion 0 of s_empty: the softmax warps have biased both accumulators of this query tile
-        ok = mbar_wait(&tail->s_empty[g], 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY);
+        ok = all_ok(mbar_wait(&tail->s_empty[g], 0, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY));
         if (ok) {
           tc_fence_after();
           issue_qk(g, 0);
@@ -254,11 +260,11 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       for (int j = 0; j < n_kv && ok; ++j) {
         if (j + 1 < n_kv) {
           const int ns = (j + 1) % KV_STAGES;
-          ok = mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 64);
+          ok = all_ok(mbar_wait_relaxed(&tail->kv_full[ns], ((j + 1) / KV_STAGES) & 1, abort_flag, p.status, ST_TIMEOUT_TMA_FULL, 64));
           for (int g = 0; g < QG && ok; ++g) {
             // completion j+1 of s_empty: the softmax warps have read the scores of key tile j for the last time and
             // put the bias back
-            ok = mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64);
+            ok = all_ok(mbar_wait_relaxed(&tail->s_empty[g], (j + 1) & 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY, 64));
             if (ok) {
               tc_fence_after();
               issue_qk(g, j + 1);
@@ -270,14 +276,20 @@ attn_tok_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         const uint32_t v_addr = smem_u32(sKV + stage * STAGE_BYTES + TILE_BYTES);
         for (int g = 0; g < QG && ok; ++g) {
           // P of tile j is in shared memory, and the same threads have folded the accumulator of tile j-1 before
-          ok = mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 64);
+          ok = all_ok(mbar_wait_relaxed(&tail->p_full[g], j & 1, abort_flag, p.status, ST_TIMEOUT_P_READY, 64));
           if (!ok) break;
           tc_fence_after();
           const uint32_t p_addr = smem_u32(sP + g * TILE_BYTES);
-          mma4_i8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, 1);  // onto the bias
-          mma_commit(&tail->pv_done[g]);
+          if (elect_one()) {
+            mma4_i8_ss(tmem_base + 256 + g * 128, make_desc_k128(p_addr), make_desc_k128(v_addr), idesc_pv, 1);  // onto the bias
+            mma_commit(&tail->pv_done[g]);
+          }
+          __syncwarp();
         }
-        if (ok) mma_commit(&tail->kv_empty[stage]);
+        if (ok) {
+          if (elect_one()) mma_commit(&tail->kv_empty[stage]);
+          __syncwarp();
+        }
       }
     }
   } else {

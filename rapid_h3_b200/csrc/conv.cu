@@ -141,34 +141,37 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(1, 1, 1, CBM, p.BN);  // f32 += bf16 * bf16
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY)) break;
+    // the whole warp runs the loop converged (waits, counters and addresses are warp-uniform); one elected lane, the
+    // same every time, issues the MMAs and the commits
+    const uint32_t idesc = make_idesc(1, 1, 1, CBM, p.BN);  // f32 += bf16 * bf16
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * 256;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * 256;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * CSTAGE_BYTES);
-          const uint32_t b_addr = a_addr + CA_BYTES;
+        const uint32_t a_addr = smem_u32(smem + stage * CSTAGE_BYTES);
+        const uint32_t b_addr = a_addr + CA_BYTES;
+        if (elect_one()) {
           // four MMAs of 16 bf16 (32 bytes) each along K
           mma4_f16_ss(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
           mma_commit(&tail->empty[stage]);
-          if (++stage == CSTAGES) { stage = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        mma_commit(&tail->acc_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        __syncwarp();
+        if (++stage == CSTAGES) { stage = 0; phase ^= 1; }
       }
+      if (!ok) break;
+      if (elect_one()) mma_commit(&tail->acc_full[acc]);
+      __syncwarp();
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   } else {
     // ------------------------------ epilogue (warps 2..5) ------------------------------

@@ -31,7 +31,10 @@ constexpr int A_BYTES = BM * BK;
 constexpr int B_BYTES = BN * BK;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 192;
-constexpr int GROUP_M = 16;  // tile rasterisation: 16 row-tiles share each column-tile in L2
+#ifndef RH3_GEMM_GROUP_M
+#define RH3_GEMM_GROUP_M 16
+#endif
+constexpr int GROUP_M = RH3_GEMM_GROUP_M;  // tile rasterisation: GROUP_M row-tiles share each column-tile in L2
 
 enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_SWIGLU = 2, EPI_F16 = 3, EPI_SWIGLU_F16 = 4 };
 
@@ -140,34 +143,41 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = KIND_F8 ? make_idesc(1, 0, 0, BM, BN) : make_idesc(2, 1, 1, BM, BN);
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY)) break;
+    // The whole warp runs the loop, converged: waits, counters, addresses and descriptors are then warp-uniform
+    // values the compiler can keep in the uniform datapath, where the MMA instruction takes its operands from; one
+    // elected lane (the same every time) issues the MMAs and the commits. On the bare issue pattern of this loop
+    // (rh3_selftest_mma_rate, patterns 1 and 3) a single lane in the loop reaches 3.2 POP/s and the converged warp
+    // 4.5; in this kernel the two forms measure the same (2.7 POP/s at K = 4096), so the issuing thread is not what
+    // holds the tensor pipe at 70 % here.
+    constexpr uint32_t idesc = KIND_F8 ? make_idesc(1, 0, 0, BM, BN) : make_idesc(2, 1, 1, BM, BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t b_addr = a_addr + A_BYTES;
+        const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+        const uint32_t b_addr = a_addr + A_BYTES;
+        if (elect_one()) {
           if (KIND_F8) mma4_f8_ss(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
           else mma4_i8_ss(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
           mma_commit(&tail->empty[stage]);  // the stage is free once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        mma_commit(&tail->acc_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
+      if (!ok) break;
+      if (elect_one()) mma_commit(&tail->acc_full[acc]);
+      __syncwarp();
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   } else {
     // ------------------------------ epilogue (warps 2..5) ------------------------------

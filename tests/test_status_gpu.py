@@ -48,7 +48,7 @@ def test_tensor_pipe_probe_returns_and_reports_a_plausible_rate(kind, random_ope
     groups = 400
 
     def run():
-        lib.call("rh3_selftest_mma_rate", kind, groups, random_operands, ctypes.addressof(ops), lib.stream())
+        lib.call("rh3_selftest_mma_rate", kind, groups, random_operands, 0, ctypes.addressof(ops), lib.stream())
 
     run()
     lib.check_status()
@@ -64,4 +64,4 @@ def test_tensor_pipe_probe_returns_and_reports_a_plausible_rate(kind, random_ope
     tops = ops.value * 3 / e0.elapsed_time(e1) / 1e9
     assert tops > (1100 if kind == 2 else 2200), tops
     with pytest.raises(RuntimeError):
-        lib.call("rh3_selftest_mma_rate", 3, groups, 0, ctypes.addressof(ops), lib.stream())
+        lib.call("rh3_selftest_mma_rate", 3, groups, 0, 0, ctypes.addressof(ops), lib.stream())
