@@ -28,7 +28,7 @@ MAGIC = 12582912.0  # 1.5 * 2^23: the bias that turns int32 accumulator bits int
 # Which exponentials are a cubic polynomial instead of exp2 (the kernel moves them from the special-function unit
 # to the FMA pipe, the idea of the reference's softmax rebalancing, csrc/attn_cake/attn_cake.cuh:75-95): the 32
 # columns of a chunk are taken four at a time, bit i of the mask selects columns 4i+2 and 4i+3 of group i.
-POLY_MASK = 0x00
+POLY_MASK = 0x55
 POLY_CLAMP = -60.0
 POLY_C = [float.fromhex(h) for h in ("0x1.fff694p-1", "0x1.62f31ap-1", "0x1.f0ddf6p-3", "0x1.c3f6fp-5")]
 
