@@ -51,6 +51,12 @@ int rh3_selftest_wait_expiry(int64_t max_polls, int* left_normally, cudaStream_t
  * instruction stream costs. */
 int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, int pattern, double* ops_out,
                           cudaStream_t stream);
+/* The main loop of a 128 x 256 int8 GEMM tile without an epilogue, on every SM (no reference counterpart): a four-stage
+ * ring; per stage a bulk copy of fill_bytes (0, 16384, 32768 or 49152) from src into shared memory, then four MMAs of
+ * 128 x 256 x 32 on the stage. Timed by the caller; *ops_out = operations of the launch. It shows the MMA rate an SM
+ * sustains while taking in fill_bytes per 512 tensor cycles: 49152 is what the GEMM's tile shape asks for. */
+int rh3_selftest_mma_feed(const void* src, int64_t src_bytes, int64_t stages, int fill_bytes, double* ops_out,
+                          cudaStream_t stream);
 
 /* ---- per-token quantizers (HBM-bound) ------------------------------------------------------ */
 /* q[M,K] int8, s[M] fp32: s = max(amax/127, 1e-12), q = clamp(rint(x/s), +-127).

@@ -76,6 +76,18 @@ def main():
                 _lib.call("rh3_selftest_mma_rate", 0, 2000, 0, pattern, ctypes.addressof(ops), _lib.stream())
             ms = _time(fn, 3)
             print(f"mma_rate int8 zero operands, {name}: {ms:.3f} ms per launch, {ops.value / ms / 1e9:.0f} TOP/s", flush=True)
+        # the GEMM main loop without an epilogue: MMA rate against the bytes an SM takes in per stage
+        for src_mb, where in ((48, "L2-resident source (48 MB)"), (2048, "HBM-resident source (2 GB)")):
+            src = torch.randint(-127, 128, (src_mb << 20,), device="cuda", dtype=torch.int8)
+            for fill in (0, 16384, 32768, 49152):
+                ops = ctypes.c_double(0)
+
+                def fn():
+                    _lib.call("rh3_selftest_mma_feed", src.data_ptr(), src.numel(), 40000, fill, ctypes.addressof(ops), _lib.stream())
+                ms = _time(fn, 3)
+                print(f"mma_feed {where}, {fill // 1024} KB per stage: {ms:.3f} ms per launch, {ops.value / ms / 1e9:.0f} TOP/s, "
+                      f"{148 * 40000 * fill / ms / 1e9:.1f} TB/s taken in", flush=True)
+            del src
         return
     if a.case == "conv":
         from rapid_h3_b200 import vae

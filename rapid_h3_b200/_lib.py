@@ -22,6 +22,7 @@ SIGNATURES = {
     "rh3_check_status": [_P, _P],
     "rh3_selftest_wait_expiry": [_I64, _P, _P],
     "rh3_selftest_mma_rate": [_I, _I64, _I, _I, _P, _P],
+    "rh3_selftest_mma_feed": [_P, _I64, _I64, _I, _P, _P],
     "rh3_quant_rows_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_quant_rows_fp8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
     "rh3_quant_tensor_fp8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P, _P],

@@ -261,7 +261,117 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random
   }
 }
 
+// The main loop of a 128 x 256 int8 GEMM tile without an epilogue: a four-stage ring of 48 KB stages; warp 1 streams
+// `fill_bytes` (0 .. 48 KB, multiples of 16 KB) per stage from global memory into the stage by bulk copies that
+// complete on the stage's barrier, warp 0 (converged, one elected lane) waits for the stage, issues four MMAs of
+// 128 x 256 x 32 on it and commits the stage free. Whatever bytes arrive are the int8 operands. What it measures:
+// the MMA rate an SM sustains while it takes in fill_bytes per 512 tensor cycles from L2 / HBM.
+__global__ void __launch_bounds__(128, 1) mma_feed_kernel(const uint8_t* __restrict__ src, long long src_bytes, int stages_total,
+                                                           int fill_bytes, int* status) {
+  constexpr int ST = 4, SB = 48 * 1024;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full[ST], empty[ST];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < ST * SB / 16; i += blockDim.x) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < ST; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  fence_proxy_async_smem();
+  if (warp == 0) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  if (warp == 1) {
+    // producer: every CTA walks its own window of the source so that the SMs do not all read the same lines
+    const long long window = (src_bytes / SB) > 0 ? (src_bytes / SB) : 1;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int i = 0; i < stages_total && ok; ++i) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&empty[stage], phase ^ 1, &abort_flag, status, ST_TIMEOUT_SELFTEST));
+      if (!ok) break;
+      if (elect_one()) {
+        if (fill_bytes > 0) {
+          const uint8_t* g = src + ((static_cast<long long>(blockIdx.x) * 131 + i) % window) * SB;
+          mbar_arrive_expect_tx(&full[stage], fill_bytes);
+          for (int o = 0; o < fill_bytes; o += 16384)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             smem_u32(smem + stage * SB + o)),
+                         "l"(g + o), "r"(16384), "r"(smem_u32(&full[stage]))
+                         : "memory");
+        } else {
+          mbar_arrive(&full[stage]);
+        }
+      }
+      __syncwarp();
+      if (++stage == ST) { stage = 0; phase ^= 1; }
+    }
+  } else if (warp == 0) {
+    constexpr uint32_t idesc = make_idesc(2, 1, 1, 128, 256);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int i = 0; i < stages_total && ok; ++i) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&full[stage], phase, &abort_flag, status, ST_TIMEOUT_SELFTEST));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(smem + stage * SB);
+      if (elect_one()) {
+        mma4_i8_ss(tmem_base + (i & 1) * 256, make_desc_k128(a_addr), make_desc_k128(a_addr + 128 * 128), idesc, 1);
+        mma_commit(&empty[stage]);
+      }
+      __syncwarp();
+      if (++stage == ST) { stage = 0; phase ^= 1; }
+    }
+    // drain: the last commit of every stage that was used
+    for (int q = 0; q < ST && ok; ++q) {
+      const int last = stages_total - 1 - ((stages_total - 1 - q) % ST + ST) % ST;
+      if (last >= 0 && (last % ST) == q)
+        ok = __all_sync(0xffffffffu, mbar_wait(&empty[q], (last / ST) & 1, &abort_flag, status, ST_TIMEOUT_SELFTEST));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 }  // namespace rh3
+
+// The GEMM main loop without an epilogue on every SM (see mma_feed_kernel): `stages` stages of four int8 MMAs of
+// 128 x 256 x 32, each stage preceded by a bulk copy of fill_bytes (0, 16384, 32768 or 49152) from `src` (device
+// memory, src_bytes >= 49152, 16-byte aligned) into the stage. *ops_out = operations of the launch.
+extern "C" int rh3_selftest_mma_feed(const void* src, int64_t src_bytes, int64_t stages, int fill_bytes, double* ops_out,
+                                     cudaStream_t stream) {
+  RH3_CHECK_ARG(stages >= 1 && stages <= (1 << 22), "selftest_mma_feed: stages=%lld must be in [1, 2^22]", (long long)stages);
+  RH3_CHECK_ARG(fill_bytes >= 0 && fill_bytes <= 49152 && fill_bytes % 16384 == 0, "selftest_mma_feed: fill_bytes must be 0, 16384, 32768 or 49152");
+  RH3_CHECK_ARG(fill_bytes == 0 || (src && src_bytes >= 49152 && (reinterpret_cast<uintptr_t>(src) & 15) == 0),
+                "selftest_mma_feed: src must be a 16-byte aligned device buffer of at least 49152 bytes");
+  int* w = rh3::device_status_word();
+  if (!w) return rh3::set_error(RH3_ARG_ERROR, "no device status word (is a CUDA device current?)");
+  const int sms = rh3::device_sm_count();
+  const int smem = 4 * 48 * 1024 + 1024;
+  if (int e = rh3::check_cuda(cudaFuncSetAttribute(rh3::mma_feed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "mma_feed smem"))
+    return e;
+  rh3::mma_feed_kernel<<<sms, 128, smem, stream>>>(static_cast<const uint8_t*>(src), static_cast<long long>(src_bytes),
+                                                   static_cast<int>(stages), fill_bytes, w);
+  if (ops_out) *ops_out = static_cast<double>(sms) * static_cast<double>(stages) * 4.0 * 2.0 * 128.0 * 256.0 * 32.0;
+  return rh3::check_cuda(cudaGetLastError(), "selftest_mma_feed launch");
+}
 
 // Launches the issue-rate probe on every SM; the caller times it with CUDA events. Operations per launch:
 // sm_count * groups * 64 * 2 * 128 * 256 * (32 for kind 0 / 1, 16 for kind 2); *ops_out receives that number.

@@ -65,3 +65,20 @@ def test_tensor_pipe_probe_returns_and_reports_a_plausible_rate(kind, random_ope
     assert tops > (1100 if kind == 2 else 2200), tops
     with pytest.raises(RuntimeError):
         lib.call("rh3_selftest_mma_rate", 3, groups, 0, 0, ctypes.addressof(ops), lib.stream())
+
+
+@pytest.mark.parametrize("fill", [0, 16384, 49152])
+def test_gemm_main_loop_probe_returns_by_itself(fill):
+    """The main-loop probe (bulk copies into a four-stage ring + MMAs, no epilogue) comes back with a clean status
+    word for stage counts that are and are not multiples of the ring size, and refuses bad arguments."""
+    from rapid_h3_b200 import _lib as lib
+    src = torch.randint(-127, 128, (8 << 20,), device="cuda", dtype=torch.int8)
+    ops = ctypes.c_double(0)
+    for stages in (1, 3, 4, 1001):
+        lib.call("rh3_selftest_mma_feed", src.data_ptr(), src.numel(), stages, fill, ctypes.addressof(ops), lib.stream())
+        lib.check_status()
+        assert ops.value == lib.lib().rh3_sm_count() * stages * 4 * 2 * 128 * 256 * 32
+    with pytest.raises(RuntimeError):
+        lib.call("rh3_selftest_mma_feed", src.data_ptr(), src.numel(), 10, 1000, ctypes.addressof(ops), lib.stream())
+    with pytest.raises(RuntimeError):
+        lib.call("rh3_selftest_mma_feed", src.data_ptr(), 100, 10, 16384, ctypes.addressof(ops), lib.stream())
