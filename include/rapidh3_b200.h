@@ -110,6 +110,10 @@ int rh3_norm_mod_rot_quant_rows_i8(const void* x, int64_t ldx, const void* w, fl
                                    void* q, int64_t ldq, float* s, cudaStream_t stream);
 
 /* ---- W8A8 row-wise-scaled GEMMs (tensor-core bound) ---------------------------------------- */
+/* Kernel choice of the GEMM entries below (no reference counterpart): 0 = one CTA per 128 x 256 tile, 1 (the default) = CTA
+ * pairs (clusters of two, tcgen05 cta_group::2) on 256 x 256 tiles, each CTA loading its own half of B, for calls with
+ * more than 128 rows and columns. Returns the previous setting; process-wide. Results are the same numbers either way. */
+int rh3_gemm_use_pairs(int on);
 /* out[M,N] bf16 = ((acc * xs[m]) * ws[n]) + bias[n]; xq[M,K] (row stride lda), wq[N,K] contiguous.
  * bias may be NULL. acc_dump (optional, [M,N] int32 / fp32 bits) receives the raw accumulators.
  * Replaces int8_rowwise_gemm / fp8_rowwise_gemm (custom_nodes/rapid_h3/csrc/fp8_rowwise.cu:512-584)

@@ -21,6 +21,7 @@ SIGNATURES = {
     "rh3_sm_count": [],
     "rh3_check_status": [_P, _P],
     "rh3_selftest_wait_expiry": [_I64, _P, _P],
+    "rh3_gemm_use_pairs": [_I],
     "rh3_selftest_mma_rate": [_I, _I64, _I, _I, _P, _P],
     "rh3_selftest_mma_feed": [_P, _I64, _I64, _I, _P, _P],
     "rh3_quant_rows_i8": [_P, _I64, _I64, _I64, _P, _I64, _P, _P],
@@ -74,7 +75,7 @@ KIND_I8, KIND_F8 = 0, 1
 _lib = None
 
 # kernels launched per entry point (for launch accounting in benchmarks)
-LAUNCHES = {"rh3_attn_kv_stats": 2, "rh3_attn_kv_stats_noalloc": 2, "rh3_attn_prepass": 3, "rh3_attn_tok_prepass": 5, "rh3_quant_tensor_fp8": 2, "rh3_version": 0, "rh3_sm_count": 0, "rh3_check_status": 0,
+LAUNCHES = {"rh3_attn_kv_stats": 2, "rh3_attn_kv_stats_noalloc": 2, "rh3_attn_prepass": 3, "rh3_attn_tok_prepass": 5, "rh3_quant_tensor_fp8": 2, "rh3_version": 0, "rh3_gemm_use_pairs": 0, "rh3_sm_count": 0, "rh3_check_status": 0,
             "rh3_attn_kv_stats_scratch_bytes": 0, "rh3_conv3d_gn_part_rows": 0}
 launch_count = 0
 

@@ -182,6 +182,50 @@ __device__ __forceinline__ void tmem_relinquish() {  // whole warp
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+// ---- CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) ----
+// The same warp index of BOTH CTAs of the pair executes alloc / relinquish / dealloc.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {  // whole warp, both CTAs
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// all threads of both CTAs
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's shared-memory window, of this CTA's shared-memory location `p` as seen in CTA `rank`
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+  return r;
+}
+// arrive on the barrier at this offset in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t rank) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr(bar, rank)) : "memory");
+}
+// TMA tile load into THIS CTA's shared memory whose bytes are counted on the barrier at the same offset in the pair's
+// even CTA (`leader_bar` = cluster_addr(bar, 0)); every CTA fetches its own tile
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+// all MMAs issued so far by this thread arrive, when they retire, on the barrier at the given cluster address
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -248,6 +292,34 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
         : "memory");                                                                                           \
   }
 RH3_DEFINE_MMA4(mma4_i8_ss, "i8")
+// The same four MMAs issued for a CTA pair (256 rows: 128 from each CTA's A tile; B's N rows split between the two
+// CTAs' tiles; each CTA's TMEM receives its 128 rows). Issued by one thread of the pair's even CTA.
+#define RH3_DEFINE_MMA4_PAIR(NAME, KIND)                                                                       \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,       \
+                                       uint32_t acc_first) {                                                    \
+    asm volatile(                                                                                              \
+        "{\n\t"                                                                                                \
+        ".reg .pred p, q;\n\t"                                                                                 \
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                                                                \
+        "setp.ne.b32 p, %4, 0;\n\t"                                                                            \
+        "setp.eq.b32 q, 0, 0;\n\t"                                                                             \
+        "add.u64 a1, %1, 2;\n\t"                                                                               \
+        "add.u64 b1, %2, 2;\n\t"                                                                               \
+        "add.u64 a2, %1, 4;\n\t"                                                                               \
+        "add.u64 b2, %2, 4;\n\t"                                                                               \
+        "add.u64 a3, %1, 6;\n\t"                                                                               \
+        "add.u64 b3, %2, 6;\n\t"                                                                               \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, p;\n\t"                                     \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], a1, b1, %3, q;\n\t"                                     \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], a2, b2, %3, q;\n\t"                                     \
+        "tcgen05.mma.cta_group::2.kind::" KIND " [%0], a3, b3, %3, q;\n\t"                                     \
+        "}\n" ::"r"(d_tmem),                                                                                   \
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc_first)                                                   \
+        : "memory");                                                                                           \
+  }
+RH3_DEFINE_MMA4_PAIR(mma4_i8_pair, "i8")
+RH3_DEFINE_MMA4_PAIR(mma4_f8_pair, "f8f6f4")
+#undef RH3_DEFINE_MMA4_PAIR
 RH3_DEFINE_MMA4(mma4_f8_ss, "f8f6f4")
 RH3_DEFINE_MMA4(mma4_f16_ss, "f16")
 #undef RH3_DEFINE_MMA4
