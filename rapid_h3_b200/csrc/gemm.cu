@@ -88,11 +88,8 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 template <int KIND_F8, int EPI>
 __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmemTail* tail, uint32_t t_row, int row,
                                              bool row_ok, float xs, int n0) {
-#pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
-    uint32_t r[32];
-    tmem_ld32(t_row + c * 32, r);
-    tmem_ld_wait_regs(r);
+  // two 32-column chunks are loaded per wait, so a tile costs four TMEM round trips instead of eight
+  auto chunk = [&](const uint32_t* r, int c) {
     const int col0 = n0 + c * 32;
     if (row_ok && col0 < p.N) {
       if (p.acc_dump) {
@@ -204,7 +201,7 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
               for (int j = 0; j < 4; ++j) {
                 const float gv = bf16_round(y[b + j]);
                 const float uv = bf16_round(y[b + 4 + j]);
-                h[j] = gv / (1.f + __expf(-gv)) * uv;
+                h[j] = __fdividef(gv, 1.f + __expf(-gv)) * uv;
               }
               w[q * 2] = pack_bf16x2(h[0], h[1]);
               w[q * 2 + 1] = pack_bf16x2(h[2], h[3]);
@@ -214,6 +211,16 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
         }
       }
     }
+  };
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; c += 2) {
+    uint32_t ra[32], rb[32];
+    tmem_ld32(t_row + c * 32, ra);
+    tmem_ld32(t_row + c * 32 + 32, rb);
+    tmem_ld_wait_regs(ra);
+    tmem_ld_wait_regs(rb);
+    chunk(ra, c);
+    chunk(rb, c + 1);
   }
 }
 
