@@ -222,6 +222,14 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(leader_bar), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_5d_pair(void* smem_dst, const CUtensorMap* m, int c0, int c1, int c2, int c3,
+                                                 int c4, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], "
+      "[%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
 // all MMAs issued so far by this thread arrive, when they retire, on the barrier at the given cluster address
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
@@ -319,6 +327,7 @@ RH3_DEFINE_MMA4(mma4_i8_ss, "i8")
   }
 RH3_DEFINE_MMA4_PAIR(mma4_i8_pair, "i8")
 RH3_DEFINE_MMA4_PAIR(mma4_f8_pair, "f8f6f4")
+RH3_DEFINE_MMA4_PAIR(mma4_f16_pair, "f16")
 #undef RH3_DEFINE_MMA4_PAIR
 RH3_DEFINE_MMA4(mma4_f8_ss, "f8f6f4")
 RH3_DEFINE_MMA4(mma4_f16_ss, "f16")
@@ -564,6 +573,8 @@ int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, uint32_t elem_bytes, 
 int make_tmap_nd(CUtensorMap* out, CUtensorMapDataType dt, uint32_t elem_bytes, const void* base, int rank,
                  const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz);
 int device_sm_count();
+// 1 when the GEMM and convolution entries launch their CTA-pair kernels (rh3_gemm_use_pairs)
+int pairs_enabled();
 // device status word (one int per device, lazily allocated at library load / first use)
 int* device_status_word();
 int read_and_clear_status(cudaStream_t stream, int* out);

@@ -75,6 +75,79 @@ __device__ __forceinline__ TileCoord conv_tile(int tile, const ConvParams& p, in
   return c;
 }
 
+// The epilogue of one output tile for one thread (= one output site): BN columns, 32 at a time from TMEM, bias and
+// residual added, bf16 stored, GroupNorm partials of the warp's 32 rows. `acc_tmem` = TMEM address of the
+// accumulator's first column; `tile_ok` false = this CTA has no tile here (the odd tile of a pair): nothing is stored.
+__device__ __forceinline__ void conv_epilogue_tile(const ConvParams& p, const float* bias_s, uint32_t acc_tmem,
+                                                   const TileCoord& c, int n0, int m_tile, bool tile_ok, int quad, int lane) {
+  const int gs = p.Cout / GN_GROUPS;  // channels per GroupNorm group (used only when gn_part != null)
+  const int m = quad * 32 + lane;
+  const int hh = m / p.bw, ww = m - hh * p.bw;
+  const int h = c.h0 + hh, w = c.w0 + ww;
+  const bool row_ok = tile_ok && m < p.bh * p.bw && h < p.H && w < p.W;
+  const int64_t site = ((static_cast<int64_t>(c.n) * p.T + c.t) * p.H + h) * p.W + w;
+  const uint32_t t_row = acc_tmem + (static_cast<uint32_t>(quad * 32) << 16);
+  float* part = (p.gn_part && tile_ok) ? p.gn_part + (static_cast<int64_t>(m_tile) * 4 + quad) * GN_GROUPS * 2 : nullptr;
+#pragma unroll 1
+  for (int cb = 0; cb < p.BN; cb += 32) {
+    uint32_t r[32];
+    tmem_ld32(t_row + cb, r);
+    tmem_ld_wait_regs(r);
+    const int col0 = n0 + cb;
+    float y[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(r[j]) + bias_s[cb + j];
+    if (p.residual && row_ok) {
+      const __nv_bfloat16* rs = p.residual + site * p.Cout + col0;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (col0 + g * 8 + 8 <= p.Cout) {
+          const uint4 v = *reinterpret_cast<const uint4*>(rs + g * 8);
+          const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            y[g * 8 + 2 * j] += bf16_lo(vw[j]);
+            y[g * 8 + 2 * j + 1] += bf16_hi(vw[j]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) y[j] = row_ok ? bf16_round(y[j]) : 0.f;  // what is stored; rows off the edge add 0
+    if (row_ok) {
+      __nv_bfloat16* o = p.out + site * p.Cout + col0;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (col0 + g * 8 + 8 <= p.Cout) {
+          *reinterpret_cast<uint4*>(o + g * 8) =
+              make_uint4(pack_bf16x2(y[g * 8], y[g * 8 + 1]), pack_bf16x2(y[g * 8 + 2], y[g * 8 + 3]),
+                         pack_bf16x2(y[g * 8 + 4], y[g * 8 + 5]), pack_bf16x2(y[g * 8 + 6], y[g * 8 + 7]));
+        }
+      }
+    }
+    if (part) {
+      // GroupNorm partials of this warp's 32 rows: channels of a group are summed per row, rows by shuffle
+      for (int j0 = 0; j0 < 32; j0 += gs) {
+        float s1 = 0.f, s2 = 0.f;
+        for (int j = j0; j < j0 + gs && j < 32; ++j) {
+          s1 += y[j];
+          s2 += y[j] * y[j];
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+          s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+          s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+        }
+        const int grp = (col0 + j0) / gs;
+        if (lane == 0 && col0 + j0 < p.Cout) {
+          part[grp * 2] = s1;
+          part[grp * 2 + 1] = s2;
+        }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(CONV_THREADS, 1)
 conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
               const ConvParams p) {
@@ -177,7 +250,6 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
     // ------------------------------ epilogue (warps 2..5) ------------------------------
     const int quad = warp & 3;
     const int et = threadIdx.x - 64;
-    const int gs = p.Cout / GN_GROUPS;  // channels per GroupNorm group (used only when gn_part != null)
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -191,72 +263,7 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
       const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
       if (bar_sync_or(1, 128, !got)) break;
       tc_fence_after();
-      const int m = quad * 32 + lane;
-      const int hh = m / p.bw, ww = m - hh * p.bw;
-      const int h = c.h0 + hh, w = c.w0 + ww;
-      const bool row_ok = m < p.bh * p.bw && h < p.H && w < p.W;
-      const int64_t site = ((static_cast<int64_t>(c.n) * p.T + c.t) * p.H + h) * p.W + w;
-      const uint32_t t_row = tmem_base + acc * 256 + (static_cast<uint32_t>(quad * 32) << 16);
-      const int m_tile = tile / num_n;
-      float* part = p.gn_part ? p.gn_part + (static_cast<int64_t>(m_tile) * 4 + quad) * GN_GROUPS * 2 : nullptr;
-#pragma unroll 1
-      for (int cb = 0; cb < p.BN; cb += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_row + cb, r);
-        tmem_ld_wait_regs(r);
-        const int col0 = n0 + cb;
-        float y[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(r[j]) + tail->bias[cb + j];
-        if (p.residual && row_ok) {
-          const __nv_bfloat16* rs = p.residual + site * p.Cout + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col0 + g * 8 + 8 <= p.Cout) {
-              const uint4 v = *reinterpret_cast<const uint4*>(rs + g * 8);
-              const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                y[g * 8 + 2 * j] += bf16_lo(vw[j]);
-                y[g * 8 + 2 * j + 1] += bf16_hi(vw[j]);
-              }
-            }
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = row_ok ? bf16_round(y[j]) : 0.f;  // what is stored; rows off the edge add 0
-        if (row_ok) {
-          __nv_bfloat16* o = p.out + site * p.Cout + col0;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col0 + g * 8 + 8 <= p.Cout) {
-              *reinterpret_cast<uint4*>(o + g * 8) =
-                  make_uint4(pack_bf16x2(y[g * 8], y[g * 8 + 1]), pack_bf16x2(y[g * 8 + 2], y[g * 8 + 3]),
-                             pack_bf16x2(y[g * 8 + 4], y[g * 8 + 5]), pack_bf16x2(y[g * 8 + 6], y[g * 8 + 7]));
-            }
-          }
-        }
-        if (part) {
-          // GroupNorm partials of this warp's 32 rows: channels of a group are summed per row, rows by shuffle
-          for (int j0 = 0; j0 < 32; j0 += gs) {
-            float s1 = 0.f, s2 = 0.f;
-            for (int j = j0; j < j0 + gs && j < 32; ++j) {
-              s1 += y[j];
-              s2 += y[j] * y[j];
-            }
-#pragma unroll
-            for (int o = 16; o; o >>= 1) {
-              s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-              s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-            }
-            const int grp = (col0 + j0) / gs;
-            if (lane == 0 && col0 + j0 < p.Cout) {
-              part[grp * 2] = s1;
-              part[grp * 2 + 1] = s2;
-            }
-          }
-        }
-      }
+      conv_epilogue_tile(p, tail->bias, tmem_base + acc * 256, c, n0, tile / num_n, true, quad, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->acc_empty[acc]);
@@ -273,6 +280,190 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same convolution on CTA pairs (clusters of two, tcgen05 cta_group::2). A pair computes two neighbouring site
+// tiles (m = 2 * pair_m + rank) x BN output channels with MMAs of 256 rows: every CTA fetches the shifted input box of
+// its own site tile and HALF of the BN weight rows (rank r: rows [r * BN/2, (r+1) * BN/2) of the column tile), so an
+// SM takes in 16 KB + BN/2 * 128 B per K chunk instead of 16 KB + BN * 128 B: the single-CTA kernel is bound by that
+// ingest, not by the tensor pipe. Each CTA's TMEM receives its own 128 sites x BN channels and its own epilogue
+// warps drain them exactly as in the single-CTA kernel (same fp32 accumulation order: results are identical).
+// When the number of site tiles is odd, the odd CTA of the last pair loads the last valid tile again and stores nothing.
+// Barriers as in the GEMM's pair kernel: both CTAs' loads count on the even CTA's `full`; stage release and
+// accumulator hand-over are one commit per CTA; every wait is bounded; the two cluster barriers are reached by all.
+// ---------------------------------------------------------------------------------------------
+constexpr int CP_STAGES = 6;
+constexpr int CP_STAGE_BYTES = CA_BYTES + 128 * 128;  // 32 KB: A box + at most 128 weight rows
+
+struct __align__(8) ConvPairSmemTail {
+  uint64_t full[CP_STAGES];
+  uint64_t empty[CP_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float bias[256];
+};
+constexpr int CONV_PAIR_SMEM_BYTES = CP_STAGES * CP_STAGE_BYTES + sizeof(ConvPairSmemTail) + 1024;
+
+// site tile m and column tile of pair-tile index `tile` for CTA `rank`: column tiles fastest, then pairs of site tiles
+__device__ __forceinline__ void conv_pair_tile(int tile, int rank, int num_m, int num_n, int& m, int& n_blk, bool& ok) {
+  n_blk = tile % num_n;
+  m = (tile / num_n) * 2 + rank;
+  ok = m < num_m;
+  if (!ok) m = num_m - 1;
+}
+
+__global__ void __launch_bounds__(CONV_THREADS, 1)
+conv3d_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
+                   const ConvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  ConvPairSmemTail* tail = reinterpret_cast<ConvPairSmemTail*>(smem + CP_STAGES * CP_STAGE_BYTES);
+  volatile int* abort_flag = &tail->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_cta_rank());   // 0 = the even CTA: it issues the MMAs
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_n = (p.Cout + p.BN - 1) / p.BN;
+  const int num_m = p.N * p.T * p.tiles_h * p.tiles_w;
+  const int num_tiles = ((num_m + 1) >> 1) * num_n;
+  const int chunks = p.Cin / CBK;
+  const int num_kb = 27 * chunks;
+  const int half_n = p.BN >> 1;
+  const uint32_t stage_tx = 2u * (static_cast<uint32_t>(p.bh * p.bw) * 128u + static_cast<uint32_t>(half_n) * 128u);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < CP_STAGES; ++s) {
+      mbar_init(&tail->full[s], 1);     // the even CTA's: one arrive.expect_tx for the bytes of both CTAs
+      mbar_init(&tail->empty[s], 1);    // one commit per CTA
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tail->acc_full[b], 1);
+      mbar_init(&tail->acc_empty[b], 8);  // the even CTA's: one arrival per epilogue warp of both CTAs
+    }
+    tail->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tail->tmem_base, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before anything arrives on them from the other side
+  tc_fence_after();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (elect_one()) {
+      tma_prefetch_desc(&tma_x);
+      tma_prefetch_desc(&tma_w);
+    }
+    __syncwarp();
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      int m, n_blk;
+      bool tile_ok;
+      conv_pair_tile(tile, rank, num_m, num_n, m, n_blk, tile_ok);
+      const TileCoord c = conv_tile(m * num_n + n_blk, p, num_n);
+      const int wrow0 = n_blk * p.BN + rank * half_n;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int tap = kb / chunks, cc = kb - tap * chunks;
+        const int dt = tap / 9, dh = (tap / 3) % 3, dw = tap % 3;
+        ok = __all_sync(0xffffffffu, mbar_wait(&tail->empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY));
+        if (!ok) break;
+        uint8_t* sa = smem + stage * CP_STAGE_BYTES;
+        const uint32_t leader_full = cluster_addr(&tail->full[stage], 0);
+        if (elect_one()) {
+          if (rank == 0) mbar_arrive_expect_tx(&tail->full[stage], stage_tx);
+          tma_load_5d_pair(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2 + p.halo, c.n, leader_full);
+          tma_load_2d_pair(sa + CA_BYTES, &tma_w, tap * p.Cin + cc * CBK, wrow0, leader_full);
+        }
+        __syncwarp();
+        if (++stage == CP_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only; converged warp, one elected lane) ------------------------------
+    if (rank == 0) {
+      const uint32_t idesc = make_idesc(1, 1, 1, 2 * CBM, p.BN);  // f32 += bf16 * bf16, 256 rows over the pair
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&tail->acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, ST_TIMEOUT_ACC_EMPTY));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL));
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * CP_STAGE_BYTES);
+          const uint32_t b_addr = a_addr + CA_BYTES;
+          const uint32_t empty0 = cluster_addr(&tail->empty[stage], 0), empty1 = cluster_addr(&tail->empty[stage], 1);
+          if (elect_one()) {
+            mma4_f16_pair(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
+            mma_commit_pair(empty0);   // the stage is free in both CTAs once these MMAs have read it
+            mma_commit_pair(empty1);
+          }
+          __syncwarp();
+          if (++stage == CP_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        const uint32_t full0 = cluster_addr(&tail->acc_full[acc], 0), full1 = cluster_addr(&tail->acc_full[acc], 1);
+        if (elect_one()) {
+          mma_commit_pair(full0);
+          mma_commit_pair(full1);
+        }
+        __syncwarp();
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5 of both CTAs) ------------------------------
+    const int quad = warp & 3;
+    const int et = threadIdx.x - 64;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      int m, n_blk;
+      bool tile_ok;
+      conv_pair_tile(tile, rank, num_m, num_n, m, n_blk, tile_ok);
+      const TileCoord c = conv_tile(m * num_n + n_blk, p, num_n);
+      const int n0 = n_blk * p.BN;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int i = et; i < p.BN; i += 128)
+        tail->bias[i] = (p.bias && n0 + i < p.Cout) ? __bfloat162float(p.bias[n0 + i]) : 0.f;
+      const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
+      if (bar_sync_or(1, 128, !got)) break;
+      tc_fence_after();
+      conv_epilogue_tile(p, tail->bias, tmem_base + acc * 256, c, n0, m, tile_ok, quad, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(&tail->acc_empty[acc], 0);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // nothing of the other CTA is in flight towards this CTA's shared memory or barriers any more
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -451,11 +642,42 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
   if (int e = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, 27 * Cin, Cout, 27 * Cin * 2, CBK, p.BN,
                            CU_TENSOR_MAP_SWIZZLE_128B))
     return e;
+  const int64_t num_m = N * T * p.tiles_h * p.tiles_w, num_n = (Cout + p.BN - 1) / p.BN;
+  // CTA pairs: two site tiles per pair and BN/2 weight rows per CTA (a multiple of 16, so every MMA shape is legal)
+  if (pairs_enabled() && num_m >= 2 && p.BN % 32 == 0) {
+    CUtensorMap twp;
+    if (int e = make_tmap_2d(&twp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, 27 * Cin, Cout, 27 * Cin * 2, CBK, p.BN / 2,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+    if (int e = check_cuda(cudaFuncSetAttribute(conv3d_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                CONV_PAIR_SMEM_BYTES),
+                           "conv3d pair smem attribute"))
+      return e;
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.blockDim = dim3(CONV_THREADS);
+    cfg.dynamicSmemBytes = CONV_PAIR_SMEM_BYTES;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(2 * (device_sm_count() / 2));
+    int max_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, conv3d_pair_kernel, &cfg) != cudaSuccess || max_clusters < 1)
+      return set_error(RH3_ARG_ERROR, "conv3d pair: no cluster of two CTAs can be resident");
+    const int64_t pair_tiles = (num_m + 1) / 2 * num_n;
+    cfg.gridDim = dim3(2 * static_cast<unsigned>(pair_tiles < max_clusters ? pair_tiles : max_clusters));
+    if (int e = check_cuda(cudaLaunchKernelEx(&cfg, conv3d_pair_kernel, tx, twp, p), "conv3d pair launch")) return e;
+    return check_cuda(cudaGetLastError(), "conv3d pair launch");
+  }
   if (int e = check_cuda(cudaFuncSetAttribute(conv3d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               CONV_SMEM_BYTES),
                          "conv3d smem attribute"))
     return e;
-  const int64_t tiles = N * T * p.tiles_h * p.tiles_w * ((Cout + p.BN - 1) / p.BN);
+  const int64_t tiles = num_m * num_n;
   const int grid = tiles < device_sm_count() ? (int)tiles : device_sm_count();
   conv3d_kernel<<<grid, CONV_THREADS, CONV_SMEM_BYTES, stream>>>(tx, tw, p);
   return check_cuda(cudaGetLastError(), "conv3d_causal launch");

@@ -624,13 +624,15 @@ int gemm_common(const void* xq, int64_t lda, const void* wq, const float* xs, co
 }
 
 }  // namespace
+int pairs_enabled() { return g_use_pairs.load(std::memory_order_relaxed); }
 }  // namespace rh3
 
 using namespace rh3;
 
 // Selects the kernel the GEMM entries launch: 0 = one CTA per 128 x 256 tile, 1 (default) = CTA pairs on 256 x 256
 // tiles (gemm_pair_kernel) for every call with more than 128 rows and more than 128 columns. Returns the previous
-// setting. Results are identical (int32 accumulators, same epilogue).
+// setting. Results are identical (int32 accumulators, same epilogue). The convolution follows the same switch
+// (conv3d_pair_kernel: fp32 accumulation in the same order, identical results).
 extern "C" int rh3_gemm_use_pairs(int on) { return g_use_pairs.exchange(on ? 1 : 0); }
 
 extern "C" int rh3_gemm_w8a8(const void* xq, int64_t lda, const void* wq, const float* xs, const float* ws,
