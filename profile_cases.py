@@ -46,7 +46,10 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--rotate", action="store_true", help="attn / prepass: the token-scaled numerics")
     ap.add_argument("--rope", action="store_true", help="prepass: with the per-head RMSNorm + RoPE fused in")
+    ap.add_argument("--single-cta", action="store_true", help="gemm / conv / vae: the single-CTA kernels instead of CTA pairs")
     a = ap.parse_args()
+    if a.single_cta:
+        _lib.lib().rh3_gemm_use_pairs(0)
     g = torch.Generator(device="cuda").manual_seed(0)
 
     def randn(*shape):

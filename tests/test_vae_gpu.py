@@ -46,6 +46,33 @@ def test_conv3d_causal_matches_oracle(vae, shape):
         assert torch.allclose(sums[..., 1], (yd * yd).sum(dim=(1, 3)), rtol=1e-5)
 
 
+@pytest.mark.parametrize("shape", [(1, 3, 6, 21, 64, 64), (2, 4, 9, 10, 128, 256), (1, 5, 7, 5, 192, 192),
+                                   (1, 2, 24, 42, 64, 512), (1, 2, 6, 7, 64, 288)])
+def test_cta_pair_kernel_equals_the_single_cta_kernel(vae, shape):
+    """The convolution on CTA pairs (two site tiles per pair, half of the weight rows per CTA; the default) against
+    the single-CTA kernel on the same inputs: outputs and GroupNorm partial sums bit for bit, including an odd number
+    of site tiles (the odd CTA of the last pair has no tile) and column tiles split over several accumulators."""
+    v, lib = vae
+    n, t, h, w, cin, cout = shape
+    g = torch.Generator().manual_seed(sum(shape) + 1)
+    x = torch.randn(n, t, h, w, cin, generator=g).to(torch.bfloat16).cuda()
+    wt = (0.05 * torch.randn(cout, 27, cin, generator=g)).to(torch.bfloat16).cuda()
+    b = (0.1 * torch.randn(cout, generator=g)).to(torch.bfloat16).cuda()
+    res = torch.randn(n, t, h, w, cout, generator=g).to(torch.bfloat16).cuda()
+    stats = cout % 32 == 0 and 32 % (cout // 32) == 0
+    prev = lib.lib().rh3_gemm_use_pairs(1)   # returns the previous setting
+    try:
+        y_pair, part_pair = v.conv3d_causal(x, wt, b, res, want_stats=stats)
+        lib.lib().rh3_gemm_use_pairs(0)
+        y_one, part_one = v.conv3d_causal(x, wt, b, res, want_stats=stats)
+    finally:
+        lib.lib().rh3_gemm_use_pairs(prev)
+    lib.check_status()
+    assert torch.equal(y_pair, y_one)
+    if stats:
+        assert torch.equal(part_pair, part_one)
+
+
 def test_causality(vae):
     """Changing frame t must leave every output frame before t untouched."""
     v, lib = vae
