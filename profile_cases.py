@@ -46,6 +46,7 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--rotate", action="store_true", help="attn / prepass: the token-scaled numerics")
     ap.add_argument("--rope", action="store_true", help="prepass: with the per-head RMSNorm + RoPE fused in")
+    ap.add_argument("--no-stats", action="store_true", help="conv: without the GroupNorm partial sums")
     ap.add_argument("--single-cta", action="store_true", help="gemm / conv / vae: the single-CTA kernels instead of CTA pairs")
     a = ap.parse_args()
     if a.single_cta:
@@ -96,7 +97,7 @@ def main():
         from rapid_h3_b200 import vae
         x = randn(1, a.T, a.HH, a.WW, a.Cin).to(torch.bfloat16)
         w = (0.02 * randn(a.Cout, 27, a.Cin)).to(torch.bfloat16)
-        ms = _time(lambda: vae.conv3d_causal(x, w, want_stats=a.Cout % 32 == 0), a.iters)
+        ms = _time(lambda: vae.conv3d_causal(x, w, want_stats=a.Cout % 32 == 0 and not a.no_stats), a.iters)
         fl = 2.0 * a.T * a.HH * a.WW * a.Cin * a.Cout * 27
         print(f"conv3d {a.T}x{a.HH}x{a.WW} {a.Cin}->{a.Cout}: {ms:.3f} ms, {fl / ms / 1e9:.1f} TFLOP/s")
         return

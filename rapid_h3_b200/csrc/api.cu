@@ -166,15 +166,17 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random
   const uint32_t tmem_base = tmem_base_s;
   if (threadIdx.x == 0 && pattern != 3) {
     const uint64_t a_desc = make_desc_k128(smem_u32(smem)), b_desc = make_desc_k128(smem_u32(smem + 128 * 128));
-    constexpr uint32_t idesc = KIND == 0 ? make_idesc(2, 1, 1, 128, 256) : (KIND == 1 ? make_idesc(1, 0, 0, 128, 256)
-                                                                                        : make_idesc(1, 1, 1, 128, 256));
+    // pattern 4: the same back-to-back issue with 128-column MMAs (half the work per instruction)
+    const int ncols = pattern == 4 ? 128 : 256;
+    const uint32_t idesc = KIND == 0 ? make_idesc(2, 1, 1, 128, ncols) : (KIND == 1 ? make_idesc(1, 0, 0, 128, ncols)
+                                                                                     : make_idesc(1, 1, 1, 128, ncols));
     bool ok = true;
     auto mma4 = [&](uint32_t d, uint64_t a, uint64_t b) {
       if (KIND == 0) mma4_i8_ss(d, a, b, idesc, 1);
       else if (KIND == 1) mma4_f8_ss(d, a, b, idesc, 1);
       else mma4_f16_ss(d, a, b, idesc, 1);
     };
-    if (pattern == 0) {
+    if (pattern == 0 || pattern == 4) {
       for (int g = 0; g < groups && ok; ++g) {
 #pragma unroll 1
         for (int i = 0; i < 16; ++i) mma4(tmem_base + (i & 1) * 256, a_desc, b_desc);   // 16 x 4 MMAs
@@ -225,8 +227,10 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int groups, int random
     // The same ring with the WHOLE warp in the loop (waits, counters and descriptors are warp-uniform, so they can live
     // in the uniform datapath) and one elected lane issuing the MMAs and the commit.
     const uint64_t a_desc = make_desc_k128(smem_u32(smem)), b_desc = make_desc_k128(smem_u32(smem + 128 * 128));
-    constexpr uint32_t idesc = KIND == 0 ? make_idesc(2, 1, 1, 128, 256) : (KIND == 1 ? make_idesc(1, 0, 0, 128, 256)
-                                                                                        : make_idesc(1, 1, 1, 128, 256));
+    // pattern 4: the same back-to-back issue with 128-column MMAs (half the work per instruction)
+    const int ncols = pattern == 4 ? 128 : 256;
+    const uint32_t idesc = KIND == 0 ? make_idesc(2, 1, 1, 128, ncols) : (KIND == 1 ? make_idesc(1, 0, 0, 128, ncols)
+                                                                                     : make_idesc(1, 1, 1, 128, ncols));
     const int n = groups * 16;
     const int stage_stride = (groups >> 20) * 1024;
     int stage = 0;
@@ -379,7 +383,7 @@ extern "C" int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operan
                                      cudaStream_t stream) {
   RH3_CHECK_ARG(kind >= 0 && kind <= 2, "selftest_mma_rate: kind must be 0 (i8), 1 (e4m3) or 2 (bf16)");
   RH3_CHECK_ARG(groups >= 1 && groups <= (1 << 16), "selftest_mma_rate: groups=%lld must be in [1, 65536]", (long long)groups);
-  RH3_CHECK_ARG(pattern >= 0 && pattern <= 3, "selftest_mma_rate: pattern must be 0..3");
+  RH3_CHECK_ARG(pattern >= 0 && pattern <= 4, "selftest_mma_rate: pattern must be 0..4");
   int* w = rh3::device_status_word();
   if (!w) return rh3::set_error(RH3_ARG_ERROR, "no device status word (is a CUDA device current?)");
   const int sms = rh3::device_sm_count();
@@ -391,7 +395,8 @@ extern "C" int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operan
     return rh3::check_cuda(cudaGetLastError(), "selftest_mma_rate launch");
   };
   int e = kind == 0 ? launch(rh3::mma_rate_kernel<0>) : (kind == 1 ? launch(rh3::mma_rate_kernel<1>) : launch(rh3::mma_rate_kernel<2>));
-  if (ops_out) *ops_out = static_cast<double>(sms) * static_cast<double>(groups) * 64.0 * 2.0 * 128.0 * 256.0 * (kind == 2 ? 16.0 : 32.0);
+  if (ops_out)
+    *ops_out = static_cast<double>(sms) * static_cast<double>(groups) * 64.0 * 2.0 * 128.0 * (pattern == 4 ? 128.0 : 256.0) * (kind == 2 ? 16.0 : 32.0);
   return e;
 }
 

@@ -10,7 +10,9 @@
 // fetched by a 5-D TMA tensor copy whose out-of-range coordinates are filled with zeros (that is the
 // padding). One output tile = bh x bw sites of one frame (bh * bw <= 128 rows of the MMA) x BN output
 // channels; the K loop runs over 27 taps x Cin/64 channel chunks (64 bf16 = one 128-byte swizzled row).
-// Same warp roles, 4-stage ring and double-buffered TMEM accumulators as the W8A8 GEMM.
+// Same warp roles and double-buffered TMEM accumulators as the W8A8 GEMM; the ring has as many stages as fit in
+// shared memory (4 of 48 KB at 256 output channels per tile, up to 12 for narrow tiles): a stage of a narrow tile
+// holds few tensor cycles of work, and the ring has to cover the L2 latency with them.
 // The epilogue also emits per-tile partial sums (sum, sum of squares of the rounded outputs) per
 // GroupNorm group, so the statistics of the next GroupNorm cost no extra pass over the activations.
 //
@@ -25,10 +27,10 @@ namespace {
 
 constexpr int CBM = 128;        // MMA rows (output sites per tile, bh * bw of them used)
 constexpr int CBK = 64;         // channels per K chunk (128 bytes of bf16)
-constexpr int CSTAGES = 4;
 constexpr int CA_BYTES = CBM * 128;
-constexpr int CB_BYTES = 256 * 128;
-constexpr int CSTAGE_BYTES = CA_BYTES + CB_BYTES;
+constexpr int CMAX_STAGES = 12;       // ring depth: as many stages of CA_BYTES + (weight rows) * 128 bytes as fit
+constexpr int CTAIL_BYTES = 2048;     // barriers and the staged bias, in front of the ring
+constexpr int CSMEM_BUDGET = 227 * 1024 - 1024 - CTAIL_BYTES;   // what the ring may take (1 KB of alignment slack)
 constexpr int CONV_THREADS = 192;
 constexpr int GN_GROUPS = 32;
 
@@ -42,12 +44,14 @@ struct ConvParams {
   const __nv_bfloat16* residual;  // [N,T,H,W,Cout] or null
   __nv_bfloat16* out;
   float* gn_part;      // [num_m_tiles * 4][32][2] partial (sum, sumsq) per GroupNorm group, or null
+  int stages, stage_bytes;   // ring: stage_bytes = kch * chunk_bytes
+  int kch, chunk_bytes;      // K chunks per stage (one barrier round trip each), CA_BYTES + (weight rows a CTA loads) * 128
   int* status;
 };
 
 struct __align__(8) ConvSmemTail {
-  uint64_t full[CSTAGES];
-  uint64_t empty[CSTAGES];
+  uint64_t full[CMAX_STAGES];
+  uint64_t empty[CMAX_STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
@@ -55,7 +59,7 @@ struct __align__(8) ConvSmemTail {
   float bias[256];
 };
 
-constexpr int CONV_SMEM_BYTES = CSTAGES * CSTAGE_BYTES + sizeof(ConvSmemTail) + 1024;
+static_assert(sizeof(ConvSmemTail) <= CTAIL_BYTES, "tail does not fit");
 
 struct TileCoord {
   int n, t, h0, w0, n_blk;
@@ -73,6 +77,33 @@ __device__ __forceinline__ TileCoord conv_tile(int tile, const ConvParams& p, in
   c.t = m % p.T;
   c.n = m / p.T;
   return c;
+}
+
+// GroupNorm partials of a warp's 32 rows over one 32-column chunk: the GS channels of a group are summed per row
+// (in channel order), the 32 rows by an xor butterfly; lane 0 writes (sum, sum of squares) of every group the chunk
+// holds. GS is a template parameter so that every index into y[] is static (a run-time group width sends the array
+// to local memory, which made this loop the slowest part of the kernel).
+template <int GS>
+__device__ __forceinline__ void gn_partials_chunk(const float* y, float* part, int col0, int Cout, int lane) {
+#pragma unroll
+  for (int j0 = 0; j0 < 32; j0 += GS) {
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = j0; j < j0 + GS; ++j) {
+      s1 += y[j];
+      s2 += y[j] * y[j];
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    }
+    const int grp = (col0 + j0) / GS;
+    if (lane == 0 && col0 + j0 < Cout) {
+      part[grp * 2] = s1;
+      part[grp * 2 + 1] = s2;
+    }
+  }
 }
 
 // The epilogue of one output tile for one thread (= one output site): BN columns, 32 at a time from TMEM, bias and
@@ -126,34 +157,28 @@ __device__ __forceinline__ void conv_epilogue_tile(const ConvParams& p, const fl
       }
     }
     if (part) {
-      // GroupNorm partials of this warp's 32 rows: channels of a group are summed per row, rows by shuffle
-      for (int j0 = 0; j0 < 32; j0 += gs) {
-        float s1 = 0.f, s2 = 0.f;
-        for (int j = j0; j < j0 + gs && j < 32; ++j) {
-          s1 += y[j];
-          s2 += y[j] * y[j];
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-          s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-          s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-        }
-        const int grp = (col0 + j0) / gs;
-        if (lane == 0 && col0 + j0 < p.Cout) {
-          part[grp * 2] = s1;
-          part[grp * 2 + 1] = s2;
-        }
+      // the group width is uniform over the launch; one instantiation per width keeps y[] in registers
+      switch (gs) {
+        case 1: gn_partials_chunk<1>(y, part, col0, p.Cout, lane); break;
+        case 2: gn_partials_chunk<2>(y, part, col0, p.Cout, lane); break;
+        case 4: gn_partials_chunk<4>(y, part, col0, p.Cout, lane); break;
+        case 8: gn_partials_chunk<8>(y, part, col0, p.Cout, lane); break;
+        case 16: gn_partials_chunk<16>(y, part, col0, p.Cout, lane); break;
+        default: gn_partials_chunk<32>(y, part, col0, p.Cout, lane); break;
       }
     }
   }
 }
 
+template <int KCH>   // K chunks per ring stage
 __global__ void __launch_bounds__(CONV_THREADS, 1)
 conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
               const ConvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  ConvSmemTail* tail = reinterpret_cast<ConvSmemTail*>(smem + CSTAGES * CSTAGE_BYTES);
+  ConvSmemTail* tail = reinterpret_cast<ConvSmemTail*>(smem);
+  smem += CTAIL_BYTES;
+  const int CSTAGES = p.stages, CSTAGE_BYTES = p.stage_bytes;
   volatile int* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -196,18 +221,21 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const TileCoord c = conv_tile(tile, p, num_n);
-        for (int kb = 0; kb < num_kb; ++kb) {
-          const int tap = kb / chunks, cc = kb - tap * chunks;
-          const int dt = tap / 9, dh = (tap / 3) % 3, dw = tap % 3;
+        for (int kb = 0; kb < num_kb; kb += KCH) {
           if (!mbar_wait(&tail->empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY)) {
             ok = false;
             break;
           }
-          uint8_t* sa = smem + stage * CSTAGE_BYTES;
-          mbar_arrive_expect_tx(&tail->full[stage], a_bytes + b_bytes);
-          // out-of-range coordinates (negative or past the edge) read zeros: spatial and causal padding
-          tma_load_5d(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2 + p.halo, c.n, &tail->full[stage]);
-          tma_load_2d(sa + CA_BYTES, &tma_w, tap * p.Cin + cc * CBK, c.n_blk * p.BN, &tail->full[stage]);
+          mbar_arrive_expect_tx(&tail->full[stage], (a_bytes + b_bytes) * KCH);
+#pragma unroll
+          for (int q = 0; q < KCH; ++q) {
+            const int tap = (kb + q) / chunks, cc = kb + q - tap * chunks;
+            const int dt = tap / 9, dh = (tap / 3) % 3, dw = tap % 3;
+            uint8_t* sa = smem + stage * CSTAGE_BYTES + q * p.chunk_bytes;
+            // out-of-range coordinates (negative or past the edge) read zeros: spatial and causal padding
+            tma_load_5d(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2 + p.halo, c.n, &tail->full[stage]);
+            tma_load_2d(sa + CA_BYTES, &tma_w, tap * p.Cin + cc * CBK, c.n_blk * p.BN, &tail->full[stage]);
+          }
           if (++stage == CSTAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -227,15 +255,18 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * 256;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = 0; kb < num_kb; kb += KCH) {
         ok = __all_sync(0xffffffffu, mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL));
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = smem_u32(smem + stage * CSTAGE_BYTES);
-        const uint32_t b_addr = a_addr + CA_BYTES;
         if (elect_one()) {
-          // four MMAs of 16 bf16 (32 bytes) each along K
-          mma4_f16_ss(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
+          // per K chunk four MMAs of 16 bf16 (32 bytes) each along K; one commit for the whole stage
+#pragma unroll
+          for (int q = 0; q < KCH; ++q) {
+            const uint32_t aq = a_addr + q * p.chunk_bytes;
+            mma4_f16_ss(d_tmem, make_desc_k128(aq), make_desc_k128(aq + CA_BYTES), idesc, (kb + q) != 0);
+          }
           mma_commit(&tail->empty[stage]);
         }
         __syncwarp();
@@ -294,19 +325,17 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
 // Barriers as in the GEMM's pair kernel: both CTAs' loads count on the even CTA's `full`; stage release and
 // accumulator hand-over are one commit per CTA; every wait is bounded; the two cluster barriers are reached by all.
 // ---------------------------------------------------------------------------------------------
-constexpr int CP_STAGES = 6;
-constexpr int CP_STAGE_BYTES = CA_BYTES + 128 * 128;  // 32 KB: A box + at most 128 weight rows
 
 struct __align__(8) ConvPairSmemTail {
-  uint64_t full[CP_STAGES];
-  uint64_t empty[CP_STAGES];
+  uint64_t full[CMAX_STAGES];
+  uint64_t empty[CMAX_STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
   float bias[256];
 };
-constexpr int CONV_PAIR_SMEM_BYTES = CP_STAGES * CP_STAGE_BYTES + sizeof(ConvPairSmemTail) + 1024;
+static_assert(sizeof(ConvPairSmemTail) <= CTAIL_BYTES, "tail does not fit");
 
 // site tile m and column tile of pair-tile index `tile` for CTA `rank`: column tiles fastest, then pairs of site tiles
 __device__ __forceinline__ void conv_pair_tile(int tile, int rank, int num_m, int num_n, int& m, int& n_blk, bool& ok) {
@@ -316,12 +345,15 @@ __device__ __forceinline__ void conv_pair_tile(int tile, int rank, int num_m, in
   if (!ok) m = num_m - 1;
 }
 
+template <int KCH>   // K chunks per ring stage
 __global__ void __launch_bounds__(CONV_THREADS, 1)
 conv3d_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
                    const ConvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  ConvPairSmemTail* tail = reinterpret_cast<ConvPairSmemTail*>(smem + CP_STAGES * CP_STAGE_BYTES);
+  ConvPairSmemTail* tail = reinterpret_cast<ConvPairSmemTail*>(smem);
+  smem += CTAIL_BYTES;
+  const int CP_STAGES = p.stages, CP_STAGE_BYTES = p.stage_bytes;
   volatile int* abort_flag = &tail->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -373,17 +405,20 @@ conv3d_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_const
       conv_pair_tile(tile, rank, num_m, num_n, m, n_blk, tile_ok);
       const TileCoord c = conv_tile(m * num_n + n_blk, p, num_n);
       const int wrow0 = n_blk * p.BN + rank * half_n;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int tap = kb / chunks, cc = kb - tap * chunks;
-        const int dt = tap / 9, dh = (tap / 3) % 3, dw = tap % 3;
+      for (int kb = 0; kb < num_kb; kb += KCH) {
         ok = __all_sync(0xffffffffu, mbar_wait(&tail->empty[stage], phase ^ 1, abort_flag, p.status, ST_TIMEOUT_STAGE_EMPTY));
         if (!ok) break;
-        uint8_t* sa = smem + stage * CP_STAGE_BYTES;
         const uint32_t leader_full = cluster_addr(&tail->full[stage], 0);
         if (elect_one()) {
-          if (rank == 0) mbar_arrive_expect_tx(&tail->full[stage], stage_tx);
-          tma_load_5d_pair(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2 + p.halo, c.n, leader_full);
-          tma_load_2d_pair(sa + CA_BYTES, &tma_w, tap * p.Cin + cc * CBK, wrow0, leader_full);
+          if (rank == 0) mbar_arrive_expect_tx(&tail->full[stage], stage_tx * KCH);
+#pragma unroll
+          for (int q = 0; q < KCH; ++q) {
+            const int tap = (kb + q) / chunks, cc = kb + q - tap * chunks;
+            const int dt = tap / 9, dh = (tap / 3) % 3, dw = tap % 3;
+            uint8_t* sa = smem + stage * CP_STAGE_BYTES + q * p.chunk_bytes;
+            tma_load_5d_pair(sa, &tma_x, cc * CBK, c.w0 + dw - 1, c.h0 + dh - 1, c.t + dt - 2 + p.halo, c.n, leader_full);
+            tma_load_2d_pair(sa + CA_BYTES, &tma_w, tap * p.Cin + cc * CBK, wrow0, leader_full);
+          }
         }
         __syncwarp();
         if (++stage == CP_STAGES) { stage = 0; phase ^= 1; }
@@ -403,15 +438,18 @@ conv3d_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_const
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb; kb += KCH) {
           ok = __all_sync(0xffffffffu, mbar_wait(&tail->full[stage], phase, abort_flag, p.status, ST_TIMEOUT_TMA_FULL));
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * CP_STAGE_BYTES);
-          const uint32_t b_addr = a_addr + CA_BYTES;
           const uint32_t empty0 = cluster_addr(&tail->empty[stage], 0), empty1 = cluster_addr(&tail->empty[stage], 1);
           if (elect_one()) {
-            mma4_f16_pair(d_tmem, make_desc_k128(a_addr), make_desc_k128(b_addr), idesc, kb != 0);
+  #pragma unroll
+          for (int q = 0; q < KCH; ++q) {
+              const uint32_t aq = a_addr + q * p.chunk_bytes;
+              mma4_f16_pair(d_tmem, make_desc_k128(aq), make_desc_k128(aq + CA_BYTES), idesc, (kb + q) != 0);
+            }
             mma_commit_pair(empty0);   // the stage is free in both CTAs once these MMAs have read it
             mma_commit_pair(empty1);
           }
@@ -590,6 +628,15 @@ void choose_tile(int H, int W, int* bh, int* bw) {
   }
 }
 
+// K chunks per ring stage. A stage costs one barrier round trip in the producer and in the MMA issuer, a few hundred
+// cycles that a narrow tile's four MMAs per chunk (2 * BN tensor cycles) do not cover: narrow tiles put two or four
+// chunks behind one barrier. The count divides the 27 * chunks_per_tap chunks of a tile.
+int choose_kch(int bn, int chunks_per_tap) {
+  int want = bn >= 256 ? 1 : (bn >= 128 ? 2 : 4);
+  while (want > 1 && chunks_per_tap % want != 0) want >>= 1;
+  return want;
+}
+
 bool a16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -649,37 +696,56 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
     if (int e = make_tmap_2d(&twp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w, 27 * Cin, Cout, 27 * Cin * 2, CBK, p.BN / 2,
                              CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
-    if (int e = check_cuda(cudaFuncSetAttribute(conv3d_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                CONV_PAIR_SMEM_BYTES),
-                           "conv3d pair smem attribute"))
+    p.chunk_bytes = CA_BYTES + p.BN / 2 * 128;
+    p.kch = choose_kch(p.BN, (int)(Cin / CBK));
+    p.stage_bytes = p.kch * p.chunk_bytes;
+    p.stages = CSMEM_BUDGET / p.stage_bytes < CMAX_STAGES ? CSMEM_BUDGET / p.stage_bytes : CMAX_STAGES;
+    const int CONV_PAIR_SMEM_BYTES = 1024 + CTAIL_BYTES + p.stages * p.stage_bytes;
+    auto launch_pair = [&](auto kern) -> int {
+      if (int e = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CONV_PAIR_SMEM_BYTES),
+                             "conv3d pair smem attribute"))
+        return e;
+      cudaLaunchConfig_t cfg{};
+      cudaLaunchAttribute attr{};
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.blockDim = dim3(CONV_THREADS);
+      cfg.dynamicSmemBytes = CONV_PAIR_SMEM_BYTES;
+      cfg.stream = stream;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      cfg.gridDim = dim3(2 * (device_sm_count() / 2));
+      int max_clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters < 1)
+        return set_error(RH3_ARG_ERROR, "conv3d pair: no cluster of two CTAs can be resident");
+      const int64_t pair_tiles = (num_m + 1) / 2 * num_n;
+      cfg.gridDim = dim3(2 * static_cast<unsigned>(pair_tiles < max_clusters ? pair_tiles : max_clusters));
+      return check_cuda(cudaLaunchKernelEx(&cfg, kern, tx, twp, p), "conv3d pair launch");
+    };
+    if (int e = p.kch == 4 ? launch_pair(conv3d_pair_kernel<4>) : p.kch == 2 ? launch_pair(conv3d_pair_kernel<2>)
+                                                                            : launch_pair(conv3d_pair_kernel<1>))
       return e;
-    cudaLaunchConfig_t cfg{};
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.blockDim = dim3(CONV_THREADS);
-    cfg.dynamicSmemBytes = CONV_PAIR_SMEM_BYTES;
-    cfg.stream = stream;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    cfg.gridDim = dim3(2 * (device_sm_count() / 2));
-    int max_clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&max_clusters, conv3d_pair_kernel, &cfg) != cudaSuccess || max_clusters < 1)
-      return set_error(RH3_ARG_ERROR, "conv3d pair: no cluster of two CTAs can be resident");
-    const int64_t pair_tiles = (num_m + 1) / 2 * num_n;
-    cfg.gridDim = dim3(2 * static_cast<unsigned>(pair_tiles < max_clusters ? pair_tiles : max_clusters));
-    if (int e = check_cuda(cudaLaunchKernelEx(&cfg, conv3d_pair_kernel, tx, twp, p), "conv3d pair launch")) return e;
     return check_cuda(cudaGetLastError(), "conv3d pair launch");
   }
-  if (int e = check_cuda(cudaFuncSetAttribute(conv3d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              CONV_SMEM_BYTES),
-                         "conv3d smem attribute"))
-    return e;
+  p.chunk_bytes = CA_BYTES + p.BN * 128;
+  p.kch = choose_kch(p.BN, (int)(Cin / CBK));
+  p.stage_bytes = p.kch * p.chunk_bytes;
+  p.stages = CSMEM_BUDGET / p.stage_bytes < CMAX_STAGES ? CSMEM_BUDGET / p.stage_bytes : CMAX_STAGES;
+  const int CONV_SMEM_BYTES = 1024 + CTAIL_BYTES + p.stages * p.stage_bytes;
   const int64_t tiles = num_m * num_n;
   const int grid = tiles < device_sm_count() ? (int)tiles : device_sm_count();
-  conv3d_kernel<<<grid, CONV_THREADS, CONV_SMEM_BYTES, stream>>>(tx, tw, p);
+  auto launch_single = [&](auto kern) -> int {
+    if (int e = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CONV_SMEM_BYTES),
+                           "conv3d smem attribute"))
+      return e;
+    kern<<<grid, CONV_THREADS, CONV_SMEM_BYTES, stream>>>(tx, tw, p);
+    return 0;
+  };
+  if (int e = p.kch == 4 ? launch_single(conv3d_kernel<4>) : p.kch == 2 ? launch_single(conv3d_kernel<2>)
+                                                                        : launch_single(conv3d_kernel<1>))
+    return e;
   return check_cuda(cudaGetLastError(), "conv3d_causal launch");
 }
 
