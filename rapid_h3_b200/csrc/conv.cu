@@ -630,9 +630,10 @@ void choose_tile(int H, int W, int* bh, int* bw) {
 
 // K chunks per ring stage. A stage costs one barrier round trip in the producer and in the MMA issuer, a few hundred
 // cycles that a narrow tile's four MMAs per chunk (2 * BN tensor cycles) do not cover: narrow tiles put two or four
-// chunks behind one barrier. The count divides the 27 * chunks_per_tap chunks of a tile.
-int choose_kch(int bn, int chunks_per_tap) {
-  int want = bn >= 256 ? 1 : (bn >= 128 ? 2 : 4);
+// chunks behind one barrier; the pair kernel (32 KB per chunk at most) also does so for full-width tiles, where it
+// still gains 4-5 %. The count divides the 27 * chunks_per_tap chunks of a tile.
+int choose_kch(int bn, int chunks_per_tap, bool pair) {
+  int want = bn > 128 ? (pair ? 2 : 1) : (bn > 64 ? 2 : 4);
   while (want > 1 && chunks_per_tap % want != 0) want >>= 1;
   return want;
 }
@@ -697,7 +698,7 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
                              CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
     p.chunk_bytes = CA_BYTES + p.BN / 2 * 128;
-    p.kch = choose_kch(p.BN, (int)(Cin / CBK));
+    p.kch = choose_kch(p.BN, (int)(Cin / CBK), true);
     p.stage_bytes = p.kch * p.chunk_bytes;
     p.stages = CSMEM_BUDGET / p.stage_bytes < CMAX_STAGES ? CSMEM_BUDGET / p.stage_bytes : CMAX_STAGES;
     const int CONV_PAIR_SMEM_BYTES = 1024 + CTAIL_BYTES + p.stages * p.stage_bytes;
@@ -730,7 +731,7 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
     return check_cuda(cudaGetLastError(), "conv3d pair launch");
   }
   p.chunk_bytes = CA_BYTES + p.BN * 128;
-  p.kch = choose_kch(p.BN, (int)(Cin / CBK));
+  p.kch = choose_kch(p.BN, (int)(Cin / CBK), false);
   p.stage_bytes = p.kch * p.chunk_bytes;
   p.stages = CSMEM_BUDGET / p.stage_bytes < CMAX_STAGES ? CSMEM_BUDGET / p.stage_bytes : CMAX_STAGES;
   const int CONV_SMEM_BYTES = 1024 + CTAIL_BYTES + p.stages * p.stage_bytes;
