@@ -48,7 +48,8 @@ int rh3_selftest_wait_expiry(int64_t max_polls, int* left_normally, cudaStream_t
  * pattern 0: 64 MMAs per commit; 1 and 2: the issue pattern of a pipelined GEMM main loop (four-stage ring: per four
  * MMAs a wait on the stage's barrier, the descriptors and a commit), descriptors rebuilt per stage (1) or kept in
  * registers (2), or with the whole warp in the loop and one elected lane issuing (3): what the issuing thread's own
- * instruction stream costs. */
+ * instruction stream costs. pattern 4: pattern 0 with MMAs of 128 columns (half the work per instruction; *ops_out
+ * counts accordingly): the rate of the narrow tiles of the 128-channel convolutions. */
 int rh3_selftest_mma_rate(int kind, int64_t groups, int random_operands, int pattern, double* ops_out,
                           cudaStream_t stream);
 /* The main loop of a 128 x 256 int8 GEMM tile without an epilogue, on every SM (no reference counterpart): a four-stage
@@ -110,9 +111,11 @@ int rh3_norm_mod_rot_quant_rows_i8(const void* x, int64_t ldx, const void* w, fl
                                    void* q, int64_t ldq, float* s, cudaStream_t stream);
 
 /* ---- W8A8 row-wise-scaled GEMMs (tensor-core bound) ---------------------------------------- */
-/* Kernel choice of the GEMM entries below (no reference counterpart): 0 = one CTA per 128 x 256 tile, 1 (the default) = CTA
- * pairs (clusters of two, tcgen05 cta_group::2) on 256 x 256 tiles, each CTA loading its own half of B, for calls with
- * more than 128 rows and columns. Returns the previous setting; process-wide. Results are the same numbers either way. */
+/* Kernel choice of the GEMM entries below and of rh3_conv3d_causal (no reference counterpart): 0 = one CTA per tile, 1 (the
+ * default) = CTA pairs (clusters of two, tcgen05 cta_group::2): 256 x 256 GEMM tiles with each CTA loading its own half of
+ * B, for calls with more than 128 rows and columns; two site tiles of the convolution per pair with each CTA loading half of
+ * the weight rows, for calls with more than one site tile. Returns the previous setting; process-wide. Results are the same
+ * bits either way. */
 int rh3_gemm_use_pairs(int on);
 /* out[M,N] bf16 = ((acc * xs[m]) * ws[n]) + bias[n]; xq[M,K] (row stride lda), wq[N,K] contiguous.
  * bias may be NULL. acc_dump (optional, [M,N] int32 / fp32 bits) receives the raw accumulators.
