@@ -163,6 +163,11 @@ __device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* m
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
+// asks L2 for the 128-byte line that holds `p` (no register, no wait): an epilogue that will read a residual row
+// issues these before it waits for its accumulator, so the reads that follow hit L2 instead of HBM
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 // generic-proxy writes to smem that an async-proxy reader (tcgen05.mma, TMA store) will consume
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

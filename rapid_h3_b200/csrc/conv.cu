@@ -106,6 +106,19 @@ __device__ __forceinline__ void gn_partials_chunk(const float* y, float* part, i
   }
 }
 
+// The residual values of a thread's output site are asked into L2 while the tile's MMAs still run.
+__device__ __forceinline__ void conv_prefetch_residual(const ConvParams& p, const TileCoord& c, int n0, bool tile_ok,
+                                                       int quad, int lane) {
+  if (!p.residual || !tile_ok) return;
+  const int m = quad * 32 + lane;
+  const int hh = m / p.bw, ww = m - hh * p.bw;
+  const int h = c.h0 + hh, w = c.w0 + ww;
+  if (m >= p.bh * p.bw || h >= p.H || w >= p.W) return;
+  const int64_t site = ((static_cast<int64_t>(c.n) * p.T + c.t) * p.H + h) * p.W + w;
+  const __nv_bfloat16* r = p.residual + site * p.Cout + n0;
+  for (int cb = 0; cb < p.BN && n0 + cb < p.Cout; cb += 64) prefetch_l2(r + cb);
+}
+
 // The epilogue of one output tile for one thread (= one output site): BN columns, 32 at a time from TMEM, bias and
 // residual added, bf16 stored, GroupNorm partials of the warp's 32 rows. `acc_tmem` = TMEM address of the
 // accumulator's first column; `tile_ok` false = this CTA has no tile here (the odd tile of a pair): nothing is stored.
@@ -291,6 +304,11 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__
         tail->bias[i] = (p.bias && n0 + i < p.Cout) ? __bfloat162float(p.bias[n0 + i]) : 0.f;
       // the four warps leave together: a warp that gave up its wait takes the others with it at this barrier
       // (which also publishes the staged bias), so none of them waits at the next tile's barrier alone
+      if (tile == static_cast<int>(blockIdx.x)) conv_prefetch_residual(p, c, n0, true, quad, lane);
+      if (tile + static_cast<int>(gridDim.x) < num_tiles) {   // the next tile's residual, a whole epilogue ahead
+        const TileCoord c2 = conv_tile(tile + gridDim.x, p, num_n);
+        conv_prefetch_residual(p, c2, c2.n_blk * p.BN, true, quad, lane);
+      }
       const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
       if (bar_sync_or(1, 128, !got)) break;
       tc_fence_after();
@@ -481,6 +499,13 @@ conv3d_pair_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_const
       asm volatile("bar.sync 1, 128;" ::: "memory");
       for (int i = et; i < p.BN; i += 128)
         tail->bias[i] = (p.bias && n0 + i < p.Cout) ? __bfloat162float(p.bias[n0 + i]) : 0.f;
+      if (tile == pair) conv_prefetch_residual(p, c, n0, tile_ok, quad, lane);
+      if (tile + num_pairs < num_tiles) {   // the next tile's residual, a whole epilogue ahead
+        int m2, nb2;
+        bool ok2;
+        conv_pair_tile(tile + num_pairs, rank, num_m, num_n, m2, nb2, ok2);
+        conv_prefetch_residual(p, conv_tile(m2 * num_n + nb2, p, num_n), nb2 * p.BN, ok2, quad, lane);
+      }
       const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
       if (bar_sync_or(1, 128, !got)) break;
       tc_fence_after();

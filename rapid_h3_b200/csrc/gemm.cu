@@ -85,11 +85,45 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 
 // The epilogue of one accumulator row: 256 columns, 32 at a time from TMEM, dequantized and stored through the fused
 // epilogue EPI. `t_row` = TMEM address of this thread's row (lane) at the accumulator's first column.
+// The residual row of an epilogue that adds one (gated residual, fp16 residual): its BN columns are asked into L2
+// while the tile's MMAs still run, so the epilogue's loads do not wait on HBM (the residual of a step is far
+// larger than L2 and cold by the time its tile comes up).
+template <int EPI>
+__device__ __forceinline__ void prefetch_residual(const GemmParams& p, int row, bool row_ok, int n0) {
+  if (!row_ok) return;
+  if (EPI == EPI_GATED) {
+    const __nv_bfloat16* r = p.resid + static_cast<int64_t>(row) * p.ldr + n0;
+#pragma unroll
+    for (int c = 0; c < BN; c += 64)
+      if (n0 + c < p.N) prefetch_l2(r + c);
+  } else if (EPI == EPI_F16) {
+    if (p.resid_h) {
+      const __half* r = p.resid_h + static_cast<int64_t>(row) * p.ldr + n0;
+#pragma unroll
+      for (int c = 0; c < BN; c += 64)
+        if (n0 + c < p.N) prefetch_l2(r + c);
+    }
+  }
+}
+
+// The gated residual's values of chunks c and c + 1 of a row (eight 16-byte pieces; zeros off the edge).
+__device__ __forceinline__ void load_gated_residual(const GemmParams& p, int row, bool row_ok, int n0, int c, uint4* dst) {
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int col0 = n0 + (c + q) * 32;
+    const __nv_bfloat16* o = p.resid + static_cast<int64_t>(row) * p.ldr + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      dst[q * 4 + g] = (row_ok && col0 + g * 8 + 8 <= p.N) ? *reinterpret_cast<const uint4*>(o + g * 8) : make_uint4(0, 0, 0, 0);
+  }
+}
+
 template <int KIND_F8, int EPI>
 __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmemTail* tail, uint32_t t_row, int row,
-                                             bool row_ok, float xs, int n0) {
-  // two 32-column chunks are loaded per wait, so a tile costs four TMEM round trips instead of eight
-  auto chunk = [&](const uint32_t* r, int c) {
+                                             bool row_ok, float xs, int n0, const uint4* res0) {
+  // two 32-column chunks are loaded per wait, so a tile costs four TMEM round trips instead of eight; `old4` = the
+  // chunk's residual values (gated residual only), loaded one round trip ahead
+  auto chunk = [&](const uint32_t* r, int c, const uint4* old4) {
     const int col0 = n0 + c * 32;
     if (row_ok && col0 < p.N) {
       if (p.acc_dump) {
@@ -123,7 +157,7 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           if (col0 + g * 8 + 8 <= p.N) {
-            const uint4 old = *reinterpret_cast<const uint4*>(o + g * 8);
+            const uint4 old = old4[g];
             const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
             uint32_t w[4];
 #pragma unroll
@@ -212,6 +246,28 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
       }
     }
   };
+  if (EPI == EPI_GATED) {
+    // the residual of the next two chunks is fetched while the current two are computed (the loads of a row are
+    // 16 bytes each from a cold 8 KB-strided row: waiting for them chunk by chunk was most of this epilogue's time)
+    // (the first two chunks' values, `res0`, were fetched by the caller before it waited for the accumulator)
+    uint4 res[2][8];
+    auto load_res = [&](uint4* dst, int c) { load_gated_residual(p, row, row_ok, n0, c, dst); };
+#pragma unroll
+    for (int i = 0; i < 8; ++i) res[0][i] = res0[i];
+#pragma unroll
+    for (int it = 0; it < BN / 64; ++it) {
+      const int c = it * 2;
+      uint32_t ra[32], rb[32];
+      tmem_ld32(t_row + c * 32, ra);
+      tmem_ld32(t_row + c * 32 + 32, rb);
+      if (it + 1 < BN / 64) load_res(res[(it + 1) & 1], c + 2);
+      tmem_ld_wait_regs(ra);
+      tmem_ld_wait_regs(rb);
+      chunk(ra, c, res[it & 1]);
+      chunk(rb, c + 1, res[it & 1] + 4);
+    }
+    return;
+  }
 #pragma unroll 1
   for (int c = 0; c < BN / 32; c += 2) {
     uint32_t ra[32], rb[32];
@@ -219,8 +275,8 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
     tmem_ld32(t_row + c * 32 + 32, rb);
     tmem_ld_wait_regs(ra);
     tmem_ld_wait_regs(rb);
-    chunk(ra, c);
-    chunk(rb, c + 1);
+    chunk(ra, c, nullptr);
+    chunk(rb, c + 1, nullptr);
   }
 }
 
@@ -342,16 +398,25 @@ gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (EPI == EPI_F16 || EPI == EPI_SWIGLU_F16) tail->aux[c] = n < p.N ? __half2float(p.bias_h[n]) : 0.f;
         if (EPI == EPI_F16) tail->aux2[c] = (p.rscale_h && n < p.N) ? __half2float(p.rscale_h[n]) : 0.f;
       }
+      const int row = m_blk * BM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      if (tile == static_cast<int>(blockIdx.x)) prefetch_residual<EPI>(p, row, row_ok, n0);
+      if (tile + static_cast<int>(gridDim.x) < num_tiles) {   // the next tile's residual, a whole epilogue ahead
+        int m2, n2;
+        tile_coords(tile + gridDim.x, num_m, num_n, m2, n2);
+        const int row2 = m2 * BM + quad * 32 + lane;
+        prefetch_residual<EPI>(p, row2, row2 < p.M, n2 * BN);
+      }
+      uint4 res0[8];
+      if (EPI == EPI_GATED) load_gated_residual(p, row, row_ok, n0, 0, res0);
       // the four warps leave together: a warp that gave up its wait takes the others with it at this barrier
       // (which also publishes the staged columns), so none of them waits at the next tile's barrier alone
       const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
       if (bar_sync_or(1, 128, !got)) break;
       tc_fence_after();
-      const int row = m_blk * BM + quad * 32 + lane;
-      const bool row_ok = row < p.M;
       const float xs = row_ok ? p.xs[row] : 0.f;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_row<KIND_F8, EPI>(p, tail, t_row, row, row_ok, xs, n0);
+      epilogue_row<KIND_F8, EPI>(p, tail, t_row, row, row_ok, xs, n0, res0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tail->acc_empty[acc]);
@@ -525,14 +590,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (EPI == EPI_F16 || EPI == EPI_SWIGLU_F16) cols->aux[c] = n < p.N ? __half2float(p.bias_h[n]) : 0.f;
         if (EPI == EPI_F16) cols->aux2[c] = (p.rscale_h && n < p.N) ? __half2float(p.rscale_h[n]) : 0.f;
       }
+      const int row = m_blk * 2 * BM + static_cast<int>(rank) * BM + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      if (tile == pair) prefetch_residual<EPI>(p, row, row_ok, n0);
+      if (tile + num_pairs < num_tiles) {   // the next tile's residual, a whole epilogue ahead
+        int m2, n2;
+        tile_coords(tile + num_pairs, num_m, num_n, m2, n2);
+        const int row2 = m2 * 2 * BM + static_cast<int>(rank) * BM + quad * 32 + lane;
+        prefetch_residual<EPI>(p, row2, row2 < p.M, n2 * BN);
+      }
+      uint4 res0[8];
+      if (EPI == EPI_GATED) load_gated_residual(p, row, row_ok, n0, 0, res0);
       const bool got = mbar_wait(&tail->acc_full[acc], acc_phase, abort_flag, p.status, ST_TIMEOUT_ACC_FULL);
       if (bar_sync_or(1, 128, !got)) break;
       tc_fence_after();
-      const int row = m_blk * 2 * BM + static_cast<int>(rank) * BM + quad * 32 + lane;
-      const bool row_ok = row < p.M;
       const float xs = row_ok ? p.xs[row] : 0.f;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
-      epilogue_row<KIND_F8, EPI>(p, cols, t_row, row, row_ok, xs, n0);
+      epilogue_row<KIND_F8, EPI>(p, cols, t_row, row, row_ok, xs, n0, res0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(&tail->acc_empty[acc], 0);
