@@ -546,7 +546,7 @@ def main():
         def alg_bytes(lq_, lk_, h_):
             return h_ * 128 * (lq_ + 2 * lk_) + h_ * 128 * 2 * lq_
         roof["traffic"], roof["traffic_unit"] = attn_traffic(alg_bytes(lq, lk, heads_local))
-    roof_gemm = tensor_roof("gemm_fc1_swiglu", "gemm_w8a8_kernel<int8, SwiGLU epilogue> (fc1)")
+    roof_gemm = tensor_roof("gemm_fc1_swiglu", "gemm_pair_kernel<int8, SwiGLU epilogue> (fc1; gemm_w8a8_kernel when CTA pairs are off)")
     roof_quant = None
     ph = phases.get("quant_norm_mod")
     if ph and ph["ms"] > 0:
