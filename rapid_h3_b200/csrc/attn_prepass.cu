@@ -153,7 +153,8 @@ __global__ void __launch_bounds__(256) rope_scatter_kernel(const __nv_bfloat16* 
                                                            int H, int heads_per_rank, int64_t row0,
                                                            const __nv_bfloat16* __restrict__ qw,
                                                            const __nv_bfloat16* __restrict__ kw, float eps,
-                                                           const __nv_bfloat16* __restrict__ tab, const ScatterDst dst) {
+                                                           const __nv_bfloat16* __restrict__ tab,
+                                                           const __grid_constant__ ScatterDst dst) {
   const int lane = threadIdx.x & 31, l16 = lane & 15;
   const int64_t id = static_cast<int64_t>(blockIdx.x) * HW_PER_CTA + (threadIdx.x >> 4);
   const bool live = id < S * H;

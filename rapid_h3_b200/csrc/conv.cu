@@ -132,21 +132,37 @@ __device__ __forceinline__ void conv_epilogue_tile(const ConvParams& p, const fl
   const int64_t site = ((static_cast<int64_t>(c.n) * p.T + c.t) * p.H + h) * p.W + w;
   const uint32_t t_row = acc_tmem + (static_cast<uint32_t>(quad * 32) << 16);
   float* part = (p.gn_part && tile_ok) ? p.gn_part + (static_cast<int64_t>(m_tile) * 4 + quad) * GN_GROUPS * 2 : nullptr;
+  // the residual of a chunk is loaded one chunk ahead (zeros where there is none), so its latency is spent under the
+  // previous chunk's arithmetic and the TMEM round trip instead of in front of the additions
+  const bool has_res = p.residual && row_ok;
+  uint4 res_next[4];
+  auto load_res = [&](int cb, uint4* dst) {
+    const int col0 = n0 + cb;
+    const __nv_bfloat16* rs = p.residual + site * p.Cout + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      dst[g] = (has_res && cb < p.BN && col0 + g * 8 + 8 <= p.Cout) ? *reinterpret_cast<const uint4*>(rs + g * 8)
+                                                                     : make_uint4(0, 0, 0, 0);
+  };
+  load_res(0, res_next);
 #pragma unroll 1
   for (int cb = 0; cb < p.BN; cb += 32) {
     uint32_t r[32];
     tmem_ld32(t_row + cb, r);
+    uint4 res[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) res[g] = res_next[g];
+    load_res(cb + 32, res_next);
     tmem_ld_wait_regs(r);
     const int col0 = n0 + cb;
     float y[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) y[j] = __uint_as_float(r[j]) + bias_s[cb + j];
-    if (p.residual && row_ok) {
-      const __nv_bfloat16* rs = p.residual + site * p.Cout + col0;
+    if (has_res) {
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         if (col0 + g * 8 + 8 <= p.Cout) {
-          const uint4 v = *reinterpret_cast<const uint4*>(rs + g * 8);
+          const uint4 v = res[g];
           const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
