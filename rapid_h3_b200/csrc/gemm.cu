@@ -56,6 +56,7 @@ struct GemmParams {
   const __half* rscale_h;  // [N] or null (EPI_F16 with residual)
   const __half* resid_h;   // [M, N] row stride ldr, or null
   __half* out_h;           // row stride ldo
+  int wide;                // bf16 output (and gated residual) rows are 32-byte aligned: 32-byte accesses in the epilogue
   int* status;
 };
 
@@ -106,6 +107,20 @@ __device__ __forceinline__ void prefetch_residual(const GemmParams& p, int row, 
   }
 }
 
+// 32 bf16 outputs of one row (four 16-byte groups) to o: 32-byte stores where the row allows it, 16-byte stores for
+// what remains in range otherwise.
+__device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* o, const uint4* w4, int col0, int N, int wide) {
+#pragma unroll
+  for (int g = 0; g < 4; g += 2) {
+    if (wide && col0 + g * 8 + 16 <= N) {
+      st_global_32(o + g * 8, w4[g], w4[g + 1]);
+    } else {
+      if (col0 + g * 8 + 8 <= N) *reinterpret_cast<uint4*>(o + g * 8) = w4[g];
+      if (col0 + g * 8 + 16 <= N) *reinterpret_cast<uint4*>(o + g * 8 + 8) = w4[g + 1];
+    }
+  }
+}
+
 // The gated residual's values of chunks c and c + 1 of a row (eight 16-byte pieces; zeros off the edge).
 __device__ __forceinline__ void load_gated_residual(const GemmParams& p, int row, bool row_ok, int n0, int c, uint4* dst) {
 #pragma unroll
@@ -113,8 +128,14 @@ __device__ __forceinline__ void load_gated_residual(const GemmParams& p, int row
     const int col0 = n0 + (c + q) * 32;
     const __nv_bfloat16* o = p.resid + static_cast<int64_t>(row) * p.ldr + col0;
 #pragma unroll
-    for (int g = 0; g < 4; ++g)
-      dst[q * 4 + g] = (row_ok && col0 + g * 8 + 8 <= p.N) ? *reinterpret_cast<const uint4*>(o + g * 8) : make_uint4(0, 0, 0, 0);
+    for (int g = 0; g < 4; g += 2) {
+      if (p.wide && row_ok && col0 + g * 8 + 16 <= p.N) {
+        ld_global_32(o + g * 8, dst[q * 4 + g], dst[q * 4 + g + 1]);
+      } else {
+        dst[q * 4 + g] = (row_ok && col0 + g * 8 + 8 <= p.N) ? *reinterpret_cast<const uint4*>(o + g * 8) : make_uint4(0, 0, 0, 0);
+        dst[q * 4 + g + 1] = (row_ok && col0 + g * 8 + 16 <= p.N) ? *reinterpret_cast<const uint4*>(o + g * 8 + 8) : make_uint4(0, 0, 0, 0);
+      }
+    }
   }
 }
 
@@ -140,36 +161,36 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
       }
       if (EPI == EPI_PLAIN) {
         __nv_bfloat16* o = p.out + static_cast<int64_t>(row) * p.ldo + col0;
+        uint4 w4[4];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          if (col0 + g * 8 + 8 <= p.N) {
-            uint32_t w[4];
+          uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int e = g * 8 + 2 * j;
-              w[j] = pack_bf16x2(__fadd_rn(y[e], tail->aux[c * 32 + e]), __fadd_rn(y[e + 1], tail->aux[c * 32 + e + 1]));
-            }
-            *reinterpret_cast<uint4*>(o + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int j = 0; j < 4; ++j) {
+            const int e = g * 8 + 2 * j;
+            w[j] = pack_bf16x2(__fadd_rn(y[e], tail->aux[c * 32 + e]), __fadd_rn(y[e + 1], tail->aux[c * 32 + e + 1]));
           }
+          w4[g] = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        store_chunk_bf16(o, w4, col0, p.N, p.wide);
       } else if (EPI == EPI_GATED) {
         __nv_bfloat16* o = p.resid + static_cast<int64_t>(row) * p.ldr + col0;
+        uint4 w4[4];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          if (col0 + g * 8 + 8 <= p.N) {
-            const uint4 old = old4[g];
-            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-            uint32_t w[4];
+          const uint4 old = old4[g];
+          const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+          uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int e = g * 8 + 2 * j;
-              const float v0 = fmaf(bf16_round(y[e]), tail->aux[c * 32 + e], bf16_lo(ow[j]));
-              const float v1 = fmaf(bf16_round(y[e + 1]), tail->aux[c * 32 + e + 1], bf16_hi(ow[j]));
-              w[j] = pack_bf16x2(v0, v1);
-            }
-            *reinterpret_cast<uint4*>(o + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int j = 0; j < 4; ++j) {
+            const int e = g * 8 + 2 * j;
+            const float v0 = fmaf(bf16_round(y[e]), tail->aux[c * 32 + e], bf16_lo(ow[j]));
+            const float v1 = fmaf(bf16_round(y[e + 1]), tail->aux[c * 32 + e + 1], bf16_hi(ow[j]));
+            w[j] = pack_bf16x2(v0, v1);
           }
+          w4[g] = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        store_chunk_bf16(o, w4, col0, p.N, p.wide);
       } else if (EPI == EPI_F16) {
         // y1 = fp16(y + bias); with a residual: out = fp16(float(y1) * rscale + resid), two separate roundings
         __half* o = p.out_h + static_cast<int64_t>(row) * p.ldo + col0;
@@ -223,9 +244,10 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
         }
       } else {  // EPI_SWIGLU: 32 columns = 4 groups of [g0..g3 | u0..u3] -> 16 outputs
         __nv_bfloat16* o = p.out + static_cast<int64_t>(row) * p.ldo + (col0 >> 1);
+        uint4 w4[2];
 #pragma unroll
-        for (int hgrp = 0; hgrp < 2; ++hgrp) {  // 16 columns -> 8 outputs -> one 16-byte store
-          if (col0 + hgrp * 16 + 16 <= p.N) {
+        for (int hgrp = 0; hgrp < 2; ++hgrp) {  // 16 columns -> 8 outputs -> 16 bytes
+          {
             uint32_t w[4];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {  // one group of 8 columns -> 4 outputs
@@ -240,8 +262,14 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, const GemmSmem
               w[q * 2] = pack_bf16x2(h[0], h[1]);
               w[q * 2 + 1] = pack_bf16x2(h[2], h[3]);
             }
-            *reinterpret_cast<uint4*>(o + hgrp * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            w4[hgrp] = make_uint4(w[0], w[1], w[2], w[3]);
           }
+        }
+        if (p.wide && col0 + 32 <= p.N) {
+          st_global_32(o, w4[0], w4[1]);
+        } else {
+          if (col0 + 16 <= p.N) *reinterpret_cast<uint4*>(o) = w4[0];
+          if (col0 + 32 <= p.N) *reinterpret_cast<uint4*>(o + 8) = w4[1];
         }
       }
     }
@@ -722,6 +750,7 @@ extern "C" int rh3_gemm_w8a8(const void* xq, int64_t lda, const void* wq, const 
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.acc_dump = acc_dump; p.status = device_status_word();
+  p.wide = (reinterpret_cast<uintptr_t>(out) & 31) == 0 && ldo % 16 == 0;
   return kind == RH3_KIND_F8 ? launch_gemm<1, EPI_PLAIN>(ta, tb, tbp, p, stream) : launch_gemm<0, EPI_PLAIN>(ta, tb, tbp, p, stream);
 }
 
@@ -737,6 +766,7 @@ extern "C" int rh3_gemm_w8a8_gated_residual(const void* xq, int64_t lda, const v
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
   p.gate = static_cast<const __nv_bfloat16*>(gate);
   p.resid = static_cast<__nv_bfloat16*>(resid); p.ldr = ldr; p.status = device_status_word();
+  p.wide = (reinterpret_cast<uintptr_t>(resid) & 31) == 0 && ldr % 16 == 0;
   return kind == RH3_KIND_F8 ? launch_gemm<1, EPI_GATED>(ta, tb, tbp, p, stream) : launch_gemm<0, EPI_GATED>(ta, tb, tbp, p, stream);
 }
 
@@ -752,6 +782,7 @@ extern "C" int rh3_gemm_w8a8_swiglu(const void* xq, int64_t lda, const void* wq,
   GemmParams p{};
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.xs = xs; p.ws = ws;
   p.out = static_cast<__nv_bfloat16*>(out); p.ldo = ldo; p.status = device_status_word();
+  p.wide = (reinterpret_cast<uintptr_t>(out) & 31) == 0 && ldo % 16 == 0;
   return kind == RH3_KIND_F8 ? launch_gemm<1, EPI_SWIGLU>(ta, tb, tbp, p, stream) : launch_gemm<0, EPI_SWIGLU>(ta, tb, tbp, p, stream);
 }
 
