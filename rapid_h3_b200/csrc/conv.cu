@@ -45,6 +45,7 @@ struct ConvParams {
   __nv_bfloat16* out;
   float* gn_part;      // [num_m_tiles * 4][32][2] partial (sum, sumsq) per GroupNorm group, or null
   int stages, stage_bytes;   // ring: stage_bytes = kch * chunk_bytes
+  int wide;                  // out (and residual) rows are 32-byte aligned: 32-byte accesses in the epilogue
   int kch, chunk_bytes;      // K chunks per stage (one barrier round trip each), CA_BYTES + (weight rows a CTA loads) * 128
   int* status;
 };
@@ -140,9 +141,16 @@ __device__ __forceinline__ void conv_epilogue_tile(const ConvParams& p, const fl
     const int col0 = n0 + cb;
     const __nv_bfloat16* rs = p.residual + site * p.Cout + col0;
 #pragma unroll
-    for (int g = 0; g < 4; ++g)
-      dst[g] = (has_res && cb < p.BN && col0 + g * 8 + 8 <= p.Cout) ? *reinterpret_cast<const uint4*>(rs + g * 8)
-                                                                     : make_uint4(0, 0, 0, 0);
+    for (int g = 0; g < 4; g += 2) {
+      if (p.wide && has_res && cb < p.BN && col0 + g * 8 + 16 <= p.Cout) {
+        ld_global_32(rs + g * 8, dst[g], dst[g + 1]);
+      } else {
+        dst[g] = (has_res && cb < p.BN && col0 + g * 8 + 8 <= p.Cout) ? *reinterpret_cast<const uint4*>(rs + g * 8)
+                                                                       : make_uint4(0, 0, 0, 0);
+        dst[g + 1] = (has_res && cb < p.BN && col0 + g * 8 + 16 <= p.Cout) ? *reinterpret_cast<const uint4*>(rs + g * 8 + 8)
+                                                                            : make_uint4(0, 0, 0, 0);
+      }
+    }
   };
   load_res(0, res_next);
 #pragma unroll 1
@@ -176,12 +184,18 @@ __device__ __forceinline__ void conv_epilogue_tile(const ConvParams& p, const fl
     for (int j = 0; j < 32; ++j) y[j] = row_ok ? bf16_round(y[j]) : 0.f;  // what is stored; rows off the edge add 0
     if (row_ok) {
       __nv_bfloat16* o = p.out + site * p.Cout + col0;
+      uint4 w4[4];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        if (col0 + g * 8 + 8 <= p.Cout) {
-          *reinterpret_cast<uint4*>(o + g * 8) =
-              make_uint4(pack_bf16x2(y[g * 8], y[g * 8 + 1]), pack_bf16x2(y[g * 8 + 2], y[g * 8 + 3]),
-                         pack_bf16x2(y[g * 8 + 4], y[g * 8 + 5]), pack_bf16x2(y[g * 8 + 6], y[g * 8 + 7]));
+      for (int g = 0; g < 4; ++g)
+        w4[g] = make_uint4(pack_bf16x2(y[g * 8], y[g * 8 + 1]), pack_bf16x2(y[g * 8 + 2], y[g * 8 + 3]),
+                           pack_bf16x2(y[g * 8 + 4], y[g * 8 + 5]), pack_bf16x2(y[g * 8 + 6], y[g * 8 + 7]));
+#pragma unroll
+      for (int g = 0; g < 4; g += 2) {
+        if (p.wide && col0 + g * 8 + 16 <= p.Cout) {
+          st_global_32(o + g * 8, w4[g], w4[g + 1]);
+        } else {
+          if (col0 + g * 8 + 8 <= p.Cout) *reinterpret_cast<uint4*>(o + g * 8) = w4[g];
+          if (col0 + g * 8 + 16 <= p.Cout) *reinterpret_cast<uint4*>(o + g * 8 + 8) = w4[g + 1];
         }
       }
     }
@@ -720,6 +734,7 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
   p.out = static_cast<__nv_bfloat16*>(out);
   p.gn_part = gn_part;
   p.status = device_status_word();
+  p.wide = (reinterpret_cast<uintptr_t>(out) & 31) == 0 && (!residual || (reinterpret_cast<uintptr_t>(residual) & 31) == 0);
   CUtensorMap tx, tw;
   const uint64_t Tin = (uint64_t)(T + halo_frames);  // frames held by x
   const uint64_t dims[5] = {(uint64_t)Cin, (uint64_t)W, (uint64_t)H, Tin, (uint64_t)N};
