@@ -80,6 +80,16 @@ def main():
                 _lib.call("rh3_selftest_mma_rate", 0, 2000, 0, pattern, ctypes.addressof(ops), _lib.stream())
             ms = _time(fn, 3)
             print(f"mma_rate int8 zero operands, {name}: {ms:.3f} ms per launch, {ops.value / ms / 1e9:.0f} TOP/s", flush=True)
+        # 128-column MMAs (the convolution's narrow tiles) against 256-column ones, random operands
+        for kind, name in ((2, "bf16"), (0, "int8")):
+            for pattern, cols in ((0, 256), (4, 128)):
+                ops = ctypes.c_double(0)
+
+                def fn():
+                    _lib.call("rh3_selftest_mma_rate", kind, 2000, 1, pattern, ctypes.addressof(ops), _lib.stream())
+                ms = _time(fn, 3)
+                print(f"mma_rate {name} random operands, {cols}-column MMAs: {ms:.3f} ms per launch, {ops.value / ms / 1e9:.0f} TOP/s",
+                      flush=True)
         # the GEMM main loop without an epilogue: MMA rate against the bytes an SM takes in per stage
         for src_mb, where in ((48, "L2-resident source (48 MB)"), (2048, "HBM-resident source (2 GB)")):
             src = torch.randint(-127, 128, (src_mb << 20,), device="cuda", dtype=torch.int8)

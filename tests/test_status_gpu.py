@@ -63,8 +63,14 @@ def test_tensor_pipe_probe_returns_and_reports_a_plausible_rate(kind, random_ope
     lib.check_status()
     tops = ops.value * 3 / e0.elapsed_time(e1) / 1e9
     assert tops > (1100 if kind == 2 else 2200), tops
+    # pattern 4: the same with 128-column MMAs (half the work per instruction), the narrow tiles of the convolution
+    lib.call("rh3_selftest_mma_rate", kind, groups, random_operands, 4, ctypes.addressof(ops), lib.stream())
+    lib.check_status()
+    assert ops.value == sms * groups * 64 * 2 * 128 * 128 * (16 if kind == 2 else 32)
     with pytest.raises(RuntimeError):
         lib.call("rh3_selftest_mma_rate", 3, groups, 0, 0, ctypes.addressof(ops), lib.stream())
+    with pytest.raises(RuntimeError):
+        lib.call("rh3_selftest_mma_rate", kind, groups, 0, 5, ctypes.addressof(ops), lib.stream())
 
 
 @pytest.mark.parametrize("fill", [0, 16384, 49152])
