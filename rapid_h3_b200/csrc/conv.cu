@@ -30,7 +30,7 @@ constexpr int CBK = 64;         // channels per K chunk (128 bytes of bf16)
 constexpr int CA_BYTES = CBM * 128;
 constexpr int CMAX_STAGES = 12;       // ring depth: as many stages of CA_BYTES + (weight rows) * 128 bytes as fit
 constexpr int CTAIL_BYTES = 2048;     // barriers and the staged bias, in front of the ring
-constexpr int CSMEM_BUDGET = 227 * 1024 - 1024 - CTAIL_BYTES;   // what the ring may take (1 KB of alignment slack)
+constexpr int CRING_MAX_BYTES = 227 * 1024 - 1024 - CTAIL_BYTES;   // what the ring may take (1 KB of alignment slack)
 constexpr int CONV_THREADS = 192;
 constexpr int GN_GROUPS = 32;
 
@@ -756,7 +756,7 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
     p.chunk_bytes = CA_BYTES + p.BN / 2 * 128;
     p.kch = choose_kch(p.BN, (int)(Cin / CBK), true);
     p.stage_bytes = p.kch * p.chunk_bytes;
-    p.stages = CSMEM_BUDGET / p.stage_bytes < CMAX_STAGES ? CSMEM_BUDGET / p.stage_bytes : CMAX_STAGES;
+    p.stages = CRING_MAX_BYTES / p.stage_bytes < CMAX_STAGES ? CRING_MAX_BYTES / p.stage_bytes : CMAX_STAGES;
     const int CONV_PAIR_SMEM_BYTES = 1024 + CTAIL_BYTES + p.stages * p.stage_bytes;
     auto launch_pair = [&](auto kern) -> int {
       if (int e = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CONV_PAIR_SMEM_BYTES),
@@ -789,7 +789,7 @@ extern "C" int rh3_conv3d_causal(const void* x, const void* w, const void* bias,
   p.chunk_bytes = CA_BYTES + p.BN * 128;
   p.kch = choose_kch(p.BN, (int)(Cin / CBK), false);
   p.stage_bytes = p.kch * p.chunk_bytes;
-  p.stages = CSMEM_BUDGET / p.stage_bytes < CMAX_STAGES ? CSMEM_BUDGET / p.stage_bytes : CMAX_STAGES;
+  p.stages = CRING_MAX_BYTES / p.stage_bytes < CMAX_STAGES ? CRING_MAX_BYTES / p.stage_bytes : CMAX_STAGES;
   const int CONV_SMEM_BYTES = 1024 + CTAIL_BYTES + p.stages * p.stage_bytes;
   const int64_t tiles = num_m * num_n;
   const int grid = tiles < device_sm_count() ? (int)tiles : device_sm_count();
