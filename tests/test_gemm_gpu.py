@@ -183,3 +183,39 @@ def test_argument_errors(ops):
         gemm.int8_gemm(xq.cuda().float(), xs.cuda(), wq.cuda(), ws.cuda())
     with pytest.raises(RuntimeError):
         gemm.int8_gemm(xq, xs, wq, ws)
+
+
+def test_epilogues_on_rows_that_are_only_16_byte_aligned(ops):
+    """Outputs and residuals whose rows are 32-byte aligned go through 32-byte stores and loads, others through the
+    16-byte path: both give the same bits (plain, gated residual, SwiGLU), here with a row stride of N + 8 elements
+    and a base 16 bytes off a 32-byte boundary."""
+    gemm, kernels, lib = ops
+    m, n, k = 300, 512, 256
+    x, w, _ = inputs.linear_case(m, k, n, seed=31)
+    xq, xs = (t.cuda() for t in ol.quantize_rows(x, "int8_rowwise"))
+    wq, ws = (t.cuda() for t in ol.quantize_weight(w, "int8_rowwise"))
+    g = inputs.gen(5)
+    gate = torch.randn(n, generator=g).to(torch.bfloat16).cuda()
+    resid0 = torch.randn(m, n, generator=g).to(torch.bfloat16).cuda()
+
+    def odd_view(rows, cols):   # [rows, cols] view: row stride cols + 8, base 16 bytes into a 32-byte aligned buffer
+        buf = torch.zeros(rows * (cols + 8) + 8, dtype=torch.bfloat16, device="cuda")
+        v = buf[8:].view(rows, cols + 8)[:, :cols]
+        assert v.data_ptr() % 32 == 16 and v.stride(0) % 16 == 8
+        return v
+
+    y = gemm.int8_gemm(xq, xs, wq, ws)
+    y_odd = odd_view(m, n)
+    gemm.int8_gemm(xq, xs, wq, ws, out=y_odd)
+    assert torch.equal(y_odd, y)
+    r = resid0.clone()
+    gemm.int8_gemm_gated_residual(xq, xs, wq, ws, gate, r)
+    r_odd = odd_view(m, n)
+    r_odd.copy_(resid0)
+    gemm.int8_gemm_gated_residual(xq, xs, wq, ws, gate, r_odd)
+    assert torch.equal(r_odd, r)
+    s = gemm.int8_gemm_swiglu(xq, xs, wq, ws)
+    s_odd = odd_view(m, n // 2)
+    gemm.int8_gemm_swiglu(xq, xs, wq, ws, out=s_odd)
+    lib.check_status()
+    assert torch.equal(s_odd, s)
