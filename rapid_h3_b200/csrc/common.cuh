@@ -474,15 +474,15 @@ __device__ __forceinline__ float warp_sum_xor(float v) {
 // exact quantizer steps without the conversion unit
 // ---------------------------------------------------------------------------------------------
 // int8 code of round_half_even(y / s) (|y / s| <= 127 by construction of s), returned in the low byte.
-// y * (1/s) is rounded by adding 1.5 * 2^23; only when the product lands within 2^-14 of a tie (its distance from
-// the exact quotient is at most 1.5e-5) is the exact IEEE quotient computed, so the code always equals the one a
-// true division would give.
+// t = fma(y, 1/s, 1.5 * 2^23) rounds the exact product P = y * (1/s) to the integer r = t - 1.5 * 2^23; d = fma(y, 1/s, -r)
+// is P's distance from r. P and the rounded quotient fl(y / s) each differ from the true quotient by at most
+// 127 * 2^-24 = 7.6e-6, so they can round to different integers only when |d| > 0.5 - 2^-14; only then is the exact
+// IEEE quotient computed. The code therefore always equals the one a true division would give.
 __device__ __forceinline__ uint32_t quant_code_i8(float y, float s, float inv) {
   const float kMagic = 12582912.f;
-  const float yq = __fmul_rn(y, inv);
-  float t = __fadd_rn(yq, kMagic);
-  const float r = __fsub_rn(t, kMagic);
-  if (fabsf(yq - r) > 0.5f - 6.103515625e-5f) t = __fadd_rn(__fdiv_rn(y, s), kMagic);
+  float t = fmaf(y, inv, kMagic);
+  const float d = fmaf(y, inv, -__fsub_rn(t, kMagic));
+  if (fabsf(d) > 0.5f - 6.103515625e-5f) t = __fadd_rn(__fdiv_rn(y, s), kMagic);
   return __float_as_uint(t);  // low byte = two's complement code
 }
 // e4m3 code of clamp(y / s, +-448) rounded to nearest even. The fast path converts y * (1/s); the exact
@@ -504,12 +504,10 @@ __device__ __forceinline__ uint2 quant8_i8(const float* y, float s, float inv) {
   bool near = false;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float yq = __fmul_rn(y[j], inv);
-    t[j] = __fadd_rn(yq, kMagic);
-    // |yq - round(yq)| <= 0.5 always. y * (1/s) differs from the exact quotient by at most 127 * 2^-23 = 1.5e-5
-    // (one rounding in 1/s, one in the product), so only values within 2^-14 of a tie can round differently;
-    // a wider window would send most warps down the division path (any of 256 values triggers it).
-    near |= fabsf(__fsub_rn(yq, __fsub_rn(t[j], kMagic))) > 0.5f - 6.103515625e-5f;
+    t[j] = fmaf(y[j], inv, kMagic);
+    // the product's distance from the integer it rounded to; a wider window than 2^-14 below a tie would send most
+    // warps down the division path (any of 256 values triggers it)
+    near |= fabsf(fmaf(y[j], inv, -__fsub_rn(t[j], kMagic))) > 0.5f - 6.103515625e-5f;
   }
   if (near) {
 #pragma unroll  // static indices: a rolled loop would push the caller's register array to local memory

@@ -13,9 +13,9 @@
 //   KIND_NORMMOD rms_norm(x) * w * (1 + scale[idx[row]]) + shift[idx[row]]
 //   KIND_HEADS   x given group-major [G, M, gw] (gw = 128: head-major attention output);
 //                output column k = group k/gw, channel k%gw
-// The division x / s is done as x * (1/s) with an exact IEEE re-division only for the rare values
-// that land within 2^-14 of a rounding tie (the product is at most 1.5e-5 away from the true quotient),
-// which keeps the codes identical to a true division.
+// The division x / s is done as fma(x, 1/s, 1.5 * 2^23) with an exact IEEE re-division only for the rare values
+// whose product lands within 2^-14 of a rounding tie (product and rounded quotient are each at most 7.6e-6 away
+// from the true quotient), which keeps the codes identical to a true division.
 #include "common.cuh"
 #include "rapidh3_b200.h"
 
