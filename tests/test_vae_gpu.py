@@ -49,7 +49,7 @@ def test_conv3d_causal_matches_oracle(vae, shape):
 
 @pytest.mark.parametrize("shape", [(1, 3, 6, 21, 64, 64), (2, 4, 9, 10, 128, 256), (1, 5, 7, 5, 192, 192),
                                    (1, 2, 24, 42, 64, 512), (1, 2, 6, 7, 64, 288), (1, 3, 8, 16, 128, 128),
-                                   (1, 2, 8, 16, 256, 64)])
+                                   (1, 2, 8, 16, 256, 64), (1, 2, 4, 8, 64, 32), (1, 2, 4, 9, 128, 96)])
 def test_cta_pair_kernel_equals_the_single_cta_kernel(vae, shape):
     """The convolution on CTA pairs (two site tiles per pair, half of the weight rows per CTA; the default) against
     the single-CTA kernel on the same inputs: outputs and GroupNorm partial sums bit for bit, including an odd number
